@@ -1,0 +1,363 @@
+// Fused softmax + cross-entropy (loss and gradient in one pass), fused MSE, the optimizer updates
+// (SGD / momentum / Nesterov with the CPU path's first-step rule; Adam / AdamW / AMSGrad) and the
+// few reductions the training path needs (sum over an axis, row argmax).
+// Semantics follow the reference CPU code: src/ops/loss.c:33-137,176-351, src/optim/sgd.c:13-115,
+// src/optim/adam.c:11-75, src/ops/reduction.c:158-198,473-513.
+#include "nc_common.cuh"
+#include "../../include/nocta_cuda.h"
+
+using namespace ncc;
+
+namespace {
+
+constexpr int kThreads = 256;
+
+// ---------------------------------------------------------------------------------------------
+// Cross entropy.  One warp per row: row max, sum of exponentials (f32 exp, double accumulation of
+// the per-row loss), optional gradient (softmax - onehot) * scale.  Per-block partial losses go to
+// `partial`; the last block (ticket counter) adds them in index order, so the loss is bit-stable
+// from run to run.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) ce_fused_kernel(float* __restrict__ loss, float* __restrict__ grad,
+                                                            const float* __restrict__ logits,
+                                                            const int64_t* __restrict__ targets, int N, int C,
+                                                            float gscale, double* __restrict__ partial,
+                                                            unsigned int* __restrict__ ticket) {
+    __shared__ double sh[32];
+    __shared__ bool last;
+    const int lane = threadIdx.x & 31;
+    const int warps_per_block = blockDim.x >> 5;
+    const int gw = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+    const int nw = gridDim.x * warps_per_block;
+    double acc = 0.0;
+    for (int r = gw; r < N; r += nw) {
+        const float* x = logits + (size_t)r * C;
+        float m = -INFINITY;
+        for (int c = lane; c < C; c += 32) m = fmaxf(m, x[c]);
+        m = warp_max(m);
+        float s = 0.f;
+        for (int c = lane; c < C; c += 32) s += expf(x[c] - m);
+        s = warp_sum(s);
+        const int64_t lab64 = targets[r];
+        const int lab = (int)lab64;  // the CPU path reads labels through (int) (loss.c:278)
+        const bool valid = lab >= 0 && lab < C;
+        if (lane == 0 && valid) acc += (double)logf(s) + (double)m - (double)x[lab];
+        if (grad) {
+            float inv = 1.f / s;
+            float* g = grad + (size_t)r * C;
+            for (int c = lane; c < C; c += 32) {
+                float p = expf(x[c] - m) * inv;
+                if (valid && c == lab) p -= 1.f;
+                g[c] = p * gscale;
+            }
+        }
+    }
+    double b = block_sum(acc, sh);
+    if (threadIdx.x == 0) {
+        partial[blockIdx.x] = b;
+        __threadfence();
+        unsigned int t = atomicAdd(ticket, 1u);
+        last = (t == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (last && threadIdx.x == 0) {
+        __threadfence();
+        double tot = 0.0;
+        for (unsigned int i = 0; i < gridDim.x; i++) tot += ((volatile double*)partial)[i];
+        if (loss) *loss = (float)(tot / (double)N);
+        *ticket = 0;
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) mse_fused_kernel(float* __restrict__ loss, float* __restrict__ gp,
+                                                             float* __restrict__ gt, const float* __restrict__ p,
+                                                             const float* __restrict__ t, size_t n, double gscale,
+                                                             double* __restrict__ partial,
+                                                             unsigned int* __restrict__ ticket) {
+    __shared__ double sh[32];
+    __shared__ bool last;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    double acc = 0.0;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float d = p[i] - t[i];
+        acc += (double)d * (double)d;
+        float g = (float)(gscale * (double)d);
+        if (gp) gp[i] = g;
+        if (gt) gt[i] = -g;
+    }
+    double b = block_sum(acc, sh);
+    if (threadIdx.x == 0) {
+        partial[blockIdx.x] = b;
+        __threadfence();
+        unsigned int k = atomicAdd(ticket, 1u);
+        last = (k == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (last && threadIdx.x == 0) {
+        __threadfence();
+        double tot = 0.0;
+        for (unsigned int i = 0; i < gridDim.x; i++) tot += ((volatile double*)partial)[i];
+        if (loss) *loss = (float)(tot / (double)n);
+        *ticket = 0;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Optimizers.  The CPU path computes in double and stores f32; so do these.
+// 20 B/param (SGD momentum: p, v, g read; p, v written), 28 B/param (Adam).
+// ---------------------------------------------------------------------------------------------
+struct SgdArgs {
+    double lr, momentum, dampening, wd, gscale;
+    int nesterov, first, write_grad;
+};
+
+__global__ void __launch_bounds__(kThreads) sgd_kernel(float* __restrict__ p, float* __restrict__ v,
+                                                       float* __restrict__ g, SgdArgs a, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        double gi = (double)g[i] * a.gscale;
+        double pi = (double)p[i];
+        if (a.wd != 0.0) {
+            // the CPU path stores the decayed gradient as f32 before using it (sgd.c:24-30)
+            float gf = (float)(gi + a.wd * pi);
+            if (a.write_grad) g[i] = gf;
+            gi = (double)gf;
+        }
+        double upd = gi;
+        if (v) {
+            double vi = (double)v[i];
+            vi = a.first ? gi : a.momentum * vi + (1.0 - a.dampening) * gi;
+            float vf = (float)vi;
+            v[i] = vf;
+            vi = (double)vf;
+            upd = a.nesterov ? gi + a.momentum * vi : vi;
+        }
+        p[i] = (float)(pi - a.lr * upd);
+    }
+}
+
+struct AdamArgs {
+    double lr, b1, b2, eps, wd, bc1, bc2, gscale;
+};
+
+__global__ void __launch_bounds__(kThreads) adam_kernel(float* __restrict__ p, float* __restrict__ m,
+                                                        float* __restrict__ v, float* __restrict__ vmax,
+                                                        const float* __restrict__ g, AdamArgs a, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        double gi = (double)g[i] * a.gscale;
+        double pi = (double)p[i];
+        if (a.wd != 0.0) pi = pi - a.lr * a.wd * pi;
+        double mi = a.b1 * (double)m[i] + (1.0 - a.b1) * gi;
+        double vi = a.b2 * (double)v[i] + (1.0 - a.b2) * gi * gi;
+        m[i] = (float)mi;
+        v[i] = (float)vi;
+        double mh = mi / a.bc1, vh = vi / a.bc2;
+        if (vmax) {
+            double vm = fmax((double)vmax[i], vh);
+            float vmf = (float)vm;
+            vmax[i] = vmf;
+            vh = (double)vmf;
+        }
+        p[i] = (float)(pi - a.lr * mh / (sqrt(vh) + a.eps));
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// out[o][i] = sum_r in[o][r][i]  (double accumulation, as src/ops/reduction.c:158-198).
+// A block owns 32 consecutive `i` for one `o`; 8 row-groups stride over r; coalesced along i.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) sum_axis_kernel(float* __restrict__ out, const float* __restrict__ in,
+                                                       size_t reduce_dim, size_t inner) {
+    __shared__ double sh[8][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const size_t o = blockIdx.y;
+    const size_t i = (size_t)blockIdx.x * 32 + tx;
+    double acc = 0.0;
+    if (i < inner) {
+        const float* base = in + o * reduce_dim * inner + i;
+        for (size_t r = ty; r < reduce_dim; r += 8) acc += (double)base[r * inner];
+    }
+    sh[ty][tx] = acc;
+    __syncthreads();
+    if (ty == 0 && i < inner) {
+        double t = 0.0;
+#pragma unroll
+        for (int k = 0; k < 8; k++) t += sh[k][tx];
+        out[o * inner + i] = (float)t;
+    }
+}
+
+// inner == 1: one warp per output, lanes stride over the reduced axis
+__global__ void __launch_bounds__(kThreads) sum_rows_kernel(float* __restrict__ out, const float* __restrict__ in,
+                                                            size_t outer, size_t reduce_dim) {
+    const int lane = threadIdx.x & 31;
+    const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    for (size_t o = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; o < outer; o += warps) {
+        double acc = 0.0;
+        for (size_t r = lane; r < reduce_dim; r += 32) acc += (double)in[o * reduce_dim + r];
+        acc = warp_sum(acc);
+        if (lane == 0) out[o] = (float)acc;
+    }
+}
+
+// First maximum per row (strict >), int64 result (src/ops/reduction.c:473-513).
+__global__ void __launch_bounds__(kThreads) argmax_rows_kernel(int64_t* __restrict__ out, const float* __restrict__ in,
+                                                               size_t rows, size_t cols) {
+    const int lane = threadIdx.x & 31;
+    const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    for (size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+        const float* x = in + r * cols;
+        float best = -INFINITY;
+        long long bi = -1;
+        for (size_t c = lane; c < cols; c += 32) {
+            float v = x[c];
+            if (bi < 0 || v > best) { best = v; bi = (long long)c; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi >= 0 && (bi < 0 || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
+        }
+        if (lane == 0) out[r] = bi < 0 ? 0 : bi;
+    }
+}
+
+struct LossScratch { double* partial; unsigned int* ticket; int blocks; };
+
+int loss_scratch(LossScratch* ls, long long work, cudaStream_t st) {
+    int blocks = grid_for(work, kThreads, 4);
+    // layout: [ticket (16 B)] [partials]
+    char* base = (char*)scratch(0, 16 + sizeof(double) * (size_t)blocks, st);
+    if (!base) return NC_CUDA_ERR_RUNTIME;
+    static void* zeroed = nullptr;
+    if (zeroed != base) {  // (re)allocated: the ticket must start at zero
+        cudaError_t e = cudaMemsetAsync(base, 0, 16, st);
+        if (e != cudaSuccess) return set_status(NC_CUDA_ERR_RUNTIME, "loss scratch memset failed");
+        zeroed = base;
+    }
+    ls->ticket = (unsigned int*)base;
+    ls->partial = (double*)(base + 16);
+    ls->blocks = blocks;
+    return NC_CUDA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int nc_cuda_cross_entropy_fused_f32_ex(float* loss, float* grad, const float* logits, const int64_t* targets,
+                                       int N, int C, float grad_scale, void* stream) {
+    NCC_REQUIRE(logits && targets && N > 0 && C > 0, "cross_entropy: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+    LossScratch ls;
+    int rc = loss_scratch(&ls, (long long)N * 32, st);
+    if (rc) return rc;
+    ce_fused_kernel<<<ls.blocks, kThreads, 0, st>>>(loss, grad, logits, targets, N, C, grad_scale / (float)N,
+                                                    ls.partial, ls.ticket);
+    NCC_COUNT_LAUNCH();
+    return launch_status("cross_entropy");
+}
+
+int nc_cuda_mse_fused_f32_ex(float* loss, float* gp, float* gt, const float* pred, const float* target, size_t n,
+                             float grad_scale, void* stream) {
+    NCC_REQUIRE(pred && target && n > 0, "mse: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+    LossScratch ls;
+    int rc = loss_scratch(&ls, (long long)n, st);
+    if (rc) return rc;
+    mse_fused_kernel<<<ls.blocks, kThreads, 0, st>>>(loss, gp, gt, pred, target, n,
+                                                     2.0 * (double)grad_scale / (double)n, ls.partial, ls.ticket);
+    NCC_COUNT_LAUNCH();
+    return launch_status("mse");
+}
+
+void nc_cuda_cross_entropy_forward_f32(float* loss, const float* logits, const int64_t* targets, int N, int C) {
+    nc_cuda_cross_entropy_fused_f32_ex(loss, nullptr, logits, targets, N, C, 1.f, current_stream());
+}
+void nc_cuda_cross_entropy_backward_f32(float* grad, const float* logits, const int64_t* targets, int N, int C) {
+    nc_cuda_cross_entropy_fused_f32_ex(nullptr, grad, logits, targets, N, C, 1.f, current_stream());
+}
+
+int nc_cuda_sgd_update_f32_ex(float* param, float* velocity, float* grad, double lr, double momentum,
+                              double dampening, double weight_decay, int nesterov, int first_step,
+                              double grad_scale, size_t n, void* stream) {
+    if (n == 0) return NC_CUDA_OK;
+    NCC_REQUIRE(param && grad, "sgd: null pointer");
+    SgdArgs a{lr, momentum, dampening, weight_decay, grad_scale, nesterov, first_step, 1};
+    float* v = (momentum != 0.0) ? velocity : nullptr;
+    NCC_REQUIRE(momentum == 0.0 || v, "sgd: momentum without a velocity buffer");
+    sgd_kernel<<<grid_for((long long)n, kThreads), kThreads, 0, (cudaStream_t)stream>>>(param, v, grad, a, n);
+    NCC_COUNT_LAUNCH();
+    return launch_status("sgd");
+}
+
+int nc_cuda_adam_update_f32_ex(float* param, float* m, float* v, float* v_max, const float* grad, double lr,
+                               double beta1, double beta2, double eps, double weight_decay, double bias_corr1,
+                               double bias_corr2, double grad_scale, size_t n, void* stream) {
+    if (n == 0) return NC_CUDA_OK;
+    NCC_REQUIRE(param && m && v && grad, "adam: null pointer");
+    AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2, grad_scale};
+    adam_kernel<<<grid_for((long long)n, kThreads), kThreads, 0, (cudaStream_t)stream>>>(param, m, v, v_max, grad, a, n);
+    NCC_COUNT_LAUNCH();
+    return launch_status("adam");
+}
+
+void nc_cuda_sgd_step_f32(float* param, const float* grad, float lr, size_t n) {
+    nc_cuda_sgd_update_f32_ex(param, nullptr, const_cast<float*>(grad), lr, 0.0, 0.0, 0.0, 0, 0, 1.0, n, current_stream());
+}
+// Legacy entry: no first-step flag in the signature, so v = mu*v + (1-d)*g always
+// (equal to the CPU rule when the velocity starts at zero and dampening is 0).
+void nc_cuda_sgd_momentum_f32(float* param, float* velocity, const float* grad, float lr, float momentum,
+                              float dampening, int nesterov, size_t n) {
+    nc_cuda_sgd_update_f32_ex(param, velocity, const_cast<float*>(grad), lr, momentum, dampening, 0.0, nesterov, 0,
+                              1.0, n, current_stream());
+}
+
+int nc_cuda_sum_axis_f32_ex(float* out, const float* in, size_t outer, size_t reduce_dim, size_t inner, void* stream) {
+    if (outer == 0 || inner == 0) return NC_CUDA_OK;
+    NCC_REQUIRE(out && in, "sum_axis: null pointer");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (inner == 1) {
+        sum_rows_kernel<<<grid_for((long long)outer * 32, kThreads), kThreads, 0, st>>>(out, in, outer, reduce_dim);
+    } else {
+        NCC_REQUIRE(outer <= 65535, "sum_axis: outer too large");
+        dim3 grid(ceil_div((long long)inner, 32), (unsigned)outer);
+        sum_axis_kernel<<<grid, 256, 0, st>>>(out, in, reduce_dim, inner);
+    }
+    NCC_COUNT_LAUNCH();
+    return launch_status("sum_axis");
+}
+void nc_cuda_sum_axis_f32(float* out, const float* in, size_t outer, size_t reduce_dim, size_t inner) {
+    nc_cuda_sum_axis_f32_ex(out, in, outer, reduce_dim, inner, current_stream());
+}
+int nc_cuda_argmax_rows_f32_ex(int64_t* out, const float* in, size_t rows, size_t cols, void* stream) {
+    if (rows == 0) return NC_CUDA_OK;
+    NCC_REQUIRE(out && in && cols > 0, "argmax_rows: bad argument");
+    argmax_rows_kernel<<<grid_for((long long)rows * 32, kThreads), kThreads, 0, (cudaStream_t)stream>>>(out, in, rows, cols);
+    NCC_COUNT_LAUNCH();
+    return launch_status("argmax_rows");
+}
+float nc_cuda_sum_f32(const float* data, size_t n) {
+    cudaStream_t st = current_stream();
+    float* d = (float*)scratch(1, 16, st);
+    if (!d) return 0.f;
+    if (nc_cuda_sum_axis_f32_ex(d, data, 1, n, 1, st)) return 0.f;
+    float h = 0.f;
+    cudaMemcpyAsync(&h, d, sizeof(float), cudaMemcpyDeviceToHost, st);
+    cudaStreamSynchronize(st);
+    return h;
+}
+size_t nc_cuda_argmax_f32(const float* data, size_t n) {
+    cudaStream_t st = current_stream();
+    int64_t* d = (int64_t*)scratch(1, 16, st);
+    if (!d) return 0;
+    if (nc_cuda_argmax_rows_f32_ex(d, data, 1, n, st)) return 0;
+    int64_t h = 0;
+    cudaMemcpyAsync(&h, d, sizeof(h), cudaMemcpyDeviceToHost, st);
+    cudaStreamSynchronize(st);
+    return (size_t)h;
+}
+
+}  // extern "C"

@@ -1,0 +1,113 @@
+// Shared helpers for the sm_100a kernel library behind the nc_cuda_* C ABI.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda.h>
+#include <stdint.h>
+#include <stddef.h>
+#include <stdio.h>
+
+// Status codes returned by every *_ex entry point (0 = success).
+enum {
+    NC_CUDA_OK = 0,
+    NC_CUDA_ERR_ARG = 1,        // bad pointer / size / unsupported shape
+    NC_CUDA_ERR_RUNTIME = 2,    // a CUDA runtime call or launch failed
+    NC_CUDA_ERR_UNSUPPORTED = 3,// shape not covered by this kernel family
+    NC_CUDA_ERR_DEVICE_WAIT = 4,// a bounded in-kernel wait gave up (see nc_cuda_device_error_word)
+    NC_CUDA_ERR_LIMIT = 5       // request exceeds a stated fixed capacity
+};
+
+namespace ncc {
+
+// Last status + message seen by this process (single host thread drives one device).
+int  set_status(int code, const char* fmt, ...);
+int  last_status();
+const char* last_message();
+
+// The stream the legacy void entry points launch on (default: the legacy default stream).
+cudaStream_t current_stream();
+
+// Device-side scratch owned by the library (grown on demand, freed at nc_cuda_cleanup).
+// `slot` separates users whose lifetimes overlap inside one entry point.
+void* scratch(int slot, size_t bytes, cudaStream_t st);
+
+// Device-resident error word the tensor-core kernels set when a bounded wait expires.
+unsigned int* device_error_word();
+
+int sm_count();
+
+// NC_CUDA_MATH_* mode selected with nc_cuda_set_math_mode.
+int math_mode();
+
+// Number of kernels launched by this library (bench bookkeeping).
+extern unsigned long long g_launches;
+#define NCC_COUNT_LAUNCH() (++ncc::g_launches)
+
+// out[c] = sum over rows of in[r][c] for a dense row-major (rows x cols) matrix; two-stage,
+// double accumulation, fixed combine order (defined in pool_norm.cu).
+int column_sums(float* out, const float* in, size_t rows, int cols, cudaStream_t st);
+
+inline int launch_status(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return set_status(NC_CUDA_ERR_RUNTIME, "%s: %s", what, cudaGetErrorString(e));
+    return NC_CUDA_OK;
+}
+
+#define NCC_TRY(expr)                                                                      \
+    do {                                                                                   \
+        cudaError_t _e = (expr);                                                           \
+        if (_e != cudaSuccess)                                                             \
+            return ncc::set_status(NC_CUDA_ERR_RUNTIME, "%s: %s", #expr, cudaGetErrorString(_e)); \
+    } while (0)
+
+#define NCC_REQUIRE(cond, ...)                                                             \
+    do {                                                                                   \
+        if (!(cond)) return ncc::set_status(NC_CUDA_ERR_ARG, __VA_ARGS__);                 \
+    } while (0)
+
+static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// Grid size for grid-stride kernels: a multiple of the SM count, capped by the work.
+inline int grid_for(long long work_items, int threads, int ctas_per_sm = 8) {
+    long long need = (work_items + threads - 1) / threads;
+    long long cap = (long long)sm_count() * ctas_per_sm;
+    if (need < 1) need = 1;
+    return (int)(need < cap ? need : cap);
+}
+
+// ---------------- device helpers ----------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum of a double; result valid in every thread. `sh` must hold 32 doubles.
+__device__ __forceinline__ double block_sum(double v, double* sh) {
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) sh[w] = v;
+    __syncthreads();
+    double r = (lane < nw) ? sh[lane] : 0.0;
+    r = warp_sum(r);
+    return r;
+}
+
+// Round an f32 to the nearest TF32 value (ties away), keeping it in an f32 container.
+__device__ __forceinline__ float round_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+}  // namespace ncc

@@ -1,0 +1,698 @@
+// MaxPool2d (forward with saved argmax, backward scatter), BatchNorm2d and LayerNorm forward/backward.
+// Every reduction is two-stage and ordered (no float atomics): partial sums per CTA in double, then a
+// fixed-order combine, so results are bit-stable from run to run.
+// Semantics follow the reference CPU path: src/nn/conv.c:672-849 (max pool: start -1e30, strict >,
+// first maximum wins), src/nn/batchnorm.c:43-165,171-371 (BatchNorm2d) and :600-702,946-1026 (LayerNorm).
+#include "nc_common.cuh"
+#include "../../include/nocta_cuda.h"
+
+using namespace ncc;
+
+namespace {
+
+constexpr int kThreads = 256;
+
+// =============================================================================================
+// Max pooling
+// =============================================================================================
+// NCHW: one thread per output element.  NHWC: one thread per output pixel x 4-channel vector when
+// C % 4 == 0 (VEC = 4), else per single channel.
+template <int LAYOUT, int VEC>
+__global__ void __launch_bounds__(kThreads) maxpool_fwd_kernel(float* __restrict__ out, uint8_t* __restrict__ idx,
+                                                               const float* __restrict__ in, int N, int C, int H,
+                                                               int W, int Ho, int Wo, int k, int stride) {
+    const size_t total = (size_t)N * (C / VEC) * Ho * Wo;
+    const size_t gstride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gstride) {
+        size_t r = i;
+        int n, c, ho, wo;
+        if (LAYOUT == 0) {
+            wo = r % Wo; r /= Wo; ho = r % Ho; r /= Ho; c = r % C; n = (int)(r / C);
+        } else {
+            c = (int)(r % (C / VEC)) * VEC; r /= (C / VEC); wo = r % Wo; r /= Wo; ho = r % Ho; n = (int)(r / Ho);
+        }
+        float best[VEC];
+        int bidx[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; v++) { best[v] = -1e30f; bidx[v] = 0; }
+        for (int kh = 0; kh < k; kh++) {
+            for (int kw = 0; kw < k; kw++) {
+                const int h = ho * stride + kh, w = wo * stride + kw;
+                float val[VEC];
+                if (LAYOUT == 0) {
+                    val[0] = in[(((size_t)n * C + c) * H + h) * W + w];
+                } else if (VEC == 4) {
+                    float4 t = *reinterpret_cast<const float4*>(in + (((size_t)n * H + h) * W + w) * C + c);
+                    val[0] = t.x; val[1 % VEC] = t.y; val[2 % VEC] = t.z; val[3 % VEC] = t.w;
+                } else {
+                    val[0] = in[(((size_t)n * H + h) * W + w) * C + c];
+                }
+#pragma unroll
+                for (int v = 0; v < VEC; v++)
+                    if (val[v] > best[v]) { best[v] = val[v]; bidx[v] = kh * k + kw; }
+            }
+        }
+        size_t o;
+        if (LAYOUT == 0) o = (((size_t)n * C + c) * Ho + ho) * Wo + wo;
+        else o = (((size_t)n * Ho + ho) * Wo + wo) * C + c;
+        if (VEC == 4) {
+            *reinterpret_cast<float4*>(out + o) = make_float4(best[0], best[1 % VEC], best[2 % VEC], best[3 % VEC]);
+            if (idx) *reinterpret_cast<uchar4*>(idx + o) =
+                make_uchar4((uint8_t)bidx[0], (uint8_t)bidx[1 % VEC], (uint8_t)bidx[2 % VEC], (uint8_t)bidx[3 % VEC]);
+        } else {
+            out[o] = best[0];
+            if (idx) idx[o] = (uint8_t)bidx[0];
+        }
+    }
+}
+
+// Non-overlapping windows (stride >= k): every input pixel is owned by at most one output, so the
+// thread of that output writes the whole window (gradient at the saved offset, zero elsewhere).
+template <int LAYOUT, int VEC>
+__global__ void __launch_bounds__(kThreads) maxpool_bwd_own_kernel(float* __restrict__ gin, const float* __restrict__ gout,
+                                                                   const uint8_t* __restrict__ idx, int N, int C, int H,
+                                                                   int W, int Ho, int Wo, int k, int stride) {
+    const size_t total = (size_t)N * (C / VEC) * Ho * Wo;
+    const size_t gstride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gstride) {
+        size_t r = i;
+        int n, c, ho, wo;
+        if (LAYOUT == 0) {
+            wo = r % Wo; r /= Wo; ho = r % Ho; r /= Ho; c = r % C; n = (int)(r / C);
+        } else {
+            c = (int)(r % (C / VEC)) * VEC; r /= (C / VEC); wo = r % Wo; r /= Wo; ho = r % Ho; n = (int)(r / Ho);
+        }
+        size_t o;
+        if (LAYOUT == 0) o = (((size_t)n * C + c) * Ho + ho) * Wo + wo;
+        else o = (((size_t)n * Ho + ho) * Wo + wo) * C + c;
+        float g[VEC];
+        int bi[VEC];
+        if (VEC == 4) {
+            float4 t = *reinterpret_cast<const float4*>(gout + o);
+            uchar4 u = *reinterpret_cast<const uchar4*>(idx + o);
+            g[0] = t.x; g[1 % VEC] = t.y; g[2 % VEC] = t.z; g[3 % VEC] = t.w;
+            bi[0] = u.x; bi[1 % VEC] = u.y; bi[2 % VEC] = u.z; bi[3 % VEC] = u.w;
+        } else {
+            g[0] = gout[o];
+            bi[0] = idx[o];
+        }
+        for (int kh = 0; kh < k; kh++) {
+            for (int kw = 0; kw < k; kw++) {
+                const int h = ho * stride + kh, w = wo * stride + kw, off = kh * k + kw;
+                if (LAYOUT == 0) {
+                    gin[(((size_t)n * C + c) * H + h) * W + w] = (bi[0] == off) ? g[0] : 0.f;
+                } else if (VEC == 4) {
+                    float4 t = make_float4(bi[0] == off ? g[0] : 0.f, bi[1 % VEC] == off ? g[1 % VEC] : 0.f,
+                                           bi[2 % VEC] == off ? g[2 % VEC] : 0.f, bi[3 % VEC] == off ? g[3 % VEC] : 0.f);
+                    *reinterpret_cast<float4*>(gin + (((size_t)n * H + h) * W + w) * C + c) = t;
+                } else {
+                    gin[(((size_t)n * H + h) * W + w) * C + c] = (bi[0] == off) ? g[0] : 0.f;
+                }
+            }
+        }
+    }
+}
+
+// Overlapping windows (stride < k): gather form — each input pixel sums the outputs whose saved
+// offset points at it (fixed (ho, wo) order, no atomics).
+template <int LAYOUT>
+__global__ void __launch_bounds__(kThreads) maxpool_bwd_gather_kernel(float* __restrict__ gin, const float* __restrict__ gout,
+                                                                      const uint8_t* __restrict__ idx, int N, int C, int H,
+                                                                      int W, int Ho, int Wo, int k, int stride) {
+    const size_t total = (size_t)N * C * H * W;
+    const size_t gstride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gstride) {
+        size_t r = i;
+        int n, c, h, w;
+        if (LAYOUT == 0) { w = r % W; r /= W; h = r % H; r /= H; c = r % C; n = (int)(r / C); }
+        else { c = r % C; r /= C; w = r % W; r /= W; h = r % H; n = (int)(r / H); }
+        float acc = 0.f;
+        for (int kh = 0; kh < k; kh++) {
+            int hh = h - kh;
+            if (hh < 0 || hh % stride) continue;
+            int ho = hh / stride;
+            if (ho >= Ho) continue;
+            for (int kw = 0; kw < k; kw++) {
+                int ww = w - kw;
+                if (ww < 0 || ww % stride) continue;
+                int wo = ww / stride;
+                if (wo >= Wo) continue;
+                size_t o = LAYOUT == 0 ? (((size_t)n * C + c) * Ho + ho) * Wo + wo
+                                       : (((size_t)n * Ho + ho) * Wo + wo) * C + c;
+                if (idx[o] == kh * k + kw) acc += gout[o];
+            }
+        }
+        gin[i] = acc;
+    }
+}
+
+template <int LAYOUT>
+int maxpool_fwd(float* out, uint8_t* idx, const float* in, int N, int C, int H, int W, int k, int s, cudaStream_t st) {
+    const int Ho = (H - k) / s + 1, Wo = (W - k) / s + 1;
+    const bool vec = LAYOUT == 1 && (C % 4 == 0) && ((uintptr_t)out % 16 == 0) && ((uintptr_t)in % 16 == 0) &&
+                     (!idx || (uintptr_t)idx % 4 == 0);
+    const size_t total = (size_t)N * C * Ho * Wo / (vec ? 4 : 1);
+    if (total == 0) return NC_CUDA_OK;
+    int grid = grid_for((long long)total, kThreads);
+    if (vec) maxpool_fwd_kernel<1, 4><<<grid, kThreads, 0, st>>>(out, idx, in, N, C, H, W, Ho, Wo, k, s);
+    else maxpool_fwd_kernel<LAYOUT, 1><<<grid, kThreads, 0, st>>>(out, idx, in, N, C, H, W, Ho, Wo, k, s);
+    NCC_COUNT_LAUNCH();
+    return launch_status("maxpool_forward");
+}
+
+template <int LAYOUT>
+int maxpool_bwd(float* gin, const float* gout, const uint8_t* idx, int N, int C, int H, int W, int k, int s,
+                cudaStream_t st) {
+    const int Ho = (H - k) / s + 1, Wo = (W - k) / s + 1;
+    if ((size_t)N * C * H * W == 0) return NC_CUDA_OK;
+    if (s < k) {
+        maxpool_bwd_gather_kernel<LAYOUT><<<grid_for((long long)N * C * H * W, kThreads), kThreads, 0, st>>>(
+            gin, gout, idx, N, C, H, W, Ho, Wo, k, s);
+        NCC_COUNT_LAUNCH();
+        return launch_status("maxpool_backward(gather)");
+    }
+    const bool covers = (s == k) && (Ho * s == H) && (Wo * s == W);
+    if (!covers) NCC_TRY(cudaMemsetAsync(gin, 0, sizeof(float) * (size_t)N * C * H * W, st));
+    const bool vec = LAYOUT == 1 && (C % 4 == 0) && ((uintptr_t)gin % 16 == 0) && ((uintptr_t)gout % 16 == 0) &&
+                     ((uintptr_t)idx % 4 == 0);
+    const size_t total = (size_t)N * C * Ho * Wo / (vec ? 4 : 1);
+    if (total == 0) return NC_CUDA_OK;
+    int grid = grid_for((long long)total, kThreads);
+    if (vec) maxpool_bwd_own_kernel<1, 4><<<grid, kThreads, 0, st>>>(gin, gout, idx, N, C, H, W, Ho, Wo, k, s);
+    else maxpool_bwd_own_kernel<LAYOUT, 1><<<grid, kThreads, 0, st>>>(gin, gout, idx, N, C, H, W, Ho, Wo, k, s);
+    NCC_COUNT_LAUNCH();
+    return launch_status("maxpool_backward");
+}
+
+// =============================================================================================
+// Per-channel / per-column two-value reductions (stage 1), shared by BatchNorm and LayerNorm.
+// A functor maps an element to the two summands; partial[slab][col][2] (double) is the output.
+// =============================================================================================
+
+// Column reduce over a row-major (rows x cols) matrix: NHWC BatchNorm (cols = C) and LayerNorm
+// dgamma/dbeta.  Block = 32 column lanes x 8 row lanes; grid.x = column tiles, grid.y = row slabs.
+template <class F>
+__global__ void __launch_bounds__(256) colreduce_kernel(double* __restrict__ partial, size_t rows, int cols,
+                                                        size_t rows_per_slab, F f) {
+    __shared__ double sh[2][8][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + tx;
+    const size_t r0 = (size_t)blockIdx.y * rows_per_slab;
+    size_t r1 = r0 + rows_per_slab;
+    if (r1 > rows) r1 = rows;
+    double a = 0.0, b = 0.0;
+    if (c < cols) {
+        for (size_t r = r0 + ty; r < r1; r += 8) {
+            float v1, v2;
+            f(r, c, v1, v2);
+            a += (double)v1;
+            b += (double)v2;
+        }
+    }
+    sh[0][ty][tx] = a;
+    sh[1][ty][tx] = b;
+    __syncthreads();
+    if (ty == 0 && c < cols) {
+        double s1 = 0.0, s2 = 0.0;
+#pragma unroll
+        for (int k = 0; k < 8; k++) { s1 += sh[0][k][tx]; s2 += sh[1][k][tx]; }
+        double* p = partial + ((size_t)blockIdx.y * cols + c) * 2;
+        p[0] = s1;
+        p[1] = s2;
+    }
+}
+
+// NCHW channel reduce: block (c, j) walks images n = j, j+J, ... of channel c, each a contiguous run
+// of `spatial` floats.
+template <class F>
+__global__ void __launch_bounds__(256) chanreduce_nchw_kernel(double* __restrict__ partial, int N, int C, int spatial, F f) {
+    __shared__ double sh[32];
+    const int c = blockIdx.x, j = blockIdx.y, J = gridDim.y;
+    double a = 0.0, b = 0.0;
+    for (int n = j; n < N; n += J) {
+        const size_t base = ((size_t)n * C + c) * spatial;
+        for (int s = threadIdx.x; s < spatial; s += blockDim.x) {
+            float v1, v2;
+            f(base + s, c, v1, v2);
+            a += (double)v1;
+            b += (double)v2;
+        }
+    }
+    a = block_sum(a, sh);
+    b = block_sum(b, sh);
+    if (threadIdx.x == 0) {
+        double* p = partial + ((size_t)j * C + c) * 2;
+        p[0] = a;
+        p[1] = b;
+    }
+}
+
+struct BnFwdSum {  // (x, x^2)
+    const float* x; int cols;
+    __device__ void operator()(size_t r, int c, float& v1, float& v2) const {
+        float t = x[r * cols + c]; v1 = t; v2 = t * t;
+    }
+};
+struct BnFwdSumFlat {  // NCHW flavour: flat index supplied
+    const float* x;
+    __device__ void operator()(size_t i, int, float& v1, float& v2) const { float t = x[i]; v1 = t; v2 = t * t; }
+};
+// (dy, dy * xhat) with optional ReLU mask taken from the forward output
+struct BnBwdSum {
+    const float* dy; const float* x; const float* y; const float* mean; const float* var; float eps; int cols;
+    __device__ void operator()(size_t r, int c, float& v1, float& v2) const {
+        size_t i = r * cols + c;
+        float g = dy[i];
+        if (y && !(y[i] > 0.f)) g = 0.f;
+        float xh = (x[i] - mean[c]) * rsqrtf(var[c] + eps);
+        v1 = g; v2 = g * xh;
+    }
+};
+struct BnBwdSumFlat {
+    const float* dy; const float* x; const float* y; const float* mean; const float* var; float eps;
+    __device__ void operator()(size_t i, int c, float& v1, float& v2) const {
+        float g = dy[i];
+        if (y && !(y[i] > 0.f)) g = 0.f;
+        float xh = (x[i] - mean[c]) * rsqrtf(var[c] + eps);
+        v1 = g; v2 = g * xh;
+    }
+};
+// LayerNorm dgamma/dbeta: (g * xhat, g) with per-row statistics
+struct LnParamSum {
+    const float* g; const float* x; const float2* stats; int cols;
+    __device__ void operator()(size_t r, int c, float& v1, float& v2) const {
+        size_t i = r * cols + c;
+        float2 s = stats[r];
+        float gv = g[i];
+        v1 = gv * ((x[i] - s.x) * s.y); v2 = gv;
+    }
+};
+
+// Stage 2 for BatchNorm forward: combine slabs in order, derive mean / biased variance, update the
+// running statistics (unbiased variance, src/nn/batchnorm.c:307-314).
+__global__ void bn_fwd_finalize_kernel(const double* __restrict__ partial, int slabs, int C, double M,
+                                       float* __restrict__ save_mean, float* __restrict__ save_var,
+                                       float* __restrict__ run_mean, float* __restrict__ run_var, double momentum) {
+    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    double s1 = 0.0, s2 = 0.0;
+    for (int s = 0; s < slabs; s++) {
+        s1 += partial[((size_t)s * C + c) * 2];
+        s2 += partial[((size_t)s * C + c) * 2 + 1];
+    }
+    double mean = s1 / M;
+    double var_sum = s2 - s1 * mean;  // sum (x - mean)^2
+    if (var_sum < 0.0) var_sum = 0.0;
+    double var = var_sum / M;
+    save_mean[c] = (float)mean;
+    save_var[c] = (float)var;
+    if (run_mean && run_var) {
+        double unbiased = (M > 1.0) ? var_sum / (M - 1.0) : var;
+        run_mean[c] = (float)((1.0 - momentum) * (double)run_mean[c] + momentum * mean);
+        run_var[c] = (float)((1.0 - momentum) * (double)run_var[c] + momentum * unbiased);
+    }
+}
+
+// eval mode: statistics come from the running buffers (or 0 / 1 when absent)
+__global__ void bn_eval_stats_kernel(int C, float* __restrict__ save_mean, float* __restrict__ save_var,
+                                     const float* __restrict__ run_mean, const float* __restrict__ run_var) {
+    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    save_mean[c] = run_mean ? run_mean[c] : 0.f;
+    save_var[c] = run_var ? run_var[c] : 1.f;
+}
+
+// y = gamma * (x - mean) * inv_std + beta (optionally ReLU).  Flat, float4 when 4 neighbours share
+// a channel (NCHW, spatial % 4 == 0) or are 4 consecutive channels (NHWC, C % 4 == 0).
+template <int LAYOUT, int VEC>
+__global__ void __launch_bounds__(kThreads) bn_apply_kernel(float* __restrict__ y, const float* __restrict__ x,
+                                                            const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                            const float* __restrict__ mean, const float* __restrict__ var,
+                                                            float eps, int C, int spatial, size_t nvec, int relu) {
+    const size_t gstride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += gstride) {
+        const size_t e = i * VEC;
+        float xv[VEC], out[VEC];
+        if (VEC == 4) {
+            float4 t = *reinterpret_cast<const float4*>(x + e);
+            xv[0] = t.x; xv[1 % VEC] = t.y; xv[2 % VEC] = t.z; xv[3 % VEC] = t.w;
+        } else xv[0] = x[e];
+#pragma unroll
+        for (int v = 0; v < VEC; v++) {
+            int c = LAYOUT == 0 ? (int)((e / spatial) % C) : (int)((e + v) % C);
+            float is = rsqrtf(var[c] + eps);
+            float g = gamma ? gamma[c] : 1.f, b = beta ? beta[c] : 0.f;
+            float o = g * ((xv[v] - mean[c]) * is) + b;
+            out[v] = (relu && !(o > 0.f)) ? 0.f : o;
+        }
+        if (VEC == 4) *reinterpret_cast<float4*>(y + e) = make_float4(out[0], out[1 % VEC], out[2 % VEC], out[3 % VEC]);
+        else y[e] = out[0];
+    }
+}
+
+__global__ void bn_bwd_finalize_kernel(const double* __restrict__ partial, int slabs, int C,
+                                       float* __restrict__ dgamma, float* __restrict__ dbeta, float* __restrict__ sums) {
+    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    double s1 = 0.0, s2 = 0.0;
+    for (int s = 0; s < slabs; s++) {
+        s1 += partial[((size_t)s * C + c) * 2];
+        s2 += partial[((size_t)s * C + c) * 2 + 1];
+    }
+    if (dbeta) dbeta[c] = (float)s1;
+    if (dgamma) dgamma[c] = (float)s2;
+    sums[2 * c] = (float)s1;
+    sums[2 * c + 1] = (float)s2;
+}
+
+// dx = gamma * inv_std / M * (M * g - sum_g - xhat * sum_gx)   (src/nn/batchnorm.c:145-158)
+template <int LAYOUT, int VEC>
+__global__ void __launch_bounds__(kThreads) bn_bwd_apply_kernel(float* __restrict__ dx, const float* __restrict__ dy,
+                                                                const float* __restrict__ x, const float* __restrict__ yrelu,
+                                                                const float* __restrict__ gamma, const float* __restrict__ mean,
+                                                                const float* __restrict__ var, const float* __restrict__ sums,
+                                                                float eps, float Mf, int C, int spatial, size_t nvec) {
+    const size_t gstride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += gstride) {
+        const size_t e = i * VEC;
+        float xv[VEC], gv[VEC], yv[VEC], out[VEC];
+        if (VEC == 4) {
+            float4 t = *reinterpret_cast<const float4*>(x + e);
+            float4 u = *reinterpret_cast<const float4*>(dy + e);
+            xv[0] = t.x; xv[1 % VEC] = t.y; xv[2 % VEC] = t.z; xv[3 % VEC] = t.w;
+            gv[0] = u.x; gv[1 % VEC] = u.y; gv[2 % VEC] = u.z; gv[3 % VEC] = u.w;
+            if (yrelu) {
+                float4 w = *reinterpret_cast<const float4*>(yrelu + e);
+                yv[0] = w.x; yv[1 % VEC] = w.y; yv[2 % VEC] = w.z; yv[3 % VEC] = w.w;
+            }
+        } else {
+            xv[0] = x[e]; gv[0] = dy[e];
+            if (yrelu) yv[0] = yrelu[e];
+        }
+#pragma unroll
+        for (int v = 0; v < VEC; v++) {
+            int c = LAYOUT == 0 ? (int)((e / spatial) % C) : (int)((e + v) % C);
+            float is = rsqrtf(var[c] + eps);
+            float g = gv[v];
+            if (yrelu && !(yv[v] > 0.f)) g = 0.f;
+            float xh = (xv[v] - mean[c]) * is;
+            float coeff = (gamma ? gamma[c] : 1.f) * is / Mf;
+            out[v] = coeff * (Mf * g - sums[2 * c] - xh * sums[2 * c + 1]);
+        }
+        if (VEC == 4) *reinterpret_cast<float4*>(dx + e) = make_float4(out[0], out[1 % VEC], out[2 % VEC], out[3 % VEC]);
+        else dx[e] = out[0];
+    }
+}
+
+// Launch stage 1 for a (N, C, spatial) tensor in either layout; returns the slab count.
+template <class FR, class FF>
+int channel_reduce(double** partial_out, int* slabs_out, int N, int C, int spatial, int layout, FR frows, FF fflat,
+                   cudaStream_t st) {
+    if (layout == 1) {
+        const size_t rows = (size_t)N * spatial;
+        int col_tiles = ceil_div(C, 32);
+        int want = (sm_count() * 4 + col_tiles - 1) / col_tiles;
+        size_t rps = (rows + want - 1) / want;
+        if (rps < 64) rps = 64;
+        int slabs = (int)((rows + rps - 1) / rps);
+        if (slabs > 65535) { slabs = 65535; rps = (rows + slabs - 1) / slabs; slabs = (int)((rows + rps - 1) / rps); }
+        double* partial = (double*)scratch(7, sizeof(double) * 2 * (size_t)slabs * C, st);
+        if (!partial) return NC_CUDA_ERR_RUNTIME;
+        colreduce_kernel<<<dim3(col_tiles, slabs), 256, 0, st>>>(partial, rows, C, rps, frows);
+        NCC_COUNT_LAUNCH();
+        *partial_out = partial;
+        *slabs_out = slabs;
+    } else {
+        int J = (sm_count() * 4 + C - 1) / C;
+        if (J > N) J = N;
+        if (J < 1) J = 1;
+        if (J > 65535) J = 65535;
+        double* partial = (double*)scratch(7, sizeof(double) * 2 * (size_t)J * C, st);
+        if (!partial) return NC_CUDA_ERR_RUNTIME;
+        chanreduce_nchw_kernel<<<dim3(C, J), 256, 0, st>>>(partial, N, C, spatial, fflat);
+        NCC_COUNT_LAUNCH();
+        *partial_out = partial;
+        *slabs_out = J;
+    }
+    return launch_status("channel_reduce");
+}
+
+// =============================================================================================
+// LayerNorm: one warp per row.
+// =============================================================================================
+__global__ void __launch_bounds__(kThreads) ln_fwd_kernel(float* __restrict__ y, const float* __restrict__ x,
+                                                          const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                          size_t rows, int cols, float eps) {
+    const int lane = threadIdx.x & 31;
+    const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    for (size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+        const float* xr = x + r * cols;
+        float* yr = y + r * cols;
+        double s = 0.0;
+        for (int c = lane; c < cols; c += 32) s += (double)xr[c];
+        s = warp_sum(s);
+        const float mean = (float)(s / cols);
+        double q = 0.0;
+        for (int c = lane; c < cols; c += 32) { float d = xr[c] - mean; q += (double)d * d; }
+        q = warp_sum(q);
+        const float inv = (float)(1.0 / sqrt(q / cols + (double)eps));
+        for (int c = lane; c < cols; c += 32) {
+            float g = gamma ? gamma[c] : 1.f, b = beta ? beta[c] : 0.f;
+            yr[c] = g * ((xr[c] - mean) * inv) + b;
+        }
+    }
+}
+
+// dx and per-row (mean, inv_std) for the parameter-gradient pass.
+__global__ void __launch_bounds__(kThreads) ln_bwd_rows_kernel(float* __restrict__ dx, float2* __restrict__ stats,
+                                                               const float* __restrict__ dy, const float* __restrict__ x,
+                                                               const float* __restrict__ gamma, size_t rows, int cols,
+                                                               float eps) {
+    const int lane = threadIdx.x & 31;
+    const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    for (size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+        const float* xr = x + r * cols;
+        const float* gr = dy + r * cols;
+        double s = 0.0;
+        for (int c = lane; c < cols; c += 32) s += (double)xr[c];
+        s = warp_sum(s);
+        const float mean = (float)(s / cols);
+        double q = 0.0;
+        for (int c = lane; c < cols; c += 32) { float d = xr[c] - mean; q += (double)d * d; }
+        q = warp_sum(q);
+        const float inv = (float)(1.0 / sqrt(q / cols + (double)eps));
+        double sg = 0.0, sgx = 0.0;
+        for (int c = lane; c < cols; c += 32) {
+            float gg = gr[c] * (gamma ? gamma[c] : 1.f);
+            float xh = (xr[c] - mean) * inv;
+            sg += (double)gg;
+            sgx += (double)gg * (double)xh;
+        }
+        sg = warp_sum(sg);
+        sgx = warp_sum(sgx);
+        const float fsg = (float)sg, fsgx = (float)sgx, D = (float)cols, coeff = inv / D;
+        for (int c = lane; c < cols; c += 32) {
+            float gg = gr[c] * (gamma ? gamma[c] : 1.f);
+            float xh = (xr[c] - mean) * inv;
+            dx[r * cols + c] = coeff * (D * gg - fsg - xh * fsgx);
+        }
+        if (lane == 0 && stats) stats[r] = make_float2(mean, inv);
+    }
+}
+
+__global__ void ln_param_finalize_kernel(const double* __restrict__ partial, int slabs, int cols,
+                                         float* __restrict__ dgamma, float* __restrict__ dbeta) {
+    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    double s1 = 0.0, s2 = 0.0;
+    for (int s = 0; s < slabs; s++) {
+        s1 += partial[((size_t)s * cols + c) * 2];
+        s2 += partial[((size_t)s * cols + c) * 2 + 1];
+    }
+    if (dgamma) dgamma[c] = (float)s1;
+    if (dbeta) dbeta[c] = (float)s2;
+}
+
+struct ColSum {  // (x, 0)
+    const float* x; int cols;
+    __device__ void operator()(size_t r, int c, float& v1, float& v2) const { v1 = x[r * cols + c]; v2 = 0.f; }
+};
+
+}  // namespace
+
+int ncc::column_sums(float* out, const float* in, size_t rows, int cols, cudaStream_t st) {
+    if (cols <= 0) return NC_CUDA_OK;
+    NCC_REQUIRE(out && (in || rows == 0), "column_sums: null pointer");
+    if (rows == 0) { NCC_TRY(cudaMemsetAsync(out, 0, sizeof(float) * cols, st)); return NC_CUDA_OK; }
+    int col_tiles = ceil_div(cols, 32);
+    int want = (sm_count() * 4 + col_tiles - 1) / col_tiles;
+    size_t rps = (rows + want - 1) / want;
+    if (rps < 64) rps = 64;
+    int slabs = (int)((rows + rps - 1) / rps);
+    if (slabs > 65535) { slabs = 65535; rps = (rows + slabs - 1) / slabs; slabs = (int)((rows + rps - 1) / rps); }
+    double* partial = (double*)scratch(7, sizeof(double) * 2 * (size_t)slabs * cols, st);
+    if (!partial) return NC_CUDA_ERR_RUNTIME;
+    colreduce_kernel<<<dim3(col_tiles, slabs), 256, 0, st>>>(partial, rows, cols, rps, ColSum{in, cols});
+    NCC_COUNT_LAUNCH();
+    ln_param_finalize_kernel<<<ceil_div(cols, 128), 128, 0, st>>>(partial, slabs, cols, out, nullptr);
+    NCC_COUNT_LAUNCH();
+    return launch_status("column_sums");
+}
+
+extern "C" {
+
+int nc_cuda_maxpool2d_forward_idx_f32_ex(float* out, uint8_t* argmax, const float* in, int N, int C, int H, int W,
+                                         int k, int stride, int layout, void* stream) {
+    NCC_REQUIRE(out && in && N >= 0 && C > 0 && k > 0 && stride > 0 && H >= k && W >= k && k * k <= 255,
+                "maxpool_forward: bad argument");
+    if (layout == 0) return maxpool_fwd<0>(out, argmax, in, N, C, H, W, k, stride, (cudaStream_t)stream);
+    return maxpool_fwd<1>(out, argmax, in, N, C, H, W, k, stride, (cudaStream_t)stream);
+}
+int nc_cuda_maxpool2d_backward_idx_f32_ex(float* gin, const float* gout, const uint8_t* argmax, int N, int C, int H,
+                                          int W, int k, int stride, int layout, void* stream) {
+    NCC_REQUIRE(gin && gout && argmax && C > 0 && k > 0 && stride > 0 && H >= k && W >= k,
+                "maxpool_backward: bad argument");
+    if (layout == 0) return maxpool_bwd<0>(gin, gout, argmax, N, C, H, W, k, stride, (cudaStream_t)stream);
+    return maxpool_bwd<1>(gin, gout, argmax, N, C, H, W, k, stride, (cudaStream_t)stream);
+}
+void nc_cuda_maxpool2d_forward_f32(float* out, const float* in, int N, int C, int H, int W, int kH, int kW, int stride) {
+    if (kH != kW) { set_status(NC_CUDA_ERR_UNSUPPORTED, "maxpool: only square windows"); return; }
+    nc_cuda_maxpool2d_forward_idx_f32_ex(out, nullptr, in, N, C, H, W, kH, stride, 0, current_stream());
+}
+// The legacy backward has no saved argmax: recompute it from the saved input (as the CPU path does).
+void nc_cuda_maxpool2d_backward_f32(float* gin, const float* gout, const float* input, const float* output, int N,
+                                    int C, int H, int W, int kH, int kW, int stride) {
+    (void)output;
+    if (kH != kW) { set_status(NC_CUDA_ERR_UNSUPPORTED, "maxpool: only square windows"); return; }
+    cudaStream_t st = current_stream();
+    const int Ho = (H - kH) / stride + 1, Wo = (W - kW) / stride + 1;
+    const size_t no = (size_t)N * C * Ho * Wo;
+    char* buf = (char*)scratch(4, no * sizeof(float) + no + 64, st);
+    if (!buf) return;
+    float* tmp = (float*)buf;
+    uint8_t* idx = (uint8_t*)(buf + no * sizeof(float));
+    if (nc_cuda_maxpool2d_forward_idx_f32_ex(tmp, idx, input, N, C, H, W, kH, stride, 0, st)) return;
+    nc_cuda_maxpool2d_backward_idx_f32_ex(gin, gout, idx, N, C, H, W, kH, stride, 0, st);
+}
+
+int nc_cuda_batchnorm_forward_f32_ex(float* y, const float* x, const float* gamma, const float* beta, float* run_mean,
+                                     float* run_var, float* save_mean, float* save_var, int N, int C, int spatial,
+                                     double momentum, double eps, int training, int layout, int relu, void* stream) {
+    NCC_REQUIRE(y && x && save_mean && save_var && N > 0 && C > 0 && spatial > 0, "batchnorm_forward: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t total = (size_t)N * C * spatial;
+    if (training) {
+        double* partial = nullptr;
+        int slabs = 0;
+        int rc = channel_reduce(&partial, &slabs, N, C, spatial, layout, BnFwdSum{x, C}, BnFwdSumFlat{x}, st);
+        if (rc) return rc;
+        bn_fwd_finalize_kernel<<<ceil_div(C, 128), 128, 0, st>>>(partial, slabs, C, (double)N * spatial, save_mean,
+                                                                save_var, run_mean, run_var, momentum);
+    } else {
+        bn_eval_stats_kernel<<<ceil_div(C, 128), 128, 0, st>>>(C, save_mean, save_var, run_mean, run_var);
+    }
+    NCC_COUNT_LAUNCH();
+    const bool al = ((uintptr_t)y % 16 == 0) && ((uintptr_t)x % 16 == 0);
+    const bool vec = al && (layout == 0 ? spatial % 4 == 0 : C % 4 == 0);
+    const size_t nvec = vec ? total / 4 : total;
+    const int grid = grid_for((long long)nvec, kThreads);
+    const float fe = (float)eps;
+    if (layout == 0) {
+        if (vec) bn_apply_kernel<0, 4><<<grid, kThreads, 0, st>>>(y, x, gamma, beta, save_mean, save_var, fe, C, spatial, nvec, relu);
+        else bn_apply_kernel<0, 1><<<grid, kThreads, 0, st>>>(y, x, gamma, beta, save_mean, save_var, fe, C, spatial, nvec, relu);
+    } else {
+        if (vec) bn_apply_kernel<1, 4><<<grid, kThreads, 0, st>>>(y, x, gamma, beta, save_mean, save_var, fe, C, spatial, nvec, relu);
+        else bn_apply_kernel<1, 1><<<grid, kThreads, 0, st>>>(y, x, gamma, beta, save_mean, save_var, fe, C, spatial, nvec, relu);
+    }
+    NCC_COUNT_LAUNCH();
+    return launch_status("batchnorm_forward");
+}
+
+int nc_cuda_batchnorm_backward_f32_ex(float* dx, float* dgamma, float* dbeta, const float* dy, const float* x,
+                                      const float* gamma, const float* save_mean, const float* save_var,
+                                      const float* relu_out, int N, int C, int spatial, double eps, int layout,
+                                      void* stream) {
+    NCC_REQUIRE(dx && dy && x && save_mean && save_var && N > 0 && C > 0 && spatial > 0, "batchnorm_backward: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t total = (size_t)N * C * spatial;
+    const float fe = (float)eps;
+    double* partial = nullptr;
+    int slabs = 0;
+    int rc = channel_reduce(&partial, &slabs, N, C, spatial, layout,
+                            BnBwdSum{dy, x, relu_out, save_mean, save_var, fe, C},
+                            BnBwdSumFlat{dy, x, relu_out, save_mean, save_var, fe}, st);
+    if (rc) return rc;
+    float* sums = (float*)scratch(6, sizeof(float) * 2 * (size_t)C, st);
+    if (!sums) return NC_CUDA_ERR_RUNTIME;
+    bn_bwd_finalize_kernel<<<ceil_div(C, 128), 128, 0, st>>>(partial, slabs, C, dgamma, dbeta, sums);
+    NCC_COUNT_LAUNCH();
+    const bool al = ((uintptr_t)dx % 16 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)dy % 16 == 0) &&
+                    (!relu_out || (uintptr_t)relu_out % 16 == 0);
+    const bool vec = al && (layout == 0 ? spatial % 4 == 0 : C % 4 == 0);
+    const size_t nvec = vec ? total / 4 : total;
+    const int grid = grid_for((long long)nvec, kThreads);
+    const float Mf = (float)((double)N * spatial);
+    if (layout == 0) {
+        if (vec) bn_bwd_apply_kernel<0, 4><<<grid, kThreads, 0, st>>>(dx, dy, x, relu_out, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec);
+        else bn_bwd_apply_kernel<0, 1><<<grid, kThreads, 0, st>>>(dx, dy, x, relu_out, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec);
+    } else {
+        if (vec) bn_bwd_apply_kernel<1, 4><<<grid, kThreads, 0, st>>>(dx, dy, x, relu_out, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec);
+        else bn_bwd_apply_kernel<1, 1><<<grid, kThreads, 0, st>>>(dx, dy, x, relu_out, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec);
+    }
+    NCC_COUNT_LAUNCH();
+    return launch_status("batchnorm_backward");
+}
+
+void nc_cuda_batchnorm_forward_f32(float* y, const float* x, const float* gamma, const float* beta, float* rm, float* rv,
+                                   float* save_mean, float* save_var, int N, int C, int spatial, float momentum,
+                                   float eps, bool training) {
+    nc_cuda_batchnorm_forward_f32_ex(y, x, gamma, beta, rm, rv, save_mean, save_var, N, C, spatial, momentum, eps,
+                                     training ? 1 : 0, 0, 0, current_stream());
+}
+void nc_cuda_batchnorm_backward_f32(float* dx, float* dgamma, float* dbeta, const float* dy, const float* x,
+                                    const float* gamma, const float* save_mean, const float* save_var, int N, int C,
+                                    int spatial, float eps) {
+    nc_cuda_batchnorm_backward_f32_ex(dx, dgamma, dbeta, dy, x, gamma, save_mean, save_var, nullptr, N, C, spatial, eps,
+                                      0, current_stream());
+}
+
+int nc_cuda_layernorm_forward_f32_ex(float* y, const float* x, const float* gamma, const float* beta, size_t rows,
+                                     size_t cols, double eps, void* stream) {
+    if (rows == 0 || cols == 0) return NC_CUDA_OK;
+    NCC_REQUIRE(y && x && cols <= 0x7fffffff, "layernorm_forward: bad argument");
+    ln_fwd_kernel<<<grid_for((long long)rows * 32, kThreads), kThreads, 0, (cudaStream_t)stream>>>(y, x, gamma, beta, rows, (int)cols, (float)eps);
+    NCC_COUNT_LAUNCH();
+    return launch_status("layernorm_forward");
+}
+
+int nc_cuda_layernorm_backward_f32_ex(float* dx, float* dgamma, float* dbeta, const float* dy, const float* x,
+                                      const float* gamma, size_t rows, size_t cols, double eps, void* stream) {
+    if (rows == 0 || cols == 0) return NC_CUDA_OK;
+    NCC_REQUIRE(dx && dy && x && cols <= 0x7fffffff, "layernorm_backward: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool params = dgamma || dbeta;
+    float2* stats = nullptr;
+    if (params) {
+        stats = (float2*)scratch(6, sizeof(float2) * rows, st);
+        if (!stats) return NC_CUDA_ERR_RUNTIME;
+    }
+    ln_bwd_rows_kernel<<<grid_for((long long)rows * 32, kThreads), kThreads, 0, st>>>(dx, stats, dy, x, gamma, rows, (int)cols, (float)eps);
+    NCC_COUNT_LAUNCH();
+    if (params) {
+        int C = (int)cols;
+        int col_tiles = ceil_div(C, 32);
+        int want = (sm_count() * 4 + col_tiles - 1) / col_tiles;
+        size_t rps = (rows + want - 1) / want;
+        if (rps < 32) rps = 32;
+        int slabs = (int)((rows + rps - 1) / rps);
+        double* partial = (double*)scratch(7, sizeof(double) * 2 * (size_t)slabs * C, st);
+        if (!partial) return NC_CUDA_ERR_RUNTIME;
+        colreduce_kernel<<<dim3(col_tiles, slabs), 256, 0, st>>>(partial, rows, C, rps, LnParamSum{dy, x, stats, C});
+        NCC_COUNT_LAUNCH();
+        ln_param_finalize_kernel<<<ceil_div(C, 128), 128, 0, st>>>(partial, slabs, C, dgamma, dbeta);
+        NCC_COUNT_LAUNCH();
+    }
+    return launch_status("layernorm_backward");
+}
+
+}  // extern "C"

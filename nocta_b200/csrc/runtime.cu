@@ -1,0 +1,223 @@
+// Device/runtime part of the nc_cuda_* ABI: memory, streams, status, library scratch.
+// Replaces the reference's src/cuda/cuda_device.cu:22-136 (which prints and drops CUDA errors).
+#include "nc_common.cuh"
+#include "../../include/nocta_cuda.h"
+#include <stdarg.h>
+#include <string.h>
+
+namespace ncc {
+
+static int g_status = NC_CUDA_OK;
+static char g_message[512] = {0};
+static cudaStream_t g_stream = nullptr;
+static int g_sm_count = 0;
+static int g_math_mode = NC_CUDA_MATH_TF32;
+unsigned long long g_launches = 0;
+
+static const int kScratchSlots = 8;
+static void* g_scratch[kScratchSlots] = {nullptr};
+static size_t g_scratch_bytes[kScratchSlots] = {0};
+static unsigned int* g_err_word = nullptr;
+
+int set_status(int code, const char* fmt, ...) {
+    g_status = code;
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_message, sizeof(g_message), fmt, ap);
+    va_end(ap);
+    if (code != NC_CUDA_OK) fprintf(stderr, "[nocta-cuda] error %d: %s\n", code, g_message);
+    return code;
+}
+int last_status() { return g_status; }
+const char* last_message() { return g_message; }
+cudaStream_t current_stream() { return g_stream; }
+int math_mode() { return g_math_mode; }
+
+int sm_count() {
+    if (g_sm_count == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            g_sm_count <= 0)
+            g_sm_count = 148;
+    }
+    return g_sm_count;
+}
+
+void* scratch(int slot, size_t bytes, cudaStream_t st) {
+    if (slot < 0 || slot >= kScratchSlots) return nullptr;
+    if (bytes <= g_scratch_bytes[slot] && g_scratch[slot]) return g_scratch[slot];
+    // Growing: earlier work on any stream may still read the old block, so drain first.
+    (void)st;
+    cudaDeviceSynchronize();
+    if (g_scratch[slot]) cudaFree(g_scratch[slot]);
+    size_t want = bytes + (bytes >> 2) + 4096;
+    void* p = nullptr;
+    if (cudaMalloc(&p, want) != cudaSuccess) {
+        g_scratch[slot] = nullptr;
+        g_scratch_bytes[slot] = 0;
+        set_status(NC_CUDA_ERR_RUNTIME, "scratch slot %d: cudaMalloc(%zu) failed", slot, want);
+        return nullptr;
+    }
+    g_scratch[slot] = p;
+    g_scratch_bytes[slot] = want;
+    return p;
+}
+
+unsigned int* device_error_word() {
+    if (!g_err_word) {
+        if (cudaMalloc((void**)&g_err_word, 64) != cudaSuccess) return nullptr;
+        cudaMemset(g_err_word, 0, 64);
+    }
+    return g_err_word;
+}
+
+static void release_all() {
+    for (int i = 0; i < kScratchSlots; i++) {
+        if (g_scratch[i]) cudaFree(g_scratch[i]);
+        g_scratch[i] = nullptr;
+        g_scratch_bytes[i] = 0;
+    }
+    if (g_err_word) cudaFree(g_err_word);
+    g_err_word = nullptr;
+}
+
+}  // namespace ncc
+
+using namespace ncc;
+
+extern "C" {
+
+bool nc_cuda_available(void) {
+    int n = 0;
+    return cudaGetDeviceCount(&n) == cudaSuccess && n > 0;
+}
+int nc_cuda_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) return 0;
+    return n;
+}
+void nc_cuda_set_device(int index) {
+    if (cudaSetDevice(index) != cudaSuccess) set_status(NC_CUDA_ERR_RUNTIME, "cudaSetDevice(%d) failed", index);
+    g_sm_count = 0;
+}
+void nc_cuda_synchronize(void) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) set_status(NC_CUDA_ERR_RUNTIME, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
+}
+void nc_cuda_init(void) {
+    if (!nc_cuda_available()) {
+        set_status(NC_CUDA_ERR_RUNTIME, "no CUDA device");
+        return;
+    }
+    cudaFree(0);
+    (void)sm_count();
+    (void)device_error_word();
+}
+void nc_cuda_cleanup(void) {
+    cudaDeviceSynchronize();
+    release_all();
+}
+void* nc_cuda_malloc(size_t size) {
+    void* p = nullptr;
+    if (size == 0) size = 16;
+    cudaError_t e = cudaMalloc(&p, size);
+    if (e != cudaSuccess) {
+        set_status(NC_CUDA_ERR_RUNTIME, "cudaMalloc(%zu): %s", size, cudaGetErrorString(e));
+        return nullptr;
+    }
+    return p;
+}
+void nc_cuda_free(void* ptr) {
+    if (ptr) cudaFree(ptr);
+}
+void nc_cuda_memcpy_h2d(void* dst, const void* src, size_t size) {
+    cudaError_t e = cudaMemcpyAsync(dst, src, size, cudaMemcpyHostToDevice, g_stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(g_stream);
+    if (e != cudaSuccess) set_status(NC_CUDA_ERR_RUNTIME, "memcpy_h2d: %s", cudaGetErrorString(e));
+}
+void nc_cuda_memcpy_d2h(void* dst, const void* src, size_t size) {
+    cudaError_t e = cudaMemcpyAsync(dst, src, size, cudaMemcpyDeviceToHost, g_stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(g_stream);
+    if (e != cudaSuccess) set_status(NC_CUDA_ERR_RUNTIME, "memcpy_d2h: %s", cudaGetErrorString(e));
+}
+void nc_cuda_memcpy_d2d(void* dst, const void* src, size_t size) {
+    cudaError_t e = cudaMemcpyAsync(dst, src, size, cudaMemcpyDeviceToDevice, g_stream);
+    if (e != cudaSuccess) set_status(NC_CUDA_ERR_RUNTIME, "memcpy_d2d: %s", cudaGetErrorString(e));
+}
+void nc_cuda_memset(void* ptr, int value, size_t size) {
+    cudaError_t e = cudaMemsetAsync(ptr, value, size, g_stream);
+    if (e != cudaSuccess) set_status(NC_CUDA_ERR_RUNTIME, "memset: %s", cudaGetErrorString(e));
+}
+int nc_cuda_device_props(int index, char* name256, size_t* total_bytes, size_t* free_bytes, int* sms) {
+    cudaDeviceProp p;
+    NCC_TRY(cudaGetDeviceProperties(&p, index));
+    if (name256) {
+        strncpy(name256, p.name, 255);
+        name256[255] = 0;
+    }
+    if (sms) *sms = p.multiProcessorCount;
+    if (total_bytes) *total_bytes = p.totalGlobalMem;
+    if (free_bytes) {
+        size_t f = 0, t = 0;
+        int cur = 0;
+        cudaGetDevice(&cur);
+        if (cur == index && cudaMemGetInfo(&f, &t) == cudaSuccess) *free_bytes = f;
+        else *free_bytes = 0;
+    }
+    return NC_CUDA_OK;
+}
+void nc_cuda_set_stream(void* stream) { g_stream = (cudaStream_t)stream; }
+void* nc_cuda_get_stream(void) { return (void*)g_stream; }
+int nc_cuda_memcpy_h2d_async(void* dst, const void* src, size_t size, void* stream) {
+    NCC_TRY(cudaMemcpyAsync(dst, src, size, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    return NC_CUDA_OK;
+}
+int nc_cuda_memcpy_d2h_async(void* dst, const void* src, size_t size, void* stream) {
+    NCC_TRY(cudaMemcpyAsync(dst, src, size, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    return NC_CUDA_OK;
+}
+int nc_cuda_memset_async(void* ptr, int value, size_t size, void* stream) {
+    NCC_TRY(cudaMemsetAsync(ptr, value, size, (cudaStream_t)stream));
+    return NC_CUDA_OK;
+}
+void* nc_cuda_host_alloc(size_t size) {
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, size ? size : 16, cudaHostAllocDefault) != cudaSuccess) {
+        set_status(NC_CUDA_ERR_RUNTIME, "cudaHostAlloc(%zu) failed", size);
+        return nullptr;
+    }
+    return p;
+}
+void nc_cuda_host_free(void* ptr) {
+    if (ptr) cudaFreeHost(ptr);
+}
+int nc_cuda_stream_synchronize(void* stream) {
+    NCC_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+    return NC_CUDA_OK;
+}
+int nc_cuda_last_status(void) { return g_status; }
+const char* nc_cuda_last_message(void) { return g_message; }
+void nc_cuda_clear_status(void) {
+    g_status = NC_CUDA_OK;
+    g_message[0] = 0;
+}
+int nc_cuda_set_math_mode(int mode) {
+    int prev = g_math_mode;
+    if (mode >= NC_CUDA_MATH_TF32 && mode <= NC_CUDA_MATH_FP32_SIMT) g_math_mode = mode;
+    else set_status(NC_CUDA_ERR_ARG, "unknown math mode %d", mode);
+    return prev;
+}
+int nc_cuda_get_math_mode(void) { return g_math_mode; }
+unsigned int nc_cuda_device_error_word(void) {
+    unsigned int* w = device_error_word();
+    unsigned int h = 0;
+    if (!w) return 0;
+    if (cudaMemcpy(&h, w, sizeof(h), cudaMemcpyDeviceToHost) != cudaSuccess) return 0xffffffffu;
+    if (h) cudaMemset(w, 0, sizeof(h));
+    return h;
+}
+unsigned long long nc_cuda_launch_count(void) { return g_launches; }
+void nc_cuda_reset_launch_count(void) { g_launches = 0; }
+
+}  // extern "C"

@@ -1,0 +1,741 @@
+// Tensor-core contractions for sm_100a: TMA-fed, tcgen05.mma (kind::tf32) with the accumulator in
+// tensor memory, written with inline PTX.  One kernel template serves three problem kinds:
+//
+//   GEMM   D(M,N) = A * B^T        either operand K-major or MN-major in memory
+//   CONV   channels-last implicit GEMM, stride 1: rows = 128 output pixels (a w x h x n box),
+//          cols = output channels, reduction = (kh, kw, 32-channel chunk).  The activation tile of
+//          one reduction step is ONE 4-D TMA box at shifted (w, h) coordinates; out-of-bounds
+//          elements are zero-filled by TMA, which is the padding.  Used for forward and, with
+//          flipped / channel-transposed weights, for dX.
+//   DW     weight gradient: rows = output channels, cols = (kh, kw, ci), reduction = 32-pixel
+//          boxes; both operands MN-major; split over the reduction with an ordered second stage.
+//
+// CTA = 6 warps: warp 0 issues TMA, warp 1 allocates TMEM and issues MMAs (one lane), warps 2-5
+// convert operands in shared memory when the math mode asks for it (round-to-nearest TF32, or the
+// hi/lo split of 3xTF32) and then run the epilogue (tcgen05.ld -> registers -> global).
+// Every mbarrier wait is bounded: on expiry the kernel records a code in the device error word,
+// drains, frees its TMEM and returns.
+//
+// No cluster launch and no multicast anywhere: each CTA loads its own tiles.
+#include "tc_gemm.cuh"
+#include "../../include/nocta_cuda.h"
+
+namespace tc {
+
+enum { KIND_GEMM = 0, KIND_CONV = 1, KIND_DW = 2 };
+
+struct TcParams {
+    int kind;
+    int M, N;              // logical output extent (store masks)
+    int num_k_tiles;       // reduction tiles in total
+    int k_tiles_per_split; // reduction tiles per blockIdx.z
+    float* D;
+    long long ldd;
+    const float* bias;
+    float alpha, beta;
+    float* partial;        // non-null: raw accumulators go to partial[z][M][N]
+    // pixel-box geometry (CONV: 128-pixel output box; DW: 32-pixel reduction box)
+    int bw, bh, bn;
+    int tiles_w, tiles_h;
+    int Ho, Wo, Nimg;
+    int kW, pad;
+    int cchunks;           // CONV: 32-channel chunks of the reduction channels
+    int wrows;             // CONV: rows per (kh,kw) block of the packed weights (= output channels)
+    int Cin;               // DW: input channels (column index -> (shift, ci))
+    int desc_variant;
+    unsigned int* err;
+};
+
+static int g_desc_variant = 0;
+void set_desc_variant(int v) { g_desc_variant = v; }
+
+// ------------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait (about half a second).  Returns false and records `code` when it gives up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int* err, unsigned int code,
+                                          volatile int* abort_flag) {
+    if (mbar_test(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    unsigned int spins = 0;
+    while (true) {
+        if (mbar_test(bar, parity)) return true;
+        if ((++spins & 255u) == 0) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > 500000000ull) {
+                *abort_flag = 1;
+                if (err) atomicCAS(err, 0u, code);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap* tm, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_4d(uint32_t dst, const CUtensorMap* tm, int c0, int c1, int c2, int c3, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, Blackwell descriptor version 1.
+//   start address, leading byte offset and stride byte offset are encoded in 16-byte units.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFFu);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version
+    d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+    return d;
+}
+
+// ------------------------------------------------------------------------------------------
+// The kernel
+// ------------------------------------------------------------------------------------------
+constexpr int BM = 128;
+constexpr int BK = 32;                 // 32 floats = one 128-byte swizzle row
+constexpr int A_BYTES = BM * BK * 4;   // 16 KB
+constexpr int CHUNK_BYTES = 32 * BK * 4;  // one 32 x 32 MN-major chunk: 4 KB
+constexpr int kMaxStages = 8;
+constexpr int kSmemBudget = 196 * 1024;
+
+template <int BN, int MODE>
+struct TileCfg {
+    static constexpr int B_BYTES = BN * BK * 4;
+    static constexpr int OPER_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGE_BYTES = OPER_BYTES * (MODE == 2 ? 2 : 1);
+    static constexpr int STAGES_RAW = kSmemBudget / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > kMaxStages ? kMaxStages : STAGES_RAW;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + alignment slack
+    static constexpr int TMEM_COLS = BN <= 64 ? 64 : (BN <= 128 ? 128 : 256);
+};
+
+template <int BN, bool A_MN, bool B_MN, int MODE>
+__global__ void __launch_bounds__(192, 1)
+tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
+    using Cfg = TileCfg<BN, MODE>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t dyn_smem[];
+    __shared__ __align__(8) uint64_t bar_full[kMaxStages];
+    __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
+    __shared__ __align__(8) uint64_t bar_conv[kMaxStages];
+    __shared__ __align__(8) uint64_t bar_acc;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t tiles_base = (smem_u32(dyn_smem) + 1023u) & ~1023u;
+    uint8_t* tiles_generic = dyn_smem + (tiles_base - smem_u32(dyn_smem));
+
+    const int n_tile = blockIdx.x, m_tile = blockIdx.y, z = blockIdx.z;
+    const int kt_begin = z * p.k_tiles_per_split;
+    int kt_end = kt_begin + p.k_tiles_per_split;
+    if (kt_end > p.num_k_tiles) kt_end = p.num_k_tiles;
+    const int nk = kt_end - kt_begin;
+
+    const int m0 = m_tile * BM, n0 = n_tile * BN;
+    // CONV: decode the output pixel box of this m tile
+    int cw0 = 0, ch0 = 0, cn0 = 0;
+    if (p.kind == KIND_CONV) {
+        int tw = m_tile % p.tiles_w;
+        int t = m_tile / p.tiles_w;
+        int th = t % p.tiles_h;
+        int tn = t / p.tiles_h;
+        cw0 = tw * p.bw; ch0 = th * p.bh; cn0 = tn * p.bn;
+    }
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+            mbar_init(smem_u32(&bar_conv[s]), 128);
+        }
+        mbar_init(smem_u32(&bar_acc), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                     "r"((uint32_t)Cfg::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    volatile int* abortp = &abort_flag;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            for (int i = 0; i < nk; i++) {
+                const int s = i % STAGES, it = i / STAGES;
+                if (!mbar_wait(smem_u32(&bar_empty[s]), (uint32_t)((it & 1) ^ 1), p.err, 0x100u + s, abortp)) break;
+                const uint32_t full = smem_u32(&bar_full[s]);
+                mbar_expect_tx(full, (uint32_t)Cfg::OPER_BYTES);
+                const uint32_t a_dst = tiles_base + (uint32_t)s * Cfg::STAGE_BYTES;
+                const uint32_t b_dst = a_dst + A_BYTES;
+                const int kt = kt_begin + i;
+                if (p.kind == KIND_GEMM) {
+                    const int k0 = kt * BK;
+                    if (!A_MN) {
+                        tma_2d(a_dst, &tmA, k0, m0, full);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BM / 32; c++) tma_2d(a_dst + c * CHUNK_BYTES, &tmA, m0 + 32 * c, k0, full);
+                    }
+                    if (!B_MN) {
+                        tma_2d(b_dst, &tmB, k0, n0, full);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BN / 32; c++) tma_2d(b_dst + c * CHUNK_BYTES, &tmB, n0 + 32 * c, k0, full);
+                    }
+                } else if (p.kind == KIND_CONV) {
+                    const int shift = kt / p.cchunks, cc = kt - shift * p.cchunks;
+                    const int kh = shift / p.kW, kw = shift - kh * p.kW;
+                    tma_4d(a_dst, &tmA, cc * 32, cw0 + kw - p.pad, ch0 + kh - p.pad, cn0, full);
+                    tma_2d(b_dst, &tmB, cc * 32, shift * p.wrows + n0, full);
+                } else {
+                    const int tw = kt % p.tiles_w;
+                    const int t = kt / p.tiles_w;
+                    const int th = t % p.tiles_h, tn = t / p.tiles_h;
+                    const int w0 = tw * p.bw, h0 = th * p.bh, nn0 = tn * p.bn;
+#pragma unroll
+                    for (int c = 0; c < BM / 32; c++) tma_4d(a_dst + c * CHUNK_BYTES, &tmA, m0 + 32 * c, w0, h0, nn0, full);
+#pragma unroll
+                    for (int c = 0; c < BN / 32; c++) {
+                        const int j = n0 + 32 * c;
+                        const int shift = j / p.Cin, ci0 = j - shift * p.Cin;
+                        const int kh = shift / p.kW, kw = shift - kh * p.kW;
+                        tma_4d(b_dst + c * CHUNK_BYTES, &tmB, ci0, w0 + kw - p.pad, h0 + kh - p.pad, nn0, full);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            // instruction descriptor: D = f32, A = B = tf32, majors, N, M = 128
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                                   ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            // K-major: 8-row groups 1024 B apart (SBO); a k-step of 8 floats advances 32 B inside the swizzle row.
+            // MN-major: 32-element chunks CHUNK_BYTES apart (LBO); a k-step of 8 rows advances 1024 B.
+            uint32_t lbo_a = A_MN ? CHUNK_BYTES : 16u, sbo_a = 1024u;
+            uint32_t lbo_b = B_MN ? CHUNK_BYTES : 16u, sbo_b = 1024u;
+            if (p.desc_variant == 1) {  // bring-up alternative: swapped roles for MN-major operands
+                if (A_MN) { lbo_a = 1024u; sbo_a = CHUNK_BYTES; }
+                if (B_MN) { lbo_b = 1024u; sbo_b = CHUNK_BYTES; }
+            }
+            const uint32_t kstep_a = A_MN ? 1024u : 32u, kstep_b = B_MN ? 1024u : 32u;
+            bool ok = true;
+            for (int i = 0; i < nk && ok; i++) {
+                const int s = i % STAGES, it = i / STAGES;
+                const uint32_t ready = MODE == 0 ? smem_u32(&bar_full[s]) : smem_u32(&bar_conv[s]);
+                if (!mbar_wait(ready, (uint32_t)(it & 1), p.err, 0x200u + s, abortp)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t a_base = tiles_base + (uint32_t)s * Cfg::STAGE_BYTES;
+                const uint32_t b_base = a_base + A_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < BK / 8; ks++) {
+                    const uint64_t da = smem_desc(a_base + ks * kstep_a, lbo_a, sbo_a);
+                    const uint64_t db = smem_desc(b_base + ks * kstep_b, lbo_b, sbo_b);
+                    umma_tf32(tmem_base, da, db, idesc, (uint32_t)((i | ks) != 0));
+                    if (MODE == 2) {
+                        const uint64_t da_lo = smem_desc(a_base + Cfg::OPER_BYTES + ks * kstep_a, lbo_a, sbo_a);
+                        const uint64_t db_lo = smem_desc(b_base + Cfg::OPER_BYTES + ks * kstep_b, lbo_b, sbo_b);
+                        umma_tf32(tmem_base, da_lo, db, idesc, 1u);
+                        umma_tf32(tmem_base, da, db_lo, idesc, 1u);
+                    }
+                }
+                umma_commit(smem_u32(&bar_empty[s]));
+            }
+            umma_commit(smem_u32(&bar_acc));
+        }
+    } else {
+        // ------------------------------ converter + epilogue warps ------------------------------
+        const int te = threadIdx.x - 64;  // 0..127
+        bool ok = true;
+        if (MODE != 0) {
+            constexpr int NV = Cfg::OPER_BYTES / 16;
+            for (int i = 0; i < nk && ok; i++) {
+                const int s = i % STAGES, it = i / STAGES;
+                if (!mbar_wait(smem_u32(&bar_full[s]), (uint32_t)(it & 1), p.err, 0x300u + s, abortp)) { ok = false; break; }
+                float4* buf = reinterpret_cast<float4*>(tiles_generic + (size_t)s * Cfg::STAGE_BYTES);
+                float4* lo = reinterpret_cast<float4*>(tiles_generic + (size_t)s * Cfg::STAGE_BYTES + Cfg::OPER_BYTES);
+                for (int j = te; j < NV; j += 128) {
+                    float4 v = buf[j];
+                    float4 h = make_float4(ncc::round_tf32(v.x), ncc::round_tf32(v.y), ncc::round_tf32(v.z), ncc::round_tf32(v.w));
+                    buf[j] = h;
+                    if (MODE == 2)
+                        lo[j] = make_float4(ncc::round_tf32(v.x - h.x), ncc::round_tf32(v.y - h.y),
+                                            ncc::round_tf32(v.z - h.z), ncc::round_tf32(v.w - h.w));
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(smem_u32(&bar_conv[s]));
+            }
+        }
+        if (ok) ok = mbar_wait(smem_u32(&bar_acc), 0u, p.err, 0x400u, abortp);
+        // all 32 lanes of a warp must agree before the aligned tcgen05.ld
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tc_fence_after();
+            const int q = warp & 3;  // TMEM lane quadrant this warp may read
+            const int r = q * 32 + lane;
+            // where does this row go?
+            long long row_off = -1;
+            if (p.kind == KIND_CONV) {
+                const int iw = r % p.bw, t = r / p.bw, ih = t % p.bh, in_ = t / p.bh;
+                const int w = cw0 + iw, h = ch0 + ih, n = cn0 + in_;
+                if (w < p.Wo && h < p.Ho && n < p.Nimg) row_off = (((long long)n * p.Ho + h) * p.Wo + w) * p.ldd;
+            } else {
+                const int m = m0 + r;
+                if (m < p.M) row_off = p.partial ? ((long long)z * p.M + m) * p.N : (long long)m * p.ldd;
+            }
+            float* base = p.partial ? p.partial : p.D;
+            const bool vec_ok = ((reinterpret_cast<uintptr_t>(base) & 15u) == 0) &&
+                                (((p.partial ? (long long)p.N : p.ldd) & 3) == 0);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (n0 + c0 >= p.N) break;  // uniform across the CTA
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+                tmem_ld_wait();
+                if (row_off < 0) continue;
+                float* dst = base + row_off + n0 + c0;
+                const int ncols = (p.N - (n0 + c0)) < 32 ? (p.N - (n0 + c0)) : 32;
+                if (p.partial) {
+                    if (vec_ok && ncols == 32) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                              __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (j < ncols) dst[j] = __uint_as_float(v[j]);
+                    }
+                } else {
+                    const float* bias = p.bias ? p.bias + n0 + c0 : nullptr;
+                    if (vec_ok && ncols == 32) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 o = make_float4(p.alpha * __uint_as_float(v[j]), p.alpha * __uint_as_float(v[j + 1]),
+                                                   p.alpha * __uint_as_float(v[j + 2]), p.alpha * __uint_as_float(v[j + 3]));
+                            if (p.beta != 0.f) {
+                                float4 old = *reinterpret_cast<const float4*>(dst + j);
+                                o.x += p.beta * old.x; o.y += p.beta * old.y; o.z += p.beta * old.z; o.w += p.beta * old.w;
+                            }
+                            if (bias) { o.x += bias[j]; o.y += bias[j + 1]; o.z += bias[j + 2]; o.w += bias[j + 3]; }
+                            *reinterpret_cast<float4*>(dst + j) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            if (j < ncols) {
+                                float o = p.alpha * __uint_as_float(v[j]);
+                                if (p.beta != 0.f) o += p.beta * dst[j];
+                                if (bias) o += bias[j];
+                                dst[j] = o;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ------------------------------ teardown ------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        // A wait expired somewhere: give copies still in flight time to land before the CTA's
+        // shared memory is released.
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) { }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Second stages and weight packing
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(float* __restrict__ D, long long ldd, const float* __restrict__ partial,
+                                                            int splits, int M, int N, const float* __restrict__ bias,
+                                                            float alpha, float beta) {
+    const size_t total = (size_t)M * N, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        float acc = 0.f;
+        for (int z = 0; z < splits; z++) acc += partial[(size_t)z * total + i];
+        const int m = (int)(i / N), n = (int)(i % N);
+        float* d = D + (size_t)m * ldd + n;
+        float o = alpha * acc;
+        if (beta != 0.f) o += beta * *d;
+        if (bias) o += bias[n];
+        *d = o;
+    }
+}
+
+// partial[z][co][(kh*kW+kw)*Cin + ci]  ->  dW[co][ci][kh][kw]
+__global__ void __launch_bounds__(256) dw_reduce_kernel(float* __restrict__ dW, const float* __restrict__ partial, int splits,
+                                                        int Cout, int Cin, int kH, int kW) {
+    const size_t total = (size_t)Cout * Cin * kH * kW, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        size_t r = i;
+        const int kw = r % kW; r /= kW;
+        const int kh = r % kH; r /= kH;
+        const int ci = r % Cin;
+        const int co = (int)(r / Cin);
+        const size_t src = (size_t)co * (kH * kW * Cin) + (size_t)(kh * kW + kw) * Cin + ci;
+        float acc = 0.f;
+        for (int z = 0; z < splits; z++) acc += partial[(size_t)z * total + src];
+        dW[i] = acc;
+    }
+}
+
+template <bool DX>
+__global__ void __launch_bounds__(256) pack_weights_kernel(float* __restrict__ wp, const float* __restrict__ w, int Cout, int Cin,
+                                                           int kH, int kW, int round) {
+    const size_t total = (size_t)Cout * Cin * kH * kW, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        size_t r = i;
+        int kh, kw, co, ci;
+        if (!DX) {  // dst (kh, kw, co, ci)
+            ci = r % Cin; r /= Cin; co = r % Cout; r /= Cout; kw = r % kW; kh = (int)(r / kW);
+        } else {    // dst (kh', kw', ci, co), source taps flipped
+            co = r % Cout; r /= Cout; ci = r % Cin; r /= Cin; kw = r % kW; kh = (int)(r / kW);
+            kh = kH - 1 - kh; kw = kW - 1 - kw;
+        }
+        float v = w[(((size_t)co * Cin + ci) * kH + kh) * kW + kw];
+        wp[i] = round ? ncc::round_tf32(v) : v;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)sym;
+    }
+    return fn;
+}
+
+// rank-2..4 f32 tensor map with 128-byte swizzle; dims/box innermost first, strides in elements for dims 1..
+static bool make_map(CUtensorMap* tm, const float* base, int rank, const unsigned long long* dims,
+                     const unsigned long long* strides_elems, const unsigned* box) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    if (reinterpret_cast<uintptr_t>(base) & 15u) return false;
+    cuuint64_t gdim[4], gstr[3];
+    cuuint32_t bdim[4], estr[4];
+    for (int i = 0; i < rank; i++) {
+        gdim[i] = dims[i];
+        bdim[i] = box[i];
+        estr[i] = 1;
+        if (dims[i] == 0 || box[i] == 0 || box[i] > 256) return false;
+    }
+    for (int i = 0; i + 1 < rank; i++) {
+        gstr[i] = strides_elems[i] * 4ull;
+        if (gstr[i] % 16 != 0) return false;
+    }
+    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<float*>(base), gdim, gstr, bdim, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+template <int BN, bool A_MN, bool B_MN, int MODE>
+static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const TcParams& p, dim3 grid, cudaStream_t st) {
+    using Cfg = TileCfg<BN, MODE>;
+    static bool attr_set = false;
+    auto kern = tc_kernel<BN, A_MN, B_MN, MODE>;
+    if (!attr_set) {
+        NCC_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        attr_set = true;
+    }
+    kern<<<grid, 192, Cfg::SMEM_BYTES, st>>>(ta, tb, p);
+    NCC_COUNT_LAUNCH();
+    return ncc::launch_status("tc_kernel");
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_mode(int mode, const CUtensorMap& ta, const CUtensorMap& tb, const TcParams& p, dim3 grid, cudaStream_t st) {
+    switch (mode) {
+        case NC_CUDA_MATH_TF32: return launch_one<BN, A_MN, B_MN, 0>(ta, tb, p, grid, st);
+        case NC_CUDA_MATH_TF32_RNA: return launch_one<BN, A_MN, B_MN, 1>(ta, tb, p, grid, st);
+        case NC_CUDA_MATH_3XTF32: return launch_one<BN, A_MN, B_MN, 2>(ta, tb, p, grid, st);
+    }
+    return ncc::set_status(NC_CUDA_ERR_ARG, "tc: unknown math mode %d", mode);
+}
+
+template <bool A_MN, bool B_MN>
+static int launch_bn(int bn, int mode, const CUtensorMap& ta, const CUtensorMap& tb, const TcParams& p, dim3 grid, cudaStream_t st) {
+    switch (bn) {
+        case 64: return launch_mode<64, A_MN, B_MN>(mode, ta, tb, p, grid, st);
+        case 128: return launch_mode<128, A_MN, B_MN>(mode, ta, tb, p, grid, st);
+        case 256: return launch_mode<256, A_MN, B_MN>(mode, ta, tb, p, grid, st);
+    }
+    return ncc::set_status(NC_CUDA_ERR_ARG, "tc: unsupported tile width %d", bn);
+}
+
+static int pick_bn(int N) { return N <= 64 ? 64 : (N <= 128 ? 128 : 256); }
+
+// splits over the reduction so that about one wave of CTAs exists; each split keeps >= 4 tiles
+static void pick_splits(int tiles, int nk, int* splits, int* kps) {
+    int s = 1;
+    const int sms = ncc::sm_count();
+    if (tiles * 2 <= sms && nk >= 8) {
+        s = sms / tiles;
+        if (s > nk / 4) s = nk / 4;
+        if (s < 1) s = 1;
+    }
+    int per = (nk + s - 1) / s;
+    *kps = per;
+    *splits = (nk + per - 1) / per;
+}
+
+int gemm(float* D, int ldd, const float* A, int lda, bool a_mn, const float* B, int ldb, bool b_mn, int M, int N, int K,
+         const float* bias, float alpha, float beta, int mode, cudaStream_t st) {
+    if (M < 128 || N < 16 || K < 32) return NC_CUDA_ERR_UNSUPPORTED;
+    if ((lda & 3) || (ldb & 3)) return NC_CUDA_ERR_UNSUPPORTED;
+    const int bn = pick_bn(N);
+    CUtensorMap ta, tb;
+    {
+        unsigned long long dims[2], str[1];
+        unsigned box[2];
+        if (!a_mn) { dims[0] = K; dims[1] = M; str[0] = lda; box[0] = 32; box[1] = 128; }
+        else       { dims[0] = M; dims[1] = K; str[0] = lda; box[0] = 32; box[1] = 32; }
+        if (!make_map(&ta, A, 2, dims, str, box)) return NC_CUDA_ERR_UNSUPPORTED;
+        if (!b_mn) { dims[0] = K; dims[1] = N; str[0] = ldb; box[0] = 32; box[1] = (unsigned)bn; }
+        else       { dims[0] = N; dims[1] = K; str[0] = ldb; box[0] = 32; box[1] = 32; }
+        if (!make_map(&tb, B, 2, dims, str, box)) return NC_CUDA_ERR_UNSUPPORTED;
+    }
+    TcParams p = {};
+    p.kind = KIND_GEMM;
+    p.M = M; p.N = N;
+    p.num_k_tiles = (K + BK - 1) / BK;
+    p.D = D; p.ldd = ldd; p.bias = bias; p.alpha = alpha; p.beta = beta;
+    p.desc_variant = g_desc_variant;
+    p.err = ncc::device_error_word();
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + bn - 1) / bn;
+    if (tiles_m > 65535) return NC_CUDA_ERR_UNSUPPORTED;
+    int splits, kps;
+    pick_splits(tiles_m * tiles_n, p.num_k_tiles, &splits, &kps);
+    p.k_tiles_per_split = kps;
+    if (splits > 1) {
+        p.partial = (float*)ncc::scratch(2, sizeof(float) * (size_t)splits * M * N, st);
+        if (!p.partial) return NC_CUDA_ERR_RUNTIME;
+    }
+    dim3 grid(tiles_n, tiles_m, splits);
+    int rc;
+    if (!a_mn && !b_mn) rc = launch_bn<false, false>(bn, mode, ta, tb, p, grid, st);
+    else if (!a_mn && b_mn) rc = launch_bn<false, true>(bn, mode, ta, tb, p, grid, st);
+    else if (a_mn && !b_mn) rc = launch_bn<true, false>(bn, mode, ta, tb, p, grid, st);
+    else rc = launch_bn<true, true>(bn, mode, ta, tb, p, grid, st);
+    if (rc) return rc;
+    if (splits > 1) {
+        splitk_reduce_kernel<<<ncc::grid_for((long long)M * N, 256), 256, 0, st>>>(D, ldd, p.partial, splits, M, N, bias, alpha, beta);
+        NCC_COUNT_LAUNCH();
+        return ncc::launch_status("splitk_reduce");
+    }
+    return NC_CUDA_OK;
+}
+
+// Pixel box (bw, bh, bn) with bw*bh*bn == pixels that wastes the fewest rows for this image size.
+static void pick_box(int pixels, int Wd, int Hd, int Nd, int* bw, int* bh, int* bn) {
+    long long best = -1;
+    for (int w = 1; w <= pixels; w *= 2)
+        for (int h = 1; w * h <= pixels; h *= 2) {
+            int n = pixels / (w * h);
+            if (w * h * n != pixels || w > 256 || h > 256 || n > 256) continue;
+            long long cover = (long long)((Wd + w - 1) / w) * w * ((Hd + h - 1) / h) * h * ((Nd + n - 1) / n) * n;
+            // prefer less waste, then wider rows (longer contiguous runs), then fewer images per box
+            if (best < 0 || cover < best || (cover == best && (w > *bw || (w == *bw && n < *bn)))) {
+                best = cover; *bw = w; *bh = h; *bn = n;
+            }
+        }
+}
+
+int conv_nhwc(float* y, const float* x, const float* wpacked, const float* bias, int N, int H, int W, int Cin, int Cout,
+              int kH, int kW, int pad, int mode, cudaStream_t st) {
+    const int Ho = H + 2 * pad - kH + 1, Wo = W + 2 * pad - kW + 1;
+    if (Ho <= 0 || Wo <= 0) return NC_CUDA_ERR_UNSUPPORTED;
+    if ((Cin & 3) || (Cout & 3) || Cin < 16 || Cout < 16) return NC_CUDA_ERR_UNSUPPORTED;
+    if ((long long)N * Ho * Wo < 128) return NC_CUDA_ERR_UNSUPPORTED;
+    const int bn_cols = pick_bn(Cout);
+    int bw = 1, bh = 1, bnn = 1;
+    pick_box(128, Wo, Ho, N, &bw, &bh, &bnn);
+    CUtensorMap ta, tb;
+    {
+        unsigned long long dims[4] = {(unsigned long long)Cin, (unsigned long long)W, (unsigned long long)H, (unsigned long long)N};
+        unsigned long long str[3] = {(unsigned long long)Cin, (unsigned long long)W * Cin, (unsigned long long)H * W * Cin};
+        unsigned box[4] = {32, (unsigned)bw, (unsigned)bh, (unsigned)bnn};
+        if (!make_map(&ta, x, 4, dims, str, box)) return NC_CUDA_ERR_UNSUPPORTED;
+        unsigned long long wd[2] = {(unsigned long long)Cin, (unsigned long long)kH * kW * Cout};
+        unsigned long long ws[1] = {(unsigned long long)Cin};
+        unsigned wb[2] = {32, (unsigned)bn_cols};
+        if (!make_map(&tb, wpacked, 2, wd, ws, wb)) return NC_CUDA_ERR_UNSUPPORTED;
+    }
+    TcParams p = {};
+    p.kind = KIND_CONV;
+    p.M = N * Ho * Wo; p.N = Cout;
+    p.cchunks = (Cin + 31) / 32;
+    p.num_k_tiles = kH * kW * p.cchunks;
+    p.k_tiles_per_split = p.num_k_tiles;
+    p.D = y; p.ldd = Cout; p.bias = bias; p.alpha = 1.f; p.beta = 0.f;
+    p.bw = bw; p.bh = bh; p.bn = bnn;
+    p.tiles_w = (Wo + bw - 1) / bw; p.tiles_h = (Ho + bh - 1) / bh;
+    p.Ho = Ho; p.Wo = Wo; p.Nimg = N;
+    p.kW = kW; p.pad = pad; p.wrows = Cout;
+    p.desc_variant = g_desc_variant;
+    p.err = ncc::device_error_word();
+    const long long tiles_m = (long long)p.tiles_w * p.tiles_h * ((N + bnn - 1) / bnn);
+    if (tiles_m > 65535) return NC_CUDA_ERR_UNSUPPORTED;
+    dim3 grid((Cout + bn_cols - 1) / bn_cols, (unsigned)tiles_m, 1);
+    return launch_bn<false, false>(bn_cols, mode, ta, tb, p, grid, st);
+}
+
+int conv_dw_nhwc(float* dW, const float* dy, const float* x, int N, int H, int W, int Cin, int Cout, int kH, int kW, int pad,
+                 int mode, cudaStream_t st) {
+    const int Ho = H + 2 * pad - kH + 1, Wo = W + 2 * pad - kW + 1;
+    if (Ho <= 0 || Wo <= 0) return NC_CUDA_ERR_UNSUPPORTED;
+    if ((Cin & 31) || (Cout & 3) || Cout < 32) return NC_CUDA_ERR_UNSUPPORTED;
+    const int Ncols = kH * kW * Cin;
+    // column tile: whole filter rows when they fit in 256 columns, else 256 / 128 / 64
+    int bn_cols;
+    if (kW * Cin <= 256 && (kW * Cin) % 32 == 0 && (kW * Cin == 64 || kW * Cin == 128 || kW * Cin == 192 || kW * Cin == 256)) bn_cols = kW * Cin;
+    else bn_cols = pick_bn(Ncols);
+    int bw = 1, bh = 1, bnn = 1;
+    pick_box(32, Wo, Ho, N, &bw, &bh, &bnn);
+    CUtensorMap ta, tb;
+    {
+        unsigned long long dims[4] = {(unsigned long long)Cout, (unsigned long long)Wo, (unsigned long long)Ho, (unsigned long long)N};
+        unsigned long long str[3] = {(unsigned long long)Cout, (unsigned long long)Wo * Cout, (unsigned long long)Ho * Wo * Cout};
+        unsigned box[4] = {32, (unsigned)bw, (unsigned)bh, (unsigned)bnn};
+        if (!make_map(&ta, dy, 4, dims, str, box)) return NC_CUDA_ERR_UNSUPPORTED;
+        unsigned long long xd[4] = {(unsigned long long)Cin, (unsigned long long)W, (unsigned long long)H, (unsigned long long)N};
+        unsigned long long xs[3] = {(unsigned long long)Cin, (unsigned long long)W * Cin, (unsigned long long)H * W * Cin};
+        if (!make_map(&tb, x, 4, xd, xs, box)) return NC_CUDA_ERR_UNSUPPORTED;
+    }
+    TcParams p = {};
+    p.kind = KIND_DW;
+    p.M = Cout; p.N = Ncols;
+    p.bw = bw; p.bh = bh; p.bn = bnn;
+    p.tiles_w = (Wo + bw - 1) / bw; p.tiles_h = (Ho + bh - 1) / bh;
+    p.Ho = Ho; p.Wo = Wo; p.Nimg = N;
+    p.kW = kW; p.pad = pad; p.Cin = Cin;
+    p.num_k_tiles = p.tiles_w * p.tiles_h * ((N + bnn - 1) / bnn);
+    p.alpha = 1.f;
+    p.desc_variant = g_desc_variant;
+    p.err = ncc::device_error_word();
+    const int tiles_m = (Cout + BM - 1) / BM, tiles_n = (Ncols + bn_cols - 1) / bn_cols;
+    int splits, kps;
+    pick_splits(tiles_m * tiles_n, p.num_k_tiles, &splits, &kps);
+    p.k_tiles_per_split = kps;
+    p.partial = (float*)ncc::scratch(2, sizeof(float) * (size_t)splits * Cout * Ncols, st);
+    if (!p.partial) return NC_CUDA_ERR_RUNTIME;
+    dim3 grid(tiles_n, tiles_m, splits);
+    int rc;
+    if (bn_cols == 192) rc = launch_mode<192, true, true>(mode, ta, tb, p, grid, st);
+    else rc = launch_bn<true, true>(bn_cols, mode, ta, tb, p, grid, st);
+    if (rc) return rc;
+    dw_reduce_kernel<<<ncc::grid_for((long long)Cout * Ncols, 256), 256, 0, st>>>(dW, p.partial, splits, Cout, Cin, kH, kW);
+    NCC_COUNT_LAUNCH();
+    return ncc::launch_status("dw_reduce");
+}
+
+int pack_weights_fwd(float* wp, const float* w, int Cout, int Cin, int kH, int kW, bool round, cudaStream_t st) {
+    pack_weights_kernel<false><<<ncc::grid_for((long long)Cout * Cin * kH * kW, 256), 256, 0, st>>>(wp, w, Cout, Cin, kH, kW, round ? 1 : 0);
+    NCC_COUNT_LAUNCH();
+    return ncc::launch_status("pack_weights_fwd");
+}
+int pack_weights_dx(float* wp, const float* w, int Cout, int Cin, int kH, int kW, bool round, cudaStream_t st) {
+    pack_weights_kernel<true><<<ncc::grid_for((long long)Cout * Cin * kH * kW, 256), 256, 0, st>>>(wp, w, Cout, Cin, kH, kW, round ? 1 : 0);
+    NCC_COUNT_LAUNCH();
+    return ncc::launch_status("pack_weights_dx");
+}
+
+}  // namespace tc
+
+// Bring-up knob (not part of the public header): selects an alternative shared-memory descriptor
+// encoding for MN-major operands so both can be checked against a known answer on hardware.
+extern "C" void nc_cuda_debug_desc_variant(int v) { tc::set_desc_variant(v); }
