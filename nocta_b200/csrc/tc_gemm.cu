@@ -139,15 +139,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor, 128-byte swizzle, Blackwell descriptor version 1.
-//   start address, leading byte offset and stride byte offset are encoded in 16-byte units.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// Shared-memory matrix descriptor, Blackwell descriptor version 1.  Start address, leading byte
+// offset and stride byte offset are encoded in 16-byte units.  layout: 2 = 128-byte swizzle on
+// 16-byte units (K-major operands), 1 = 128-byte swizzle on 32-byte units, the only swizzled
+// layout the tensor core accepts for MN-major 32-bit operands.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
     uint64_t d = 0;
     d |= (uint64_t)((addr >> 4) & 0x3FFFu);
     d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
     d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
     d |= (uint64_t)1 << 46;  // descriptor version
-    d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+    d |= (uint64_t)layout << 61;
     return d;
 }
 
@@ -169,7 +171,12 @@ struct TileCfg {
     static constexpr int STAGES_RAW = kSmemBudget / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > kMaxStages ? kMaxStages : STAGES_RAW;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + alignment slack
-    static constexpr int TMEM_COLS = BN <= 64 ? 64 : (BN <= 128 ? 128 : 256);
+    static constexpr int ACC_COLS = BN <= 64 ? 64 : (BN <= 128 ? 128 : 256);
+    // 3xTF32 spreads the reduction over several accumulators (round-robin per k-step) and adds them
+    // in FP32 in the epilogue: the tensor core's own accumulation is the largest error term left in
+    // that mode and it grows with the number of additions into one accumulator.
+    static constexpr int NACC = MODE == 2 ? (512 / ACC_COLS > 4 ? 4 : 512 / ACC_COLS) : 1;
+    static constexpr int TMEM_COLS = ACC_COLS * NACC;
 };
 
 template <int BN, bool A_MN, bool B_MN, int MODE>
@@ -283,13 +290,16 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
                                    ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             // K-major: 8-row groups 1024 B apart (SBO); a k-step of 8 floats advances 32 B inside the swizzle row.
-            // MN-major: 32-element chunks CHUNK_BYTES apart (LBO); a k-step of 8 rows advances 1024 B.
-            uint32_t lbo_a = A_MN ? CHUNK_BYTES : 16u, sbo_a = 1024u;
-            uint32_t lbo_b = B_MN ? CHUNK_BYTES : 16u, sbo_b = 1024u;
+            // MN-major: rows are reduction indices, 128 B (32 elements of M/N) each; the swizzle atom is
+            // 4 rows (SBO = 512 B between atoms along k), 32-element chunks are CHUNK_BYTES apart (LBO);
+            // a k-step of 8 rows advances 1024 B.
+            uint32_t lbo_a = A_MN ? CHUNK_BYTES : 16u, sbo_a = A_MN ? 512u : 1024u;
+            uint32_t lbo_b = B_MN ? CHUNK_BYTES : 16u, sbo_b = B_MN ? 512u : 1024u;
             if (p.desc_variant == 1) {  // bring-up alternative: swapped roles for MN-major operands
-                if (A_MN) { lbo_a = 1024u; sbo_a = CHUNK_BYTES; }
-                if (B_MN) { lbo_b = 1024u; sbo_b = CHUNK_BYTES; }
+                if (A_MN) { lbo_a = 512u; sbo_a = CHUNK_BYTES; }
+                if (B_MN) { lbo_b = 512u; sbo_b = CHUNK_BYTES; }
             }
+            const uint32_t lay_a = A_MN ? 1u : 2u, lay_b = B_MN ? 1u : 2u;
             const uint32_t kstep_a = A_MN ? 1024u : 32u, kstep_b = B_MN ? 1024u : 32u;
             bool ok = true;
             for (int i = 0; i < nk && ok; i++) {
@@ -301,14 +311,19 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                 const uint32_t b_base = a_base + A_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < BK / 8; ks++) {
-                    const uint64_t da = smem_desc(a_base + ks * kstep_a, lbo_a, sbo_a);
-                    const uint64_t db = smem_desc(b_base + ks * kstep_b, lbo_b, sbo_b);
-                    umma_tf32(tmem_base, da, db, idesc, (uint32_t)((i | ks) != 0));
+                    const uint64_t da = smem_desc(a_base + ks * kstep_a, lbo_a, sbo_a, lay_a);
+                    const uint64_t db = smem_desc(b_base + ks * kstep_b, lbo_b, sbo_b, lay_b);
                     if (MODE == 2) {
-                        const uint64_t da_lo = smem_desc(a_base + Cfg::OPER_BYTES + ks * kstep_a, lbo_a, sbo_a);
-                        const uint64_t db_lo = smem_desc(b_base + Cfg::OPER_BYTES + ks * kstep_b, lbo_b, sbo_b);
-                        umma_tf32(tmem_base, da_lo, db, idesc, 1u);
-                        umma_tf32(tmem_base, da, db_lo, idesc, 1u);
+                        // accumulator (ks % NACC); small cross terms first, then the main product
+                        const uint32_t acc = tmem_base + (uint32_t)((ks % Cfg::NACC) * Cfg::ACC_COLS);
+                        const bool first = (i == 0) && (ks < Cfg::NACC);
+                        const uint64_t da_lo = smem_desc(a_base + Cfg::OPER_BYTES + ks * kstep_a, lbo_a, sbo_a, lay_a);
+                        const uint64_t db_lo = smem_desc(b_base + Cfg::OPER_BYTES + ks * kstep_b, lbo_b, sbo_b, lay_b);
+                        umma_tf32(acc, da_lo, db, idesc, first ? 0u : 1u);
+                        umma_tf32(acc, da, db_lo, idesc, 1u);
+                        umma_tf32(acc, da, db, idesc, 1u);
+                    } else {
+                        umma_tf32(tmem_base, da, db, idesc, (uint32_t)((i | ks) != 0));
                     }
                 }
                 umma_commit(smem_u32(&bar_empty[s]));
@@ -364,6 +379,16 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
                 tmem_ld_wait();
+                if (Cfg::NACC > 1) {
+#pragma unroll 1
+                    for (int a = 1; a < Cfg::NACC; a++) {
+                        uint32_t u[32];
+                        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * Cfg::ACC_COLS + c0), u);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(u[j]));
+                    }
+                }
                 if (row_off < 0) continue;
                 float* dst = base + row_off + n0 + c0;
                 const int ncols = (p.N - (n0 + c0)) < 32 ? (p.N - (n0 + c0)) : 32;
@@ -501,7 +526,7 @@ static EncodeTiledFn encode_fn() {
 
 // rank-2..4 f32 tensor map with 128-byte swizzle; dims/box innermost first, strides in elements for dims 1..
 static bool make_map(CUtensorMap* tm, const float* base, int rank, const unsigned long long* dims,
-                     const unsigned long long* strides_elems, const unsigned* box) {
+                     const unsigned long long* strides_elems, const unsigned* box, bool mn_major) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     if (reinterpret_cast<uintptr_t>(base) & 15u) return false;
@@ -518,7 +543,8 @@ static bool make_map(CUtensorMap* tm, const float* base, int rank, const unsigne
         if (gstr[i] % 16 != 0) return false;
     }
     CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<float*>(base), gdim, gstr, bdim, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
@@ -557,7 +583,8 @@ static int launch_bn(int bn, int mode, const CUtensorMap& ta, const CUtensorMap&
     return ncc::set_status(NC_CUDA_ERR_ARG, "tc: unsupported tile width %d", bn);
 }
 
-static int pick_bn(int N) { return N <= 64 ? 64 : (N <= 128 ? 128 : 256); }
+// 3xTF32 prefers 128-column tiles: four accumulators fit in tensor memory instead of two.
+static int pick_bn(int N, int mode = 0) { return N <= 64 ? 64 : ((N <= 128 || mode == NC_CUDA_MATH_3XTF32) ? 128 : 256); }
 
 // splits over the reduction so that about one wave of CTAs exists; each split keeps >= 4 tiles
 static void pick_splits(int tiles, int nk, int* splits, int* kps) {
@@ -577,17 +604,17 @@ int gemm(float* D, int ldd, const float* A, int lda, bool a_mn, const float* B, 
          const float* bias, float alpha, float beta, int mode, cudaStream_t st) {
     if (M < 128 || N < 16 || K < 32) return NC_CUDA_ERR_UNSUPPORTED;
     if ((lda & 3) || (ldb & 3)) return NC_CUDA_ERR_UNSUPPORTED;
-    const int bn = pick_bn(N);
+    const int bn = pick_bn(N, mode);
     CUtensorMap ta, tb;
     {
         unsigned long long dims[2], str[1];
         unsigned box[2];
         if (!a_mn) { dims[0] = K; dims[1] = M; str[0] = lda; box[0] = 32; box[1] = 128; }
         else       { dims[0] = M; dims[1] = K; str[0] = lda; box[0] = 32; box[1] = 32; }
-        if (!make_map(&ta, A, 2, dims, str, box)) return NC_CUDA_ERR_UNSUPPORTED;
+        if (!make_map(&ta, A, 2, dims, str, box, a_mn)) return NC_CUDA_ERR_UNSUPPORTED;
         if (!b_mn) { dims[0] = K; dims[1] = N; str[0] = ldb; box[0] = 32; box[1] = (unsigned)bn; }
         else       { dims[0] = N; dims[1] = K; str[0] = ldb; box[0] = 32; box[1] = 32; }
-        if (!make_map(&tb, B, 2, dims, str, box)) return NC_CUDA_ERR_UNSUPPORTED;
+        if (!make_map(&tb, B, 2, dims, str, box, b_mn)) return NC_CUDA_ERR_UNSUPPORTED;
     }
     TcParams p = {};
     p.kind = KIND_GEMM;
@@ -641,7 +668,7 @@ int conv_nhwc(float* y, const float* x, const float* wpacked, const float* bias,
     if (Ho <= 0 || Wo <= 0) return NC_CUDA_ERR_UNSUPPORTED;
     if ((Cin & 3) || (Cout & 3) || Cin < 16 || Cout < 16) return NC_CUDA_ERR_UNSUPPORTED;
     if ((long long)N * Ho * Wo < 128) return NC_CUDA_ERR_UNSUPPORTED;
-    const int bn_cols = pick_bn(Cout);
+    const int bn_cols = pick_bn(Cout, mode);
     int bw = 1, bh = 1, bnn = 1;
     pick_box(128, Wo, Ho, N, &bw, &bh, &bnn);
     CUtensorMap ta, tb;
@@ -649,11 +676,11 @@ int conv_nhwc(float* y, const float* x, const float* wpacked, const float* bias,
         unsigned long long dims[4] = {(unsigned long long)Cin, (unsigned long long)W, (unsigned long long)H, (unsigned long long)N};
         unsigned long long str[3] = {(unsigned long long)Cin, (unsigned long long)W * Cin, (unsigned long long)H * W * Cin};
         unsigned box[4] = {32, (unsigned)bw, (unsigned)bh, (unsigned)bnn};
-        if (!make_map(&ta, x, 4, dims, str, box)) return NC_CUDA_ERR_UNSUPPORTED;
+        if (!make_map(&ta, x, 4, dims, str, box, false)) return NC_CUDA_ERR_UNSUPPORTED;
         unsigned long long wd[2] = {(unsigned long long)Cin, (unsigned long long)kH * kW * Cout};
         unsigned long long ws[1] = {(unsigned long long)Cin};
         unsigned wb[2] = {32, (unsigned)bn_cols};
-        if (!make_map(&tb, wpacked, 2, wd, ws, wb)) return NC_CUDA_ERR_UNSUPPORTED;
+        if (!make_map(&tb, wpacked, 2, wd, ws, wb, false)) return NC_CUDA_ERR_UNSUPPORTED;
     }
     TcParams p = {};
     p.kind = KIND_CONV;
@@ -691,10 +718,10 @@ int conv_dw_nhwc(float* dW, const float* dy, const float* x, int N, int H, int W
         unsigned long long dims[4] = {(unsigned long long)Cout, (unsigned long long)Wo, (unsigned long long)Ho, (unsigned long long)N};
         unsigned long long str[3] = {(unsigned long long)Cout, (unsigned long long)Wo * Cout, (unsigned long long)Ho * Wo * Cout};
         unsigned box[4] = {32, (unsigned)bw, (unsigned)bh, (unsigned)bnn};
-        if (!make_map(&ta, dy, 4, dims, str, box)) return NC_CUDA_ERR_UNSUPPORTED;
+        if (!make_map(&ta, dy, 4, dims, str, box, true)) return NC_CUDA_ERR_UNSUPPORTED;
         unsigned long long xd[4] = {(unsigned long long)Cin, (unsigned long long)W, (unsigned long long)H, (unsigned long long)N};
         unsigned long long xs[3] = {(unsigned long long)Cin, (unsigned long long)W * Cin, (unsigned long long)H * W * Cin};
-        if (!make_map(&tb, x, 4, xd, xs, box)) return NC_CUDA_ERR_UNSUPPORTED;
+        if (!make_map(&tb, x, 4, xd, xs, box, true)) return NC_CUDA_ERR_UNSUPPORTED;
     }
     TcParams p = {};
     p.kind = KIND_DW;
