@@ -1,0 +1,403 @@
+/*
+ * nocta/nocta.h — the nc_* C API of the B200 training backend (host side).
+ *
+ * Source-compatible with the reference library's public API for the training path: same type
+ * names, struct field order (applications read t->shape, t->grad, m->params, opt->t directly),
+ * function names, argument meaning and error behaviour (NULL + nc_last_error, never abort).
+ * Reference declarations: include/nocta/core/{dtype,error,memory,device,tensor}.h,
+ * autograd/{node,backward}.h, ops/{arithmetic,matmul,activation,reduction,loss}.h,
+ * nn/{module,linear,conv,batchnorm,dropout}.h, optim/{optimizer,sgd,adam}.h.
+ *
+ * Differences a caller can observe:
+ *   - Arithmetic runs on the CUDA device only.  nc_init() makes CUDA the default device, so
+ *     tensors created afterwards live in device memory; an op given a CPU-resident tensor
+ *     fails with NC_ERR_DEVICE instead of computing on the host.
+ *   - Element accessors (the nc_tensor_get / nc_tensor_set family) work on device tensors by copying the one element.
+ *   - 4-D activations produced by conv / batchnorm / relu / maxpool on the device are stored
+ *     channels-last; their shape is still (N,C,H,W) and their strides say so.
+ *   - nc_flatten, nc_tensor_reshape-of-an-activation (through nc_flatten) and nc_gelu take part
+ *     in autograd (the reference registers no node for them).
+ *   - nc_node carries extra trailing fields; code that only touches the reference's fields is
+ *     unaffected because nodes are always allocated by nc_node_create.
+ */
+#ifndef NOCTA_B200_NOCTA_H
+#define NOCTA_B200_NOCTA_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NOCTA_VERSION "0.6.0-b200"
+#define NOCTA_VERSION_MAJOR 0
+#define NOCTA_VERSION_MINOR 6
+#define NOCTA_VERSION_PATCH 0
+
+/* ------------------------------------------------------------------ dtypes (core/dtype.h) */
+typedef enum { NC_F32, NC_F64, NC_I32, NC_I64, NC_U8, NC_BOOL, NC_DTYPE_COUNT } nc_dtype;
+size_t nc_dtype_sizeof(nc_dtype dtype);
+const char* nc_dtype_to_string(nc_dtype dtype);
+
+/* ------------------------------------------------------------------ errors (core/error.h:6-55) */
+typedef enum {
+    NC_OK = 0,
+    NC_ERR_NULL_PTR,
+    NC_ERR_ALLOC,
+    NC_ERR_SHAPE_MISMATCH,
+    NC_ERR_DTYPE_MISMATCH,
+    NC_ERR_INDEX_OUT_OF_BOUNDS,
+    NC_ERR_INVALID_AXIS,
+    NC_ERR_INVALID_SHAPE,
+    NC_ERR_INVALID_DTYPE,
+    NC_ERR_NOT_CONTIGUOUS,
+    NC_ERR_NO_GRAD,
+    NC_ERR_GRAPH_CYCLE,
+    NC_ERR_IO,
+    NC_ERR_UNKNOWN,
+    NC_ERR_DEVICE /* new: tensor is not on the CUDA device, or a kernel call failed */
+} nc_error;
+extern nc_error nc_last_error;
+extern char nc_error_context[256];
+const char* nc_error_string(nc_error err);
+#define NC_SET_ERROR(err, ...)                                              \
+    do {                                                                    \
+        nc_last_error = (err);                                              \
+        snprintf(nc_error_context, sizeof(nc_error_context), __VA_ARGS__);  \
+    } while (0)
+static inline nc_error nc_get_error(void) { return nc_last_error; }
+static inline void nc_clear_error(void) { nc_last_error = NC_OK; nc_error_context[0] = '\0'; }
+
+/* ------------------------------------------------------------------ devices (core/device.h) */
+typedef enum { NC_DEVICE_CPU = 0, NC_DEVICE_CUDA = 1 } nc_device_type;
+typedef struct {
+    nc_device_type type;
+    int index;
+    char name[256];
+    size_t total_memory;
+    size_t free_memory;
+} nc_device_info;
+void nc_set_default_device(nc_device_type type);
+nc_device_type nc_get_default_device(void);
+nc_device_info nc_cuda_device_info(int device_index);
+/* the nc_cuda_* runtime entry points (nc_cuda_available, nc_cuda_init, ...) are declared in nocta_cuda.h */
+
+/* ------------------------------------------------------------------ memory (core/memory.h) */
+void* nc_alloc(size_t size);
+void* nc_calloc(size_t count, size_t size);
+void* nc_realloc(void* ptr, size_t old_size, size_t new_size);
+void nc_free(void* ptr);
+typedef struct {
+    size_t total_allocated, total_freed, current_usage, peak_usage, allocation_count, free_count;
+} nc_mem_stats;
+nc_mem_stats nc_memory_stats(void);
+void nc_memory_stats_reset(void);
+void nc_memory_report(void);
+/* new: device pool statistics (bytes held by the caching device allocator / handed out) */
+typedef struct {
+    size_t bytes_reserved, bytes_in_use, peak_in_use, cuda_mallocs, pool_hits;
+} nc_device_pool_stats;
+nc_device_pool_stats nc_device_pool_get_stats(void);
+void nc_device_pool_release(void); /* return cached blocks to the driver */
+
+typedef struct {
+    void* data;      /* CPU pointer (NULL while the bytes live on the device only) */
+    void* cuda_data; /* device pointer (NULL while on the CPU only) */
+    size_t size;     /* bytes */
+    int refcount;
+    nc_device_type device;
+} nc_storage;
+nc_storage* nc_storage_create(size_t size);
+nc_storage* nc_storage_create_on(size_t size, nc_device_type device);
+nc_storage* nc_storage_retain(nc_storage* storage);
+void nc_storage_release(nc_storage* storage);
+int nc_storage_refcount(const nc_storage* storage);
+void nc_storage_to_device(nc_storage* s, nc_device_type target);
+void nc_storage_ensure_on(nc_storage* s, nc_device_type target);
+void* nc_storage_data_ptr(nc_storage* s);
+void nc_storage_sync_to_cpu(nc_storage* s);
+
+/* ------------------------------------------------------------------ tensors (core/tensor.h) */
+#define NC_MAX_DIMS 8
+typedef struct nc_node nc_node;
+typedef struct nc_tensor {
+    nc_storage* storage;
+    size_t offset; /* elements */
+    size_t ndim;
+    size_t shape[NC_MAX_DIMS];
+    size_t strides[NC_MAX_DIMS]; /* elements */
+    size_t numel;
+    nc_dtype dtype;
+    bool requires_grad;
+    struct nc_tensor* grad;
+    nc_node* grad_fn;
+    bool is_leaf;
+    bool is_contiguous;
+    bool is_reachable;
+} nc_tensor;
+
+nc_tensor* nc_tensor_empty(const size_t* shape, size_t ndim, nc_dtype dtype);
+nc_tensor* nc_tensor_zeros(const size_t* shape, size_t ndim, nc_dtype dtype);
+nc_tensor* nc_tensor_ones(const size_t* shape, size_t ndim, nc_dtype dtype);
+nc_tensor* nc_tensor_full(const size_t* shape, size_t ndim, nc_dtype dtype, double value);
+nc_tensor* nc_tensor_from_data(const void* data, const size_t* shape, size_t ndim, nc_dtype dtype);
+nc_tensor* nc_tensor_scalar(double value, nc_dtype dtype);
+nc_tensor* nc_tensor_arange(double start, double end, double step, nc_dtype dtype);
+nc_tensor* nc_tensor_rand(const size_t* shape, size_t ndim, nc_dtype dtype);
+nc_tensor* nc_tensor_randn(const size_t* shape, size_t ndim, nc_dtype dtype);
+nc_tensor* nc_tensor_clone(const nc_tensor* r);
+void nc_tensor_free(nc_tensor* t);
+/* new: seed for nc_tensor_rand/randn and the module initialisers (the reference seeds from time()) */
+void nc_manual_seed(uint64_t seed);
+
+static inline size_t nc_tensor_numel(const nc_tensor* t) { return t ? t->numel : 0; }
+static inline size_t nc_tensor_ndim(const nc_tensor* t) { return t ? t->ndim : 0; }
+static inline size_t nc_tensor_shape(const nc_tensor* t, size_t dim) { return (t && dim < t->ndim) ? t->shape[dim] : 0; }
+static inline size_t nc_tensor_stride(const nc_tensor* t, size_t dim) { return (t && dim < t->ndim) ? t->strides[dim] : 0; }
+static inline nc_dtype nc_tensor_dtype(const nc_tensor* t) { return t ? t->dtype : NC_F32; }
+static inline bool nc_tensor_is_contiguous(const nc_tensor* t) { return t ? t->is_contiguous : false; }
+/* CPU pointer to element 0, or NULL while the tensor lives on the device */
+void* nc_tensor_data(const nc_tensor* t);
+#define nc_tensor_data_f32(t) ((float*)nc_tensor_data(t))
+#define nc_tensor_data_f64(t) ((double*)nc_tensor_data(t))
+#define nc_tensor_data_i32(t) ((int32_t*)nc_tensor_data(t))
+#define nc_tensor_data_i64(t) ((int64_t*)nc_tensor_data(t))
+static inline size_t nc_tensor_nbytes(const nc_tensor* t) { return t ? t->numel * nc_dtype_sizeof(t->dtype) : 0; }
+
+double nc_tensor_get_flat(const nc_tensor* t, size_t idx);
+void nc_tensor_set_flat(nc_tensor* t, size_t idx, double value);
+double nc_tensor_get(const nc_tensor* t, const size_t* indices);
+void nc_tensor_set(nc_tensor* t, const size_t* indices, double value);
+double nc_tensor_get1(const nc_tensor* t, size_t i);
+double nc_tensor_get2(const nc_tensor* t, size_t i, size_t j);
+double nc_tensor_get3(const nc_tensor* t, size_t i, size_t j, size_t k);
+double nc_tensor_get4(const nc_tensor* t, size_t i, size_t j, size_t k, size_t l);
+void nc_tensor_set1(nc_tensor* t, size_t i, double value);
+void nc_tensor_set2(nc_tensor* t, size_t i, size_t j, double value);
+void nc_tensor_set3(nc_tensor* t, size_t i, size_t j, size_t k, double value);
+void nc_tensor_set4(nc_tensor* t, size_t i, size_t j, size_t k, size_t l, double value);
+
+nc_tensor* nc_tensor_reshape(nc_tensor* t, const size_t* shape, size_t ndim);
+nc_tensor* nc_tensor_flatten(nc_tensor* t);
+nc_tensor* nc_tensor_transpose(nc_tensor* t, size_t dim0, size_t dim1);
+nc_tensor* nc_tensor_t(nc_tensor* t);
+nc_tensor* nc_tensor_contiguous(nc_tensor* t);
+void nc_tensor_requires_grad_(nc_tensor* t, bool requires_grad);
+nc_tensor* nc_tensor_detach(const nc_tensor* t);
+void nc_tensor_zero_grad_(nc_tensor* t);
+void nc_tensor_print(const nc_tensor* t);
+void nc_tensor_print_shape(const nc_tensor* t);
+bool nc_tensor_shape_eq(const nc_tensor* a, const nc_tensor* b);
+void nc_tensor_fill_(nc_tensor* t, double value);
+nc_error nc_tensor_copy_(nc_tensor* dst, const nc_tensor* src);
+void nc_tensor_to_device(nc_tensor* t, nc_device_type device);
+
+/* ------------------------------------------------------------------ autograd (autograd/node.h, backward.h) */
+#define NC_MAX_INPUTS 8
+/* receives the output gradient and the node's SAVED tensors; returns a nc_calloc'd array with one
+ * gradient per node INPUT (entries may be NULL); the engine frees the entries and the array */
+typedef nc_tensor** (*nc_backward_fn)(nc_tensor* grad_output, nc_tensor** saved, size_t n_saved);
+struct nc_node {
+    const char* op_name;
+    nc_backward_fn backward;
+    nc_tensor* inputs[NC_MAX_INPUTS];
+    size_t n_inputs;
+    nc_tensor* saved_tensors[NC_MAX_INPUTS];
+    bool saved_tensors_owned[NC_MAX_INPUTS];
+    size_t n_saved;
+    nc_tensor* output;
+    int visited;
+    int ref_count;
+    /* ---- fields beyond the reference layout ---- */
+    double params[8]; /* op hyper-parameters kept on the host (stride, padding, eps, ...) */
+};
+nc_node* nc_node_create(const char* op_name, nc_backward_fn backward);
+void nc_node_add_input(nc_node* node, nc_tensor* input);
+void nc_node_save_tensor(nc_node* node, nc_tensor* t);
+void nc_node_save_owned_tensor(nc_node* node, nc_tensor* t);
+void nc_node_free(nc_node* node);
+
+nc_error nc_backward(nc_tensor* t, nc_tensor* grad_output);
+nc_error nc_backward_scalar(nc_tensor* loss);
+nc_node** nc_build_topo(nc_tensor* t, size_t* n_nodes);
+typedef enum { NC_GRAD_REPLACE, NC_GRAD_ACCUMULATE } nc_grad_mode;
+void nc_set_grad_mode(nc_grad_mode mode);
+nc_grad_mode nc_get_grad_mode(void);
+typedef struct { int prev_enabled; } nc_no_grad_guard;
+nc_no_grad_guard nc_no_grad_begin(void);
+void nc_no_grad_end(nc_no_grad_guard* guard);
+int nc_grad_enabled(void);
+void nc_set_grad_enabled(int enabled);
+#define NC_NO_GRAD_BEGIN() nc_no_grad_guard _ng = nc_no_grad_begin()
+#define NC_NO_GRAD_END() nc_no_grad_end(&_ng)
+
+/* ------------------------------------------------------------------ ops (the ops headers) - the subset on the training path */
+nc_tensor* nc_add(nc_tensor* a, nc_tensor* b); /* same shape, or b broadcast over the last dim */
+nc_tensor* nc_sub(nc_tensor* a, nc_tensor* b);
+nc_tensor* nc_mul(nc_tensor* a, nc_tensor* b); /* same shape (e.g. a supplied dropout mask) */
+nc_tensor* nc_add_scalar(nc_tensor* a, double s);
+nc_tensor* nc_mul_scalar(nc_tensor* a, double s);
+void nc_add_(nc_tensor* a, nc_tensor* b);
+void nc_mul_scalar_(nc_tensor* a, double s);
+nc_tensor* nc_matmul(nc_tensor* a, nc_tensor* b); /* 2-D f32 */
+nc_tensor* nc_relu(nc_tensor* x);
+nc_tensor* nc_gelu(nc_tensor* x);
+nc_tensor* nc_softmax(nc_tensor* x, int dim);
+nc_tensor* nc_sum(nc_tensor* x, int axis, bool keepdim);
+nc_tensor* nc_sum_all(nc_tensor* x);
+nc_tensor* nc_mean_all(nc_tensor* x);
+nc_tensor* nc_argmax(nc_tensor* x, int axis, bool keepdim);
+nc_tensor* nc_mse_loss(nc_tensor* pred, nc_tensor* target);
+nc_tensor* nc_cross_entropy_loss(nc_tensor* logits, nc_tensor* targets);
+typedef enum { NC_REDUCTION_MEAN, NC_REDUCTION_SUM, NC_REDUCTION_NONE } nc_reduction;
+nc_tensor* nc_cross_entropy_loss_ex(nc_tensor* logits, nc_tensor* targets, nc_reduction reduction);
+
+/* ------------------------------------------------------------------ modules (nn/module.h) */
+#define NC_MAX_PARAMS 64
+#define NC_MAX_SUBMODULES 32
+#define NC_MAX_NAME_LEN 64
+typedef struct nc_module nc_module;
+typedef nc_tensor* (*nc_forward_fn)(nc_module* self, nc_tensor* input);
+struct nc_module {
+    char name[NC_MAX_NAME_LEN];
+    nc_tensor* params[NC_MAX_PARAMS];
+    char* param_names[NC_MAX_PARAMS];
+    size_t n_params;
+    nc_module* submodules[NC_MAX_SUBMODULES];
+    char* submodule_names[NC_MAX_SUBMODULES];
+    size_t n_submodules;
+    nc_forward_fn forward;
+    bool training;
+    void* extra;
+    void (*free_extra)(void*);
+};
+nc_module* nc_module_create(const char* name);
+void nc_module_free(nc_module* m);
+nc_tensor* nc_module_forward(nc_module* m, nc_tensor* input);
+void nc_module_add_param(nc_module* m, const char* name, nc_tensor* param);
+void nc_module_add_submodule(nc_module* m, const char* name, nc_module* sub);
+nc_tensor* nc_module_get_param(nc_module* m, const char* name);
+nc_module* nc_module_get_submodule(nc_module* m, const char* name);
+typedef void (*nc_param_callback)(const char* name, nc_tensor* param, void* ctx);
+void nc_module_parameters(nc_module* m, nc_param_callback cb, void* ctx);
+size_t nc_module_num_parameters(nc_module* m);
+void nc_module_train(nc_module* m, bool mode);
+static inline void nc_module_eval(nc_module* m) { nc_module_train(m, false); }
+static inline bool nc_module_is_training(nc_module* m) { return m ? m->training : false; }
+void nc_module_zero_grad(nc_module* m);
+void nc_module_requires_grad_(nc_module* m, bool requires_grad);
+void nc_module_print(nc_module* m);
+/* new: move every parameter (and its gradient) of the module tree */
+void nc_module_to_device(nc_module* m, nc_device_type device);
+
+/* ------------------------------------------------------------------ layers (nn/linear.h, conv.h, batchnorm.h, dropout.h) */
+nc_module* nc_linear(size_t in_features, size_t out_features, bool bias);
+nc_tensor* nc_linear_weight(nc_module* linear);
+nc_tensor* nc_linear_bias(nc_module* linear);
+nc_tensor* nc_linear_forward(nc_tensor* input, nc_tensor* weight, nc_tensor* bias);
+
+nc_module* nc_conv2d(size_t in_channels, size_t out_channels, size_t kernel_size, size_t stride, size_t padding, bool bias);
+nc_module* nc_conv2d_simple(size_t in_channels, size_t out_channels, size_t kernel_size);
+nc_tensor* nc_conv2d_weight(nc_module* conv);
+nc_tensor* nc_conv2d_bias(nc_module* conv);
+nc_tensor* nc_conv2d_forward(nc_tensor* input, nc_tensor* weight, nc_tensor* bias, size_t stride, size_t padding);
+nc_module* nc_maxpool2d(size_t kernel_size, size_t stride);
+nc_module* nc_maxpool2d_simple(size_t kernel_size);
+nc_tensor* nc_maxpool2d_forward(nc_tensor* input, size_t kernel_size, size_t stride);
+static inline size_t nc_conv_output_size(size_t input_size, size_t kernel_size, size_t stride, size_t padding) {
+    return (input_size + 2 * padding - kernel_size) / stride + 1;
+}
+nc_module* nc_flatten(void);
+/* new: the functional form behind nc_flatten: (N, ...) -> (N, rest), differentiable */
+nc_tensor* nc_flatten_forward(nc_tensor* input);
+
+typedef struct {
+    size_t num_features;
+    double eps;
+    double momentum;
+    bool affine;
+    bool track_running_stats;
+} nc_batchnorm2d_config;
+static const nc_batchnorm2d_config NC_BATCHNORM2D_DEFAULT = {0, 1e-5, 0.1, true, true};
+nc_module* nc_batchnorm2d(size_t num_features);
+nc_module* nc_batchnorm2d_ex(nc_batchnorm2d_config config);
+nc_tensor* nc_batchnorm2d_weight(nc_module* bn);
+nc_tensor* nc_batchnorm2d_bias(nc_module* bn);
+nc_tensor* nc_batchnorm2d_running_mean(nc_module* bn);
+nc_tensor* nc_batchnorm2d_running_var(nc_module* bn);
+nc_tensor* nc_batchnorm2d_forward_fn(nc_tensor* input, nc_tensor* running_mean, nc_tensor* running_var,
+                                     nc_tensor* weight, nc_tensor* bias, bool training, double momentum, double eps);
+typedef struct {
+    size_t* normalized_shape;
+    size_t normalized_ndim;
+    double eps;
+    bool elementwise_affine;
+} nc_layernorm_config;
+nc_module* nc_layernorm(const size_t* normalized_shape, size_t ndim);
+nc_module* nc_layernorm_ex(nc_layernorm_config config);
+nc_tensor* nc_layernorm_forward_fn(nc_tensor* input, const size_t* normalized_shape, size_t normalized_ndim,
+                                   nc_tensor* weight, nc_tensor* bias, double eps);
+/* new: dropout with a caller-supplied keep mask already scaled by 1/(1-p): y = x * mask */
+nc_tensor* nc_dropout_mask_fn(nc_tensor* x, nc_tensor* mask);
+
+/* ------------------------------------------------------------------ optimizers (the optim headers) */
+#define NC_MAX_OPTIM_PARAMS 256
+typedef struct nc_optimizer nc_optimizer;
+typedef void (*nc_optim_step_fn)(nc_optimizer* self);
+struct nc_optimizer {
+    nc_tensor* params[NC_MAX_OPTIM_PARAMS];
+    size_t n_params;
+    double lr;
+    nc_optim_step_fn step;
+    void* state;
+    void (*free_state)(void*);
+    size_t t;
+};
+void nc_optimizer_free(nc_optimizer* opt);
+void nc_optimizer_step(nc_optimizer* opt);
+void nc_optimizer_zero_grad(nc_optimizer* opt);
+void nc_optimizer_set_lr(nc_optimizer* opt, double lr);
+double nc_optimizer_get_lr(nc_optimizer* opt);
+void nc_optimizer_add_module(nc_optimizer* opt, nc_module* m);
+void nc_optimizer_add_param(nc_optimizer* opt, nc_tensor* param);
+/* new: gradients are multiplied by this before the update (1/world_size under data parallel) */
+void nc_optimizer_set_grad_scale(nc_optimizer* opt, double scale);
+
+typedef struct {
+    double momentum;
+    double dampening;
+    double weight_decay;
+    bool nesterov;
+} nc_sgd_config;
+static const nc_sgd_config NC_SGD_DEFAULT = {0.0, 0.0, 0.0, false};
+nc_optimizer* nc_sgd(double lr, nc_sgd_config config);
+nc_optimizer* nc_sgd_from_module(nc_module* m, double lr, nc_sgd_config config);
+nc_optimizer* nc_sgd_simple(nc_module* m, double lr);
+nc_optimizer* nc_sgd_momentum(nc_module* m, double lr, double momentum);
+
+typedef struct {
+    double beta1;
+    double beta2;
+    double eps;
+    double weight_decay;
+    bool amsgrad;
+} nc_adam_config;
+static const nc_adam_config NC_ADAM_DEFAULT = {0.9, 0.999, 1e-8, 0.0, false};
+nc_optimizer* nc_adam(double lr, nc_adam_config config);
+nc_optimizer* nc_adam_from_module(nc_module* m, double lr, nc_adam_config config);
+nc_optimizer* nc_adam_default(nc_module* m, double lr);
+nc_optimizer* nc_adamw(nc_module* m, double lr, double weight_decay);
+
+/* ------------------------------------------------------------------ library init (nocta.h:60-74) */
+void nc_init(void);    /* brings up the CUDA backend and makes it the default device */
+void nc_cleanup(void); /* frees pools and library scratch */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NOCTA_B200_NOCTA_H */

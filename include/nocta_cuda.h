@@ -74,6 +74,11 @@ void  nc_cuda_clear_status(void);
 /* new: math mode for contractions (NC_CUDA_MATH_*); returns the previous mode */
 int   nc_cuda_set_math_mode(int mode);
 int   nc_cuda_get_math_mode(void);
+/* new: operand conditioning for NC_CUDA_MATH_TF32.  While on, the activation / gradient kernels (relu, gelu,
+ * add/sub/mul, bias add, batchnorm, layernorm, loss gradients and their backward forms) round each value
+ * they store to the nearest TF32 number, which removes the truncation bias of a tensor-core contraction
+ * that reads it next.  Off by default (plain f32 results).  Returns the previous setting. */
+int   nc_cuda_set_round_outputs(int on);
 /* new: reads and clears the device-side error word set when a bounded in-kernel wait expires */
 unsigned int nc_cuda_device_error_word(void);
 /* new: number of kernels this library has launched since the last reset (bookkeeping for benches) */

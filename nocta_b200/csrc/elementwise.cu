@@ -14,9 +14,10 @@ constexpr int kThreads = 256;
 
 __device__ __forceinline__ float4 ld4(const float* p, size_t i) { return reinterpret_cast<const float4*>(p)[i]; }
 __device__ __forceinline__ void st4(float* p, size_t i, float4 v) { reinterpret_cast<float4*>(p)[i] = v; }
+__device__ __forceinline__ float4 rnd4(float4 v) { return make_float4(round_tf32(v.x), round_tf32(v.y), round_tf32(v.z), round_tf32(v.w)); }
 
 // out[i] = f(a[i], b[i]); b may be null when NIN == 1; NIN == 0 means no input at all.
-template <int NIN, class F>
+template <int NIN, bool RND, class F>
 __global__ void __launch_bounds__(kThreads) ew_kernel(float* __restrict__ out, const float* __restrict__ a,
                                                       const float* __restrict__ b, size_t n4, size_t n, F f) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -30,6 +31,7 @@ __global__ void __launch_bounds__(kThreads) ew_kernel(float* __restrict__ out, c
         float4 r0, r1;
         r0.x = f(a0.x, b0.x); r0.y = f(a0.y, b0.y); r0.z = f(a0.z, b0.z); r0.w = f(a0.w, b0.w);
         r1.x = f(a1.x, b1.x); r1.y = f(a1.y, b1.y); r1.z = f(a1.z, b1.z); r1.w = f(a1.w, b1.w);
+        if (RND) { r0 = rnd4(r0); r1 = rnd4(r1); }
         st4(out, i, r0);
         st4(out, i + stride, r1);
     }
@@ -39,24 +41,28 @@ __global__ void __launch_bounds__(kThreads) ew_kernel(float* __restrict__ out, c
         if (NIN >= 2) b0 = ld4(b, i);
         float4 r0;
         r0.x = f(a0.x, b0.x); r0.y = f(a0.y, b0.y); r0.z = f(a0.z, b0.z); r0.w = f(a0.w, b0.w);
+        if (RND) r0 = rnd4(r0);
         st4(out, i, r0);
     }
     for (size_t j = n4 * 4 + t0; j < n; j += stride) {
         float av = NIN >= 1 ? a[j] : 0.f, bv = NIN >= 2 ? b[j] : 0.f;
-        out[j] = f(av, bv);
+        float r = f(av, bv);
+        out[j] = RND ? round_tf32(r) : r;
     }
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// rnd: round results to TF32 (activations / gradients in plain TF32 mode); never for fill / copy
 template <int NIN, class F>
-int launch_ew(float* out, const float* a, const float* b, size_t n, cudaStream_t st, F f, const char* what) {
+int launch_ew(float* out, const float* a, const float* b, size_t n, cudaStream_t st, F f, const char* what, bool rnd = false) {
     if (n == 0) return NC_CUDA_OK;
     NCC_REQUIRE(out && (NIN < 1 || a) && (NIN < 2 || b), "%s: null pointer", what);
     bool vec = aligned16(out) && (NIN < 1 || aligned16(a)) && (NIN < 2 || aligned16(b));
     size_t n4 = vec ? n / 4 : 0;
     int grid = grid_for((long long)(vec ? (n + 3) / 4 : n), kThreads, 8);
-    ew_kernel<NIN, F><<<grid, kThreads, 0, st>>>(out, a, b, n4, n, f);
+    if (rnd) ew_kernel<NIN, true, F><<<grid, kThreads, 0, st>>>(out, a, b, n4, n, f);
+    else ew_kernel<NIN, false, F><<<grid, kThreads, 0, st>>>(out, a, b, n4, n, f);
     NCC_COUNT_LAUNCH();
     return launch_status(what);
 }
@@ -93,10 +99,12 @@ struct GeluBwdF { __device__ float operator()(float dy, float x) const { return 
 
 // out[i] = a[i] + b[i % inner]
 __global__ void __launch_bounds__(kThreads) bias_rows_kernel(float* __restrict__ out, const float* __restrict__ a,
-                                                             const float* __restrict__ b, size_t total, int inner) {
+                                                             const float* __restrict__ b, size_t total, int inner, int rnd) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride)
-        out[i] = a[i] + b[i % (size_t)inner];
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        float r = a[i] + b[i % (size_t)inner];
+        out[i] = rnd ? round_tf32(r) : r;
+    }
 }
 
 // One warp per row; columns strided over lanes.  Max-subtracted exponentials, f32.
@@ -182,20 +190,20 @@ int nc_cuda_copy_f32_ex(float* dst, const float* src, size_t n, void* stream) {
 int nc_cuda_binary_f32_ex(int op, float* out, const float* a, const float* b, size_t n, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     switch (op) {
-        case 0: return launch_ew<2>(out, a, b, n, st, AddF{}, "add");
-        case 1: return launch_ew<2>(out, a, b, n, st, SubF{}, "sub");
-        case 2: return launch_ew<2>(out, a, b, n, st, MulF{}, "mul");
-        case 3: return launch_ew<2>(out, a, b, n, st, DivF{}, "div");
+        case 0: return launch_ew<2>(out, a, b, n, st, AddF{}, "add", round_outputs());
+        case 1: return launch_ew<2>(out, a, b, n, st, SubF{}, "sub", round_outputs());
+        case 2: return launch_ew<2>(out, a, b, n, st, MulF{}, "mul", round_outputs());
+        case 3: return launch_ew<2>(out, a, b, n, st, DivF{}, "div", round_outputs());
     }
     return set_status(NC_CUDA_ERR_ARG, "binary: unknown op %d", op);
 }
 int nc_cuda_scalar_f32_ex(int op, float* out, const float* a, float s, size_t n, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     switch (op) {
-        case 0: return launch_ew<1>(out, a, nullptr, n, st, AddSF{s}, "add_scalar");
-        case 1: return launch_ew<1>(out, a, nullptr, n, st, SubSF{s}, "sub_scalar");
-        case 2: return launch_ew<1>(out, a, nullptr, n, st, MulSF{s}, "mul_scalar");
-        case 3: return launch_ew<1>(out, a, nullptr, n, st, DivSF{s}, "div_scalar");
+        case 0: return launch_ew<1>(out, a, nullptr, n, st, AddSF{s}, "add_scalar", round_outputs());
+        case 1: return launch_ew<1>(out, a, nullptr, n, st, SubSF{s}, "sub_scalar", round_outputs());
+        case 2: return launch_ew<1>(out, a, nullptr, n, st, MulSF{s}, "mul_scalar", round_outputs());
+        case 3: return launch_ew<1>(out, a, nullptr, n, st, DivSF{s}, "div_scalar", round_outputs());
     }
     return set_status(NC_CUDA_ERR_ARG, "scalar: unknown op %d", op);
 }
@@ -203,7 +211,7 @@ int nc_cuda_add_broadcast_batch_f32_ex(float* out, const float* a, const float* 
                                        void* stream) {
     if (total == 0) return NC_CUDA_OK;
     NCC_REQUIRE(out && a && b && inner > 0, "add_broadcast: bad argument");
-    bias_rows_kernel<<<grid_for((long long)total, kThreads), kThreads, 0, (cudaStream_t)stream>>>(out, a, b, total, inner);
+    bias_rows_kernel<<<grid_for((long long)total, kThreads), kThreads, 0, (cudaStream_t)stream>>>(out, a, b, total, inner, round_outputs() ? 1 : 0);
     NCC_COUNT_LAUNCH();
     return launch_status("add_broadcast");
 }
@@ -237,16 +245,16 @@ int nc_cuda_round_tf32_f32_ex(float* dst, const float* src, size_t n, void* stre
     return launch_ew<1>(dst, src, nullptr, n, (cudaStream_t)stream, RoundF{}, "round_tf32");
 }
 int nc_cuda_relu_f32_ex(float* out, const float* in, size_t n, void* stream) {
-    return launch_ew<1>(out, in, nullptr, n, (cudaStream_t)stream, ReluF{}, "relu");
+    return launch_ew<1>(out, in, nullptr, n, (cudaStream_t)stream, ReluF{}, "relu", round_outputs());
 }
 int nc_cuda_relu_backward_f32_ex(float* gi, const float* go, const float* input, size_t n, void* stream) {
-    return launch_ew<2>(gi, go, input, n, (cudaStream_t)stream, ReluBwdF{}, "relu_backward");
+    return launch_ew<2>(gi, go, input, n, (cudaStream_t)stream, ReluBwdF{}, "relu_backward", round_outputs());
 }
 int nc_cuda_gelu_f32_ex(float* out, const float* in, size_t n, void* stream) {
-    return launch_ew<1>(out, in, nullptr, n, (cudaStream_t)stream, GeluF{}, "gelu");
+    return launch_ew<1>(out, in, nullptr, n, (cudaStream_t)stream, GeluF{}, "gelu", round_outputs());
 }
 int nc_cuda_gelu_backward_f32_ex(float* gi, const float* go, const float* input, size_t n, void* stream) {
-    return launch_ew<2>(gi, go, input, n, (cudaStream_t)stream, GeluBwdF{}, "gelu_backward");
+    return launch_ew<2>(gi, go, input, n, (cudaStream_t)stream, GeluBwdF{}, "gelu_backward", round_outputs());
 }
 int nc_cuda_softmax_f32_ex(float* out, const float* in, size_t batch, size_t dim, void* stream) {
     if (batch == 0 || dim == 0) return NC_CUDA_OK;

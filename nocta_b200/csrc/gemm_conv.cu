@@ -225,6 +225,17 @@ void nhwc_strides(size_t s[4], int C, int H, int W) {
     s[0] = (size_t)H * W * C; s[1] = 1; s[2] = (size_t)W * C; s[3] = (size_t)C;
 }
 
+// Parameters keep their full f32 value in memory; in plain TF32 mode the Linear GEMMs read a copy
+// rounded to the nearest TF32 value (library scratch) so that the tensor core's truncation of its
+// operands is exact.  Skipped when the GEMM will run on the FP32 SIMT kernel anyway (fewer than 128 rows).
+const float* conditioned_weight(const float* W, size_t n, int rows, cudaStream_t st) {
+    if (math_mode() != NC_CUDA_MATH_TF32 || rows < 128) return W;
+    float* Wr = (float*)scratch(3, sizeof(float) * n, st);
+    if (!Wr) return nullptr;
+    if (nc_cuda_round_tf32_f32_ex(Wr, W, n, st)) return nullptr;
+    return Wr;
+}
+
 }  // namespace
 
 extern "C" {
@@ -244,8 +255,10 @@ void nc_cuda_matmul_f32(float* C, const float* A, const float* B, int M, int N, 
 int nc_cuda_linear_forward_f32_ex(float* y, const float* x, const float* W, const float* bias, int batch, int in_f,
                                   int out_f, void* stream) {
     NCC_REQUIRE(y && x && W && batch > 0 && in_f > 0 && out_f > 0, "linear_forward: bad argument");
+    const float* Wc = conditioned_weight(W, (size_t)out_f * in_f, batch, (cudaStream_t)stream);
+    if (!Wc) return NC_CUDA_ERR_RUNTIME;
     // y(B,out) = x(B,in) * W(out,in)^T : both operands K-major
-    return gemm_dispatch(y, out_f, x, in_f, false, W, in_f, false, batch, out_f, in_f, bias, 1.f, 0.f, (cudaStream_t)stream);
+    return gemm_dispatch(y, out_f, x, in_f, false, Wc, in_f, false, batch, out_f, in_f, bias, 1.f, 0.f, (cudaStream_t)stream);
 }
 
 int nc_cuda_linear_backward_f32_ex(float* dx, float* dW, float* db, const float* dy, const float* x, const float* W,
@@ -255,8 +268,10 @@ int nc_cuda_linear_backward_f32_ex(float* dx, float* dW, float* db, const float*
     int rc;
     if (dx) {
         NCC_REQUIRE(W, "linear_backward: dx needs W");
+        const float* Wc = conditioned_weight(W, (size_t)out_f * in_f, batch, st);
+        if (!Wc) return NC_CUDA_ERR_RUNTIME;
         // dx(B,in) = dy(B,out) * W(out,in): A K-major (k = out), B stored (K = out, N = in) -> MN-major
-        rc = gemm_dispatch(dx, in_f, dy, out_f, false, W, in_f, true, batch, in_f, out_f, nullptr, 1.f, 0.f, st);
+        rc = gemm_dispatch(dx, in_f, dy, out_f, false, Wc, in_f, true, batch, in_f, out_f, nullptr, 1.f, 0.f, st);
         if (rc) return rc;
     }
     if (dW) {

@@ -22,7 +22,7 @@ __global__ void __launch_bounds__(kThreads) ce_fused_kernel(float* __restrict__ 
                                                             const float* __restrict__ logits,
                                                             const int64_t* __restrict__ targets, int N, int C,
                                                             float gscale, double* __restrict__ partial,
-                                                            unsigned int* __restrict__ ticket) {
+                                                            unsigned int* __restrict__ ticket, int rnd) {
     __shared__ double sh[32];
     __shared__ bool last;
     const int lane = threadIdx.x & 31;
@@ -48,7 +48,8 @@ __global__ void __launch_bounds__(kThreads) ce_fused_kernel(float* __restrict__ 
             for (int c = lane; c < C; c += 32) {
                 float p = expf(x[c] - m) * inv;
                 if (valid && c == lab) p -= 1.f;
-                g[c] = p * gscale;
+                float o = p * gscale;
+                g[c] = rnd ? round_tf32(o) : o;
             }
         }
     }
@@ -73,7 +74,7 @@ __global__ void __launch_bounds__(kThreads) mse_fused_kernel(float* __restrict__
                                                              float* __restrict__ gt, const float* __restrict__ p,
                                                              const float* __restrict__ t, size_t n, double gscale,
                                                              double* __restrict__ partial,
-                                                             unsigned int* __restrict__ ticket) {
+                                                             unsigned int* __restrict__ ticket, int rnd) {
     __shared__ double sh[32];
     __shared__ bool last;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -82,6 +83,7 @@ __global__ void __launch_bounds__(kThreads) mse_fused_kernel(float* __restrict__
         float d = p[i] - t[i];
         acc += (double)d * (double)d;
         float g = (float)(gscale * (double)d);
+        if (rnd) g = round_tf32(g);
         if (gp) gp[i] = g;
         if (gt) gt[i] = -g;
     }
@@ -255,7 +257,7 @@ int nc_cuda_cross_entropy_fused_f32_ex(float* loss, float* grad, const float* lo
     int rc = loss_scratch(&ls, (long long)N * 32, st);
     if (rc) return rc;
     ce_fused_kernel<<<ls.blocks, kThreads, 0, st>>>(loss, grad, logits, targets, N, C, grad_scale / (float)N,
-                                                    ls.partial, ls.ticket);
+                                                    ls.partial, ls.ticket, round_outputs() ? 1 : 0);
     NCC_COUNT_LAUNCH();
     return launch_status("cross_entropy");
 }
@@ -268,7 +270,7 @@ int nc_cuda_mse_fused_f32_ex(float* loss, float* gp, float* gt, const float* pre
     int rc = loss_scratch(&ls, (long long)n, st);
     if (rc) return rc;
     mse_fused_kernel<<<ls.blocks, kThreads, 0, st>>>(loss, gp, gt, pred, target, n,
-                                                     2.0 * (double)grad_scale / (double)n, ls.partial, ls.ticket);
+                                                     2.0 * (double)grad_scale / (double)n, ls.partial, ls.ticket, round_outputs() ? 1 : 0);
     NCC_COUNT_LAUNCH();
     return launch_status("mse");
 }

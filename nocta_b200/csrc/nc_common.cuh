@@ -38,6 +38,13 @@ int sm_count();
 // NC_CUDA_MATH_* mode selected with nc_cuda_set_math_mode.
 int math_mode();
 
+// When switched on (nc_cuda_set_round_outputs), the activation / gradient kernels round what they
+// write to the nearest TF32 value, so a tensor-core contraction that consumes it (and drops the low
+// 13 mantissa bits of its operands) reads exactly representable data and its error stays zero-mean.
+// Costs one cvt per element in kernels that wait on memory.  Off by default: results are plain f32.
+bool round_outputs();
+int set_round_outputs(int on);
+
 // Number of kernels launched by this library (bench bookkeeping).
 extern unsigned long long g_launches;
 #define NCC_COUNT_LAUNCH() (++ncc::g_launches)

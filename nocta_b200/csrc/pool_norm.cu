@@ -328,7 +328,7 @@ template <int LAYOUT, int VEC>
 __global__ void __launch_bounds__(kThreads) bn_apply_kernel(float* __restrict__ y, const float* __restrict__ x,
                                                             const float* __restrict__ gamma, const float* __restrict__ beta,
                                                             const float* __restrict__ mean, const float* __restrict__ var,
-                                                            float eps, int C, int spatial, size_t nvec, int relu) {
+                                                            float eps, int C, int spatial, size_t nvec, int relu, int rnd) {
     const size_t gstride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += gstride) {
         const size_t e = i * VEC;
@@ -343,7 +343,8 @@ __global__ void __launch_bounds__(kThreads) bn_apply_kernel(float* __restrict__ 
             float is = rsqrtf(var[c] + eps);
             float g = gamma ? gamma[c] : 1.f, b = beta ? beta[c] : 0.f;
             float o = g * ((xv[v] - mean[c]) * is) + b;
-            out[v] = (relu && !(o > 0.f)) ? 0.f : o;
+            o = (relu && !(o > 0.f)) ? 0.f : o;
+            out[v] = rnd ? round_tf32(o) : o;
         }
         if (VEC == 4) *reinterpret_cast<float4*>(y + e) = make_float4(out[0], out[1 % VEC], out[2 % VEC], out[3 % VEC]);
         else y[e] = out[0];
@@ -371,7 +372,7 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_apply_kernel(float* __restric
                                                                 const float* __restrict__ x, const float* __restrict__ yrelu,
                                                                 const float* __restrict__ gamma, const float* __restrict__ mean,
                                                                 const float* __restrict__ var, const float* __restrict__ sums,
-                                                                float eps, float Mf, int C, int spatial, size_t nvec) {
+                                                                float eps, float Mf, int C, int spatial, size_t nvec, int rnd) {
     const size_t gstride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += gstride) {
         const size_t e = i * VEC;
@@ -397,7 +398,8 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_apply_kernel(float* __restric
             if (yrelu && !(yv[v] > 0.f)) g = 0.f;
             float xh = (xv[v] - mean[c]) * is;
             float coeff = (gamma ? gamma[c] : 1.f) * is / Mf;
-            out[v] = coeff * (Mf * g - sums[2 * c] - xh * sums[2 * c + 1]);
+            float o = coeff * (Mf * g - sums[2 * c] - xh * sums[2 * c + 1]);
+            out[v] = rnd ? round_tf32(o) : o;
         }
         if (VEC == 4) *reinterpret_cast<float4*>(dx + e) = make_float4(out[0], out[1 % VEC], out[2 % VEC], out[3 % VEC]);
         else dx[e] = out[0];
@@ -442,7 +444,7 @@ int channel_reduce(double** partial_out, int* slabs_out, int N, int C, int spati
 // =============================================================================================
 __global__ void __launch_bounds__(kThreads) ln_fwd_kernel(float* __restrict__ y, const float* __restrict__ x,
                                                           const float* __restrict__ gamma, const float* __restrict__ beta,
-                                                          size_t rows, int cols, float eps) {
+                                                          size_t rows, int cols, float eps, int rnd) {
     const int lane = threadIdx.x & 31;
     const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
     for (size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
@@ -458,7 +460,8 @@ __global__ void __launch_bounds__(kThreads) ln_fwd_kernel(float* __restrict__ y,
         const float inv = (float)(1.0 / sqrt(q / cols + (double)eps));
         for (int c = lane; c < cols; c += 32) {
             float g = gamma ? gamma[c] : 1.f, b = beta ? beta[c] : 0.f;
-            yr[c] = g * ((xr[c] - mean) * inv) + b;
+            float o = g * ((xr[c] - mean) * inv) + b;
+            yr[c] = rnd ? round_tf32(o) : o;
         }
     }
 }
@@ -467,7 +470,7 @@ __global__ void __launch_bounds__(kThreads) ln_fwd_kernel(float* __restrict__ y,
 __global__ void __launch_bounds__(kThreads) ln_bwd_rows_kernel(float* __restrict__ dx, float2* __restrict__ stats,
                                                                const float* __restrict__ dy, const float* __restrict__ x,
                                                                const float* __restrict__ gamma, size_t rows, int cols,
-                                                               float eps) {
+                                                               float eps, int rnd) {
     const int lane = threadIdx.x & 31;
     const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
     for (size_t r = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
@@ -494,7 +497,8 @@ __global__ void __launch_bounds__(kThreads) ln_bwd_rows_kernel(float* __restrict
         for (int c = lane; c < cols; c += 32) {
             float gg = gr[c] * (gamma ? gamma[c] : 1.f);
             float xh = (xr[c] - mean) * inv;
-            dx[r * cols + c] = coeff * (D * gg - fsg - xh * fsgx);
+            float o = coeff * (D * gg - fsg - xh * fsgx);
+            dx[r * cols + c] = rnd ? round_tf32(o) : o;
         }
         if (lane == 0 && stats) stats[r] = make_float2(mean, inv);
     }
@@ -598,11 +602,11 @@ int nc_cuda_batchnorm_forward_f32_ex(float* y, const float* x, const float* gamm
     const int grid = grid_for((long long)nvec, kThreads);
     const float fe = (float)eps;
     if (layout == 0) {
-        if (vec) bn_apply_kernel<0, 4><<<grid, kThreads, 0, st>>>(y, x, gamma, beta, save_mean, save_var, fe, C, spatial, nvec, relu);
-        else bn_apply_kernel<0, 1><<<grid, kThreads, 0, st>>>(y, x, gamma, beta, save_mean, save_var, fe, C, spatial, nvec, relu);
+        if (vec) bn_apply_kernel<0, 4><<<grid, kThreads, 0, st>>>(y, x, gamma, beta, save_mean, save_var, fe, C, spatial, nvec, relu, round_outputs() ? 1 : 0);
+        else bn_apply_kernel<0, 1><<<grid, kThreads, 0, st>>>(y, x, gamma, beta, save_mean, save_var, fe, C, spatial, nvec, relu, round_outputs() ? 1 : 0);
     } else {
-        if (vec) bn_apply_kernel<1, 4><<<grid, kThreads, 0, st>>>(y, x, gamma, beta, save_mean, save_var, fe, C, spatial, nvec, relu);
-        else bn_apply_kernel<1, 1><<<grid, kThreads, 0, st>>>(y, x, gamma, beta, save_mean, save_var, fe, C, spatial, nvec, relu);
+        if (vec) bn_apply_kernel<1, 4><<<grid, kThreads, 0, st>>>(y, x, gamma, beta, save_mean, save_var, fe, C, spatial, nvec, relu, round_outputs() ? 1 : 0);
+        else bn_apply_kernel<1, 1><<<grid, kThreads, 0, st>>>(y, x, gamma, beta, save_mean, save_var, fe, C, spatial, nvec, relu, round_outputs() ? 1 : 0);
     }
     NCC_COUNT_LAUNCH();
     return launch_status("batchnorm_forward");
@@ -633,11 +637,11 @@ int nc_cuda_batchnorm_backward_f32_ex(float* dx, float* dgamma, float* dbeta, co
     const int grid = grid_for((long long)nvec, kThreads);
     const float Mf = (float)((double)N * spatial);
     if (layout == 0) {
-        if (vec) bn_bwd_apply_kernel<0, 4><<<grid, kThreads, 0, st>>>(dx, dy, x, relu_out, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec);
-        else bn_bwd_apply_kernel<0, 1><<<grid, kThreads, 0, st>>>(dx, dy, x, relu_out, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec);
+        if (vec) bn_bwd_apply_kernel<0, 4><<<grid, kThreads, 0, st>>>(dx, dy, x, relu_out, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec, round_outputs() ? 1 : 0);
+        else bn_bwd_apply_kernel<0, 1><<<grid, kThreads, 0, st>>>(dx, dy, x, relu_out, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec, round_outputs() ? 1 : 0);
     } else {
-        if (vec) bn_bwd_apply_kernel<1, 4><<<grid, kThreads, 0, st>>>(dx, dy, x, relu_out, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec);
-        else bn_bwd_apply_kernel<1, 1><<<grid, kThreads, 0, st>>>(dx, dy, x, relu_out, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec);
+        if (vec) bn_bwd_apply_kernel<1, 4><<<grid, kThreads, 0, st>>>(dx, dy, x, relu_out, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec, round_outputs() ? 1 : 0);
+        else bn_bwd_apply_kernel<1, 1><<<grid, kThreads, 0, st>>>(dx, dy, x, relu_out, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec, round_outputs() ? 1 : 0);
     }
     NCC_COUNT_LAUNCH();
     return launch_status("batchnorm_backward");
@@ -660,7 +664,7 @@ int nc_cuda_layernorm_forward_f32_ex(float* y, const float* x, const float* gamm
                                      size_t cols, double eps, void* stream) {
     if (rows == 0 || cols == 0) return NC_CUDA_OK;
     NCC_REQUIRE(y && x && cols <= 0x7fffffff, "layernorm_forward: bad argument");
-    ln_fwd_kernel<<<grid_for((long long)rows * 32, kThreads), kThreads, 0, (cudaStream_t)stream>>>(y, x, gamma, beta, rows, (int)cols, (float)eps);
+    ln_fwd_kernel<<<grid_for((long long)rows * 32, kThreads), kThreads, 0, (cudaStream_t)stream>>>(y, x, gamma, beta, rows, (int)cols, (float)eps, round_outputs() ? 1 : 0);
     NCC_COUNT_LAUNCH();
     return launch_status("layernorm_forward");
 }
@@ -676,7 +680,7 @@ int nc_cuda_layernorm_backward_f32_ex(float* dx, float* dgamma, float* dbeta, co
         stats = (float2*)scratch(6, sizeof(float2) * rows, st);
         if (!stats) return NC_CUDA_ERR_RUNTIME;
     }
-    ln_bwd_rows_kernel<<<grid_for((long long)rows * 32, kThreads), kThreads, 0, st>>>(dx, stats, dy, x, gamma, rows, (int)cols, (float)eps);
+    ln_bwd_rows_kernel<<<grid_for((long long)rows * 32, kThreads), kThreads, 0, st>>>(dx, stats, dy, x, gamma, rows, (int)cols, (float)eps, round_outputs() ? 1 : 0);
     NCC_COUNT_LAUNCH();
     if (params) {
         int C = (int)cols;

@@ -32,6 +32,9 @@ int last_status() { return g_status; }
 const char* last_message() { return g_message; }
 cudaStream_t current_stream() { return g_stream; }
 int math_mode() { return g_math_mode; }
+static int g_round_outputs = 0;
+bool round_outputs() { return g_round_outputs != 0; }
+int set_round_outputs(int on) { int p = g_round_outputs; g_round_outputs = on ? 1 : 0; return p; }
 
 int sm_count() {
     if (g_sm_count == 0) {
@@ -209,6 +212,7 @@ int nc_cuda_set_math_mode(int mode) {
     return prev;
 }
 int nc_cuda_get_math_mode(void) { return g_math_mode; }
+int nc_cuda_set_round_outputs(int on) { return ncc::set_round_outputs(on); }
 unsigned int nc_cuda_device_error_word(void) {
     unsigned int* w = device_error_word();
     unsigned int h = 0;

@@ -1,0 +1,139 @@
+/*
+ * Optimizers: SGD (momentum, dampening, Nesterov, L2) and Adam / AdamW / AMSGrad.  The update of
+ * one parameter tensor is one fused kernel that also applies the gradient scale (1/world under
+ * data parallel).  Rules follow the reference CPU path (src/optim/optimizer.c:3-51,
+ * src/optim/sgd.c:13-171, src/optim/adam.c:11-131): the step counter t is per optimizer; SGD uses
+ * v = g on the very first step (t == 0) and increments t after the sweep; Adam increments t first
+ * and derives the bias corrections from it in double on the host.
+ */
+#include "internal.h"
+#include <math.h>
+
+typedef struct { double grad_scale; } opt_common;
+typedef struct { opt_common c; nc_sgd_config cfg; nc_tensor* velocity[NC_MAX_OPTIM_PARAMS]; } sgd_state;
+typedef struct { opt_common c; nc_adam_config cfg; nc_tensor* m[NC_MAX_OPTIM_PARAMS]; nc_tensor* v[NC_MAX_OPTIM_PARAMS]; nc_tensor* vmax[NC_MAX_OPTIM_PARAMS]; } adam_state;
+
+void nc_optimizer_free(nc_optimizer* opt) {
+    if (!opt) return;
+    if (opt->state && opt->free_state) opt->free_state(opt->state);
+    nc_free(opt);
+}
+void nc_optimizer_step(nc_optimizer* opt) { if (opt && opt->step) opt->step(opt); }
+void nc_optimizer_zero_grad(nc_optimizer* opt) {
+    if (!opt) return;
+    for (size_t i = 0; i < opt->n_params; i++) nc_tensor_zero_grad_(opt->params[i]);
+}
+void nc_optimizer_set_lr(nc_optimizer* opt, double lr) { if (opt) opt->lr = lr; }
+double nc_optimizer_get_lr(nc_optimizer* opt) { return opt ? opt->lr : 0.0; }
+void nc_optimizer_add_param(nc_optimizer* opt, nc_tensor* param) {
+    if (!opt || !param || opt->n_params >= NC_MAX_OPTIM_PARAMS) return;
+    opt->params[opt->n_params++] = param;
+}
+static void cb_add(const char* name, nc_tensor* p, void* ctx) { (void)name; nc_optimizer_add_param(ctx, p); }
+void nc_optimizer_add_module(nc_optimizer* opt, nc_module* m) { if (opt && m) nc_module_parameters(m, cb_add, opt); }
+void nc_optimizer_set_grad_scale(nc_optimizer* opt, double scale) { if (opt && opt->state) ((opt_common*)opt->state)->grad_scale = scale; }
+
+static nc_tensor* state_like(const nc_tensor* p) {
+    nc_tensor* s = nci_empty_on(p->shape, p->ndim, p->dtype, p->storage->device);
+    if (s) nc_tensor_fill_(s, 0.0);
+    return s;
+}
+static bool param_ready(const nc_tensor* p, const char* who) {
+    if (!p->grad) return false;
+    if (!nci_need_cuda_f32(p, who) || !nci_need_cuda_f32(p->grad, who)) return false;
+    if (!p->is_contiguous || !p->grad->is_contiguous) { NC_SET_ERROR(NC_ERR_NOT_CONTIGUOUS, "%s: parameters must be contiguous", who); return false; }
+    return true;
+}
+
+/* ------------------------------------------------------------------ SGD */
+static void sgd_step(nc_optimizer* self) {
+    sgd_state* st = self->state;
+    for (size_t i = 0; i < self->n_params; i++) {
+        nc_tensor* p = self->params[i];
+        if (!param_ready(p, "sgd")) continue;
+        float* vel = NULL;
+        if (st->cfg.momentum != 0.0) {
+            if (!st->velocity[i]) st->velocity[i] = state_like(p);
+            if (!st->velocity[i]) continue;
+            vel = nci_fptr(st->velocity[i]);
+        }
+        nci_ok(nc_cuda_sgd_update_f32_ex(nci_fptr(p), vel, nci_fptr(p->grad), self->lr, st->cfg.momentum, st->cfg.dampening,
+                                         st->cfg.weight_decay, st->cfg.nesterov ? 1 : 0, self->t == 0 ? 1 : 0, st->c.grad_scale, p->numel,
+                                         nci_stream()), "sgd step");
+    }
+    self->t++;
+}
+static void sgd_free(void* state) {
+    sgd_state* st = state;
+    for (size_t i = 0; i < NC_MAX_OPTIM_PARAMS; i++) if (st->velocity[i]) nc_tensor_free(st->velocity[i]);
+    nc_free(st);
+}
+nc_optimizer* nc_sgd(double lr, nc_sgd_config config) {
+    nc_optimizer* o = nc_calloc(1, sizeof(nc_optimizer));
+    sgd_state* st = o ? nc_calloc(1, sizeof(sgd_state)) : NULL;
+    if (!st) { nc_free(o); return NULL; }
+    st->c.grad_scale = 1.0;
+    st->cfg = config;
+    o->lr = lr; o->step = sgd_step; o->state = st; o->free_state = sgd_free;
+    return o;
+}
+nc_optimizer* nc_sgd_from_module(nc_module* m, double lr, nc_sgd_config config) {
+    nc_optimizer* o = nc_sgd(lr, config);
+    if (o) nc_optimizer_add_module(o, m);
+    return o;
+}
+nc_optimizer* nc_sgd_simple(nc_module* m, double lr) { return nc_sgd_from_module(m, lr, NC_SGD_DEFAULT); }
+nc_optimizer* nc_sgd_momentum(nc_module* m, double lr, double momentum) {
+    nc_sgd_config c = NC_SGD_DEFAULT;
+    c.momentum = momentum;
+    return nc_sgd_from_module(m, lr, c);
+}
+
+/* ------------------------------------------------------------------ Adam / AdamW */
+static void adam_step(nc_optimizer* self) {
+    adam_state* st = self->state;
+    self->t++;
+    const double bc1 = 1.0 - pow(st->cfg.beta1, (double)self->t), bc2 = 1.0 - pow(st->cfg.beta2, (double)self->t);
+    for (size_t i = 0; i < self->n_params; i++) {
+        nc_tensor* p = self->params[i];
+        if (!param_ready(p, "adam")) continue;
+        if (!st->m[i]) {
+            st->m[i] = state_like(p);
+            st->v[i] = state_like(p);
+            if (st->cfg.amsgrad) st->vmax[i] = state_like(p);
+        }
+        if (!st->m[i] || !st->v[i]) continue;
+        nci_ok(nc_cuda_adam_update_f32_ex(nci_fptr(p), nci_fptr(st->m[i]), nci_fptr(st->v[i]), st->vmax[i] ? nci_fptr(st->vmax[i]) : NULL,
+                                          nci_fptr(p->grad), self->lr, st->cfg.beta1, st->cfg.beta2, st->cfg.eps, st->cfg.weight_decay, bc1,
+                                          bc2, st->c.grad_scale, p->numel, nci_stream()), "adam step");
+    }
+}
+static void adam_free(void* state) {
+    adam_state* st = state;
+    for (size_t i = 0; i < NC_MAX_OPTIM_PARAMS; i++) {
+        if (st->m[i]) nc_tensor_free(st->m[i]);
+        if (st->v[i]) nc_tensor_free(st->v[i]);
+        if (st->vmax[i]) nc_tensor_free(st->vmax[i]);
+    }
+    nc_free(st);
+}
+nc_optimizer* nc_adam(double lr, nc_adam_config config) {
+    nc_optimizer* o = nc_calloc(1, sizeof(nc_optimizer));
+    adam_state* st = o ? nc_calloc(1, sizeof(adam_state)) : NULL;
+    if (!st) { nc_free(o); return NULL; }
+    st->c.grad_scale = 1.0;
+    st->cfg = config;
+    o->lr = lr; o->step = adam_step; o->state = st; o->free_state = adam_free;
+    return o;
+}
+nc_optimizer* nc_adam_from_module(nc_module* m, double lr, nc_adam_config config) {
+    nc_optimizer* o = nc_adam(lr, config);
+    if (o) nc_optimizer_add_module(o, m);
+    return o;
+}
+nc_optimizer* nc_adam_default(nc_module* m, double lr) { return nc_adam_from_module(m, lr, NC_ADAM_DEFAULT); }
+nc_optimizer* nc_adamw(nc_module* m, double lr, double weight_decay) {
+    nc_adam_config c = NC_ADAM_DEFAULT;
+    c.weight_decay = weight_decay;
+    return nc_adam_from_module(m, lr, c);
+}
