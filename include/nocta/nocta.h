@@ -367,6 +367,9 @@ void nc_optimizer_add_module(nc_optimizer* opt, nc_module* m);
 void nc_optimizer_add_param(nc_optimizer* opt, nc_tensor* param);
 /* new: gradients are multiplied by this before the update (1/world_size under data parallel) */
 void nc_optimizer_set_grad_scale(nc_optimizer* opt, double scale);
+/* new: move all parameter gradients into one device allocation (views at 256-byte aligned offsets);
+ * returns its device address and length in floats, so data-parallel code can all-reduce one range */
+void* nc_optimizer_flatten_grads(nc_optimizer* opt, size_t* n_floats);
 
 typedef struct {
     double momentum;

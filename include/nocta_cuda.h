@@ -85,6 +85,12 @@ unsigned int nc_cuda_device_error_word(void);
 unsigned long long nc_cuda_launch_count(void);
 void  nc_cuda_reset_launch_count(void);
 
+/* new: per-launch CUDA-event timing of the tensor-core contraction kernel on its launching stream.
+ * begin() arms it; end() waits for the last timed launch and returns the summed kernel time, the
+ * number of timed launches and their algorithmic FLOPs (2*M*N*K of each logical contraction). */
+int nc_cuda_tc_profile_begin(void);
+int nc_cuda_tc_profile_end(double* total_ms, unsigned long long* launches, double* flops);
+
 /* ---------------- elementwise (reference: cuda_kernels.h:26-49, src/cuda/cuda_elementwise.cu) ---- */
 void nc_cuda_fill_f32(float* data, float value, size_t n);                        /* :26 */
 void nc_cuda_copy_f32(float* dst, const float* src, size_t n);                    /* :28 */

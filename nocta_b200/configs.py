@@ -264,9 +264,10 @@ def _adam(api, net, lr, wd):
 # ----------------------------------------------------------------------------------------------
 # one training step
 # ----------------------------------------------------------------------------------------------
-def train_step(r: Runner, net: Net, forward, loss_kind, tensors):
-    """zero_grad -> forward -> loss -> backward -> optimizer step.  Returns the loss tensor (kept
-    alive in net.keep until free_step_tensors)."""
+def train_step(r: Runner, net: Net, forward, loss_kind, tensors, after_backward=None):
+    """zero_grad -> forward -> loss -> backward -> [after_backward()] -> optimizer step.  Returns the
+    loss tensor (kept alive in net.keep until free_step_tensors).  `after_backward` is where a
+    data-parallel caller sums the gradients across ranks."""
     api = r.api
     api.nc_optimizer_zero_grad(net.optimizer)
     if loss_kind == "ce":
@@ -280,6 +281,8 @@ def train_step(r: Runner, net: Net, forward, loss_kind, tensors):
     rc = api.nc_backward_scalar(loss)
     if rc != 0:
         raise RuntimeError(f"nc_backward_scalar failed with {rc}")
+    if after_backward is not None:
+        after_backward()
     api.nc_optimizer_step(net.optimizer)
     return loss
 

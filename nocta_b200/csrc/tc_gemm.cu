@@ -549,6 +549,18 @@ static bool make_map(CUtensorMap* tm, const float* base, int rank, const unsigne
     return r == CUDA_SUCCESS;
 }
 
+// Optional per-launch timing of the tensor-core kernel (CUDA events on the launching stream), used by
+// the benchmark to report achieved TFLOP/s of this kernel inside a real training step.
+struct ProfState {
+    bool on = false;
+    int n = 0, cap = 0;
+    cudaEvent_t* start = nullptr;
+    cudaEvent_t* stop = nullptr;
+    double flops = 0.0;
+    double next_flops = 0.0;  // algorithmic FLOPs of the launch about to be made
+};
+static ProfState g_prof;
+
 template <int BN, bool A_MN, bool B_MN, int MODE>
 static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const TcParams& p, dim3 grid, cudaStream_t st) {
     using Cfg = TileCfg<BN, MODE>;
@@ -558,7 +570,14 @@ static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const TcPara
         NCC_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         attr_set = true;
     }
+    const bool prof = g_prof.on && g_prof.n < g_prof.cap;
+    if (prof) cudaEventRecord(g_prof.start[g_prof.n], st);
     kern<<<grid, 192, Cfg::SMEM_BYTES, st>>>(ta, tb, p);
+    if (prof) {
+        cudaEventRecord(g_prof.stop[g_prof.n], st);
+        g_prof.n++;
+        g_prof.flops += g_prof.next_flops;
+    }
     NCC_COUNT_LAUNCH();
     return ncc::launch_status("tc_kernel");
 }
@@ -633,6 +652,7 @@ int gemm(float* D, int ldd, const float* A, int lda, bool a_mn, const float* B, 
         if (!p.partial) return NC_CUDA_ERR_RUNTIME;
     }
     dim3 grid(tiles_n, tiles_m, splits);
+    g_prof.next_flops = 2.0 * M * (double)N * K;
     int rc;
     if (!a_mn && !b_mn) rc = launch_bn<false, false>(bn, mode, ta, tb, p, grid, st);
     else if (!a_mn && b_mn) rc = launch_bn<false, true>(bn, mode, ta, tb, p, grid, st);
@@ -698,6 +718,7 @@ int conv_nhwc(float* y, const float* x, const float* wpacked, const float* bias,
     const long long tiles_m = (long long)p.tiles_w * p.tiles_h * ((N + bnn - 1) / bnn);
     if (tiles_m > 65535) return NC_CUDA_ERR_UNSUPPORTED;
     dim3 grid((Cout + bn_cols - 1) / bn_cols, (unsigned)tiles_m, 1);
+    g_prof.next_flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
     return launch_bn<false, false>(bn_cols, mode, ta, tb, p, grid, st);
 }
 
@@ -741,6 +762,7 @@ int conv_dw_nhwc(float* dW, const float* dy, const float* x, int N, int H, int W
     p.partial = (float*)ncc::scratch(2, sizeof(float) * (size_t)splits * Cout * Ncols, st);
     if (!p.partial) return NC_CUDA_ERR_RUNTIME;
     dim3 grid(tiles_n, tiles_m, splits);
+    g_prof.next_flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
     int rc;
     if (bn_cols == 192) rc = launch_mode<192, true, true>(mode, ta, tb, p, grid, st);
     else rc = launch_bn<true, true>(bn_cols, mode, ta, tb, p, grid, st);
@@ -762,6 +784,40 @@ int pack_weights_dx(float* wp, const float* w, int Cout, int Cin, int kH, int kW
 }
 
 }  // namespace tc
+
+extern "C" int nc_cuda_tc_profile_begin(void) {
+    using tc::g_prof;
+    if (!g_prof.start) {
+        g_prof.cap = 16384;
+        g_prof.start = new cudaEvent_t[g_prof.cap];
+        g_prof.stop = new cudaEvent_t[g_prof.cap];
+        for (int i = 0; i < g_prof.cap; i++) {
+            if (cudaEventCreate(&g_prof.start[i]) != cudaSuccess || cudaEventCreate(&g_prof.stop[i]) != cudaSuccess)
+                return ncc::set_status(NC_CUDA_ERR_RUNTIME, "tc profile: cudaEventCreate failed");
+        }
+    }
+    g_prof.n = 0;
+    g_prof.flops = 0.0;
+    g_prof.on = true;
+    return NC_CUDA_OK;
+}
+extern "C" int nc_cuda_tc_profile_end(double* total_ms, unsigned long long* launches, double* flops) {
+    using tc::g_prof;
+    g_prof.on = false;
+    double ms = 0.0;
+    if (g_prof.n > 0) {
+        if (cudaEventSynchronize(g_prof.stop[g_prof.n - 1]) != cudaSuccess)
+            return ncc::set_status(NC_CUDA_ERR_RUNTIME, "tc profile: cudaEventSynchronize failed");
+        for (int i = 0; i < g_prof.n; i++) {
+            float t = 0.f;
+            if (cudaEventElapsedTime(&t, g_prof.start[i], g_prof.stop[i]) == cudaSuccess) ms += t;
+        }
+    }
+    if (total_ms) *total_ms = ms;
+    if (launches) *launches = (unsigned long long)g_prof.n;
+    if (flops) *flops = g_prof.flops;
+    return NC_CUDA_OK;
+}
 
 // Bring-up knob (not part of the public header): selects an alternative shared-memory descriptor
 // encoding for MN-major operands so both can be checked against a known answer on hardware.

@@ -53,6 +53,8 @@ SIGNATURES = {
     "nc_cuda_device_error_word": (C.c_uint, []),
     "nc_cuda_launch_count": (C.c_ulonglong, []),
     "nc_cuda_reset_launch_count": (None, []),
+    "nc_cuda_tc_profile_begin": (_i, []),
+    "nc_cuda_tc_profile_end": (_i, [C.POINTER(_d), C.POINTER(C.c_ulonglong), C.POINTER(_d)]),
     # elementwise
     "nc_cuda_fill_f32": (None, [_p, _f, _z]),
     "nc_cuda_copy_f32": (None, [_p, _p, _z]),

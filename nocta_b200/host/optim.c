@@ -33,6 +33,47 @@ static void cb_add(const char* name, nc_tensor* p, void* ctx) { (void)name; nc_o
 void nc_optimizer_add_module(nc_optimizer* opt, nc_module* m) { if (opt && m) nc_module_parameters(m, cb_add, opt); }
 void nc_optimizer_set_grad_scale(nc_optimizer* opt, double scale) { if (opt && opt->state) ((opt_common*)opt->state)->grad_scale = scale; }
 
+/* Re-homes every parameter gradient of the optimizer into ONE device allocation (each gradient becomes a
+ * view at a 256-byte aligned offset) and returns its device address and length in floats.  A data-parallel
+ * caller sums that single range across ranks instead of one small buffer per parameter; padding between
+ * views is zero and stays zero.  Gradients keep their values. */
+void* nc_optimizer_flatten_grads(nc_optimizer* opt, size_t* n_floats) {
+    if (!opt || !n_floats) return NULL;
+    size_t total = 0;
+    for (size_t i = 0; i < opt->n_params; i++) {
+        nc_tensor* p = opt->params[i];
+        if (!p || p->dtype != NC_F32 || !nci_on_cuda(p)) { NC_SET_ERROR(NC_ERR_DEVICE, "flatten_grads: f32 CUDA parameters required"); return NULL; }
+        total += (p->numel + 63) & ~(size_t)63;
+    }
+    if (!total) return NULL;
+    nc_storage* arena = nc_storage_create_on(total * sizeof(float), NC_DEVICE_CUDA);
+    if (!arena) return NULL;
+    nc_cuda_memset_async(arena->cuda_data, 0, total * sizeof(float), nci_stream());
+    size_t off = 0;
+    for (size_t i = 0; i < opt->n_params; i++) {
+        nc_tensor* p = opt->params[i];
+        nc_tensor* g = nc_calloc(1, sizeof(nc_tensor));
+        if (!g) { nc_storage_release(arena); return NULL; }
+        g->storage = nc_storage_retain(arena);
+        g->offset = off;
+        g->ndim = p->ndim;
+        g->numel = p->numel;
+        memcpy(g->shape, p->shape, sizeof(g->shape));
+        memcpy(g->strides, p->strides, sizeof(g->strides));
+        g->dtype = NC_F32;
+        g->is_leaf = true;
+        g->is_contiguous = true;
+        if (p->grad) { nc_tensor_copy_(g, p->grad); nc_tensor_free(p->grad); }
+        p->grad = g;
+        p->requires_grad = true;
+        off += (p->numel + 63) & ~(size_t)63;
+    }
+    void* base = arena->cuda_data;
+    nc_storage_release(arena); /* the views keep it alive */
+    *n_floats = total;
+    return base;
+}
+
 static nc_tensor* state_like(const nc_tensor* p) {
     nc_tensor* s = nci_empty_on(p->shape, p->ndim, p->dtype, p->storage->device);
     if (s) nc_tensor_fill_(s, 0.0);
