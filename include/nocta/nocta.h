@@ -332,6 +332,12 @@ nc_tensor* nc_batchnorm2d_running_mean(nc_module* bn);
 nc_tensor* nc_batchnorm2d_running_var(nc_module* bn);
 nc_tensor* nc_batchnorm2d_forward_fn(nc_tensor* input, nc_tensor* running_mean, nc_tensor* running_var,
                                      nc_tensor* weight, nc_tensor* bias, bool training, double momentum, double eps);
+/* new: BatchNorm2d followed by ReLU as ONE forward kernel pass and ONE backward pass (the output is
+ * the ReLU mask); same result as nc_relu(nc_batchnorm2d_forward_fn(...)).  The module form takes a
+ * module made by nc_batchnorm2d / nc_batchnorm2d_ex. */
+nc_tensor* nc_batchnorm2d_relu_forward_fn(nc_tensor* input, nc_tensor* running_mean, nc_tensor* running_var,
+                                          nc_tensor* weight, nc_tensor* bias, bool training, double momentum, double eps);
+nc_tensor* nc_batchnorm2d_relu(nc_module* bn, nc_tensor* x);
 typedef struct {
     size_t* normalized_shape;
     size_t normalized_ndim;

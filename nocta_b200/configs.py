@@ -60,9 +60,13 @@ class Runner:
         if hasattr(lib, "nc_flatten_forward"):
             self.flatten = self._bind(lib.nc_flatten_forward)
             self.gelu = api.nc_gelu
+            lib.nc_batchnorm2d_relu.restype = capi.TensorP
+            lib.nc_batchnorm2d_relu.argtypes = [capi.ModuleP, capi.TensorP]
+            self._bn_relu = lib.nc_batchnorm2d_relu
         else:  # reference build: differentiable shims compiled next to it
             self.flatten = api.shim_flatten
             self.gelu = api.shim_gelu
+            self._bn_relu = None
         if on_device:
             lib.nc_init.restype = None
             lib.nc_init()
@@ -75,6 +79,13 @@ class Runner:
         fn.restype = capi.TensorP
         fn.argtypes = [capi.TensorP]
         return fn
+
+    def bn_relu(self, keep, module, x):
+        """BatchNorm2d + ReLU: one fused call where the library has it, else the two reference calls."""
+        if self._bn_relu is not None:
+            return _k(keep, self._bn_relu(module, x))
+        h = _k(keep, self.api.nc_module_forward(module, x))
+        return _k(keep, self.api.nc_relu(h))
 
     def tensor(self, a: np.ndarray, requires_grad=False):
         # after nc_init the default device is CUDA, so from_data uploads
@@ -154,8 +165,7 @@ def build_convbn(r: Runner, seed=1236, batch=128):
         h = xt
         for c, b in (("conv1", "bn1"), ("conv2", "bn2")):
             h = _k(k, a.nc_module_forward(m[c], h))
-            h = _k(k, a.nc_module_forward(m[b], h))
-            h = _k(k, a.nc_relu(h))
+            h = r.bn_relu(k, m[b], h)
             h = _k(k, a.nc_maxpool2d_forward(h, 2, 2))
         h = _k(k, r.flatten(h))
         return _k(k, a.nc_module_forward(m["fc"], h))
@@ -227,8 +237,7 @@ def build_vgg(r: Runner, seed=1239, batch=256, classes=100, rank=0, size=64, wid
         for names in stages:
             for c, b in names:
                 h = _k(k, a.nc_module_forward(m[c], h))
-                h = _k(k, a.nc_module_forward(m[b], h))
-                h = _k(k, a.nc_relu(h))
+                h = r.bn_relu(k, m[b], h)
             h = _k(k, a.nc_maxpool2d_forward(h, 2, 2))
         h = _k(k, r.flatten(h))
         return _k(k, a.nc_module_forward(m["fc"], h))

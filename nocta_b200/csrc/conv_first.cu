@@ -1,0 +1,179 @@
+// First-layer convolution (3 input channels, 3x3, stride 1) with a channels-last output: the case the
+// tensor-core implicit GEMM cannot tile (reduction length 27) and that is bound by writing the output,
+// not by arithmetic.  Forward: 4..16 threads per output pixel, 16 output channels each, the 27 patch
+// values in registers and the weights in shared memory.  Weight gradient: the reduction over all
+// pixels is split over CTAs; each CTA stages 64-pixel tiles of dY and of the 27-wide patches in shared
+// memory, every thread owns one output channel and 8 of the (padded to 32) patch positions; per-CTA
+// partial sums are combined in a fixed order.  No input gradient: the network input needs none.
+// Semantics: src/nn/conv.c:269-299 (dW), :381-586 (forward) of the reference.
+#include "nc_common.cuh"
+
+namespace convfirst {
+
+constexpr int K = 27;   // 3 channels x 3 x 3, ordered (ci, kh, kw) like the reference weight layout
+constexpr int KP = 32;  // padded patch width
+
+struct Geo {
+    int N, H, W, Cout, pad, Ho, Wo;
+    long long xs[4];  // input strides (n, c, h, w) in elements
+};
+
+__device__ __forceinline__ void load_patch(float (&x)[K], const float* __restrict__ in, const Geo& g, int n, int ho, int wo) {
+#pragma unroll
+    for (int ci = 0; ci < 3; ci++)
+#pragma unroll
+        for (int kh = 0; kh < 3; kh++)
+#pragma unroll
+            for (int kw = 0; kw < 3; kw++) {
+                const int h = ho + kh - g.pad, w = wo + kw - g.pad;
+                float v = 0.f;
+                if (h >= 0 && h < g.H && w >= 0 && w < g.W) v = in[n * g.xs[0] + ci * g.xs[1] + h * g.xs[2] + w * g.xs[3]];
+                x[(ci * 3 + kh) * 3 + kw] = v;
+            }
+}
+
+// y (N,Ho,Wo,Cout) channels-last; weights (Cout, 27)
+__global__ void __launch_bounds__(256) fwd_kernel(float* __restrict__ y, const float* __restrict__ in, const float* __restrict__ w,
+                                                  const float* __restrict__ bias, Geo g, long long pixels) {
+    extern __shared__ float ws[];  // [K][Cout] then bias [Cout]
+    float* bs = ws + K * g.Cout;
+    for (int i = threadIdx.x; i < K * g.Cout; i += blockDim.x) {
+        const int co = i % g.Cout, k = i / g.Cout;
+        ws[i] = w[co * K + k];
+    }
+    for (int i = threadIdx.x; i < g.Cout; i += blockDim.x) bs[i] = bias ? bias[i] : 0.f;
+    __syncthreads();
+    const int tpp = g.Cout / 16;  // threads per pixel
+    const int ppb = blockDim.x / tpp;
+    const int lp = threadIdx.x / tpp, cq = threadIdx.x % tpp;
+    for (long long p = (long long)blockIdx.x * ppb + lp; p < pixels; p += (long long)gridDim.x * ppb) {
+        const int wo = (int)(p % g.Wo);
+        const long long t = p / g.Wo;
+        const int ho = (int)(t % g.Ho), n = (int)(t / g.Ho);
+        float x[K];
+        load_patch(x, in, g, n, ho, wo);
+        float acc[16];
+#pragma unroll
+        for (int j = 0; j < 16; j++) acc[j] = bs[cq * 16 + j];
+#pragma unroll
+        for (int k = 0; k < K; k++) {
+            const float4* wr = reinterpret_cast<const float4*>(ws + k * g.Cout + cq * 16);
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const float4 wv = wr[q];
+                acc[4 * q + 0] = fmaf(x[k], wv.x, acc[4 * q + 0]);
+                acc[4 * q + 1] = fmaf(x[k], wv.y, acc[4 * q + 1]);
+                acc[4 * q + 2] = fmaf(x[k], wv.z, acc[4 * q + 2]);
+                acc[4 * q + 3] = fmaf(x[k], wv.w, acc[4 * q + 3]);
+            }
+        }
+        float4* dst = reinterpret_cast<float4*>(y + p * g.Cout + cq * 16);
+#pragma unroll
+        for (int q = 0; q < 4; q++) dst[q] = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+    }
+}
+
+// partial[block][co][KP]; block handles pixels [blockIdx.x * per_block, +per_block)
+constexpr int TP = 64;  // pixels per shared-memory tile
+template <int COUT>
+__global__ void __launch_bounds__(COUT * 4) dw_kernel(float* __restrict__ partial, const float* __restrict__ dy,
+                                                      const float* __restrict__ in, Geo g, long long pixels, long long per_block) {
+    __shared__ __align__(16) float sdy[TP][COUT];
+    __shared__ __align__(16) float sx[TP][KP];
+    const int co = threadIdx.x % COUT, grp = threadIdx.x / COUT;  // grp 0..3 -> patch positions grp*8 .. +7
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) acc[j] = 0.f;
+    const long long p0 = (long long)blockIdx.x * per_block;
+    long long p1 = p0 + per_block;
+    if (p1 > pixels) p1 = pixels;
+    for (long long base = p0; base < p1; base += TP) {
+        const int cnt = (int)((p1 - base) < TP ? (p1 - base) : TP);
+        // dY tile: rows are contiguous in channels-last memory
+        for (int i = threadIdx.x; i < TP * COUT / 4; i += blockDim.x) {
+            const int r = i / (COUT / 4), c4 = i % (COUT / 4);
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < cnt) v = reinterpret_cast<const float4*>(dy + (base + r) * COUT)[c4];
+            reinterpret_cast<float4*>(&sdy[r][0])[c4] = v;
+        }
+        // patches: one (pixel, position) per thread-iteration
+        for (int i = threadIdx.x; i < TP * KP; i += blockDim.x) {
+            const int r = i / KP, k = i % KP;
+            float v = 0.f;
+            if (r < cnt && k < K) {
+                const long long p = base + r;
+                const int wo = (int)(p % g.Wo);
+                const long long t = p / g.Wo;
+                const int ho = (int)(t % g.Ho), n = (int)(t / g.Ho);
+                const int kw = k % 3, kh = (k / 3) % 3, ci = k / 9;
+                const int h = ho + kh - g.pad, w = wo + kw - g.pad;
+                if (h >= 0 && h < g.H && w >= 0 && w < g.W) v = in[n * g.xs[0] + ci * g.xs[1] + h * g.xs[2] + w * g.xs[3]];
+            }
+            sx[r][k] = v;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int r = 0; r < TP; r++) {
+            const float d = sdy[r][co];
+            const float4 a = *reinterpret_cast<const float4*>(&sx[r][grp * 8]);
+            const float4 b = *reinterpret_cast<const float4*>(&sx[r][grp * 8 + 4]);
+            acc[0] = fmaf(d, a.x, acc[0]); acc[1] = fmaf(d, a.y, acc[1]); acc[2] = fmaf(d, a.z, acc[2]); acc[3] = fmaf(d, a.w, acc[3]);
+            acc[4] = fmaf(d, b.x, acc[4]); acc[5] = fmaf(d, b.y, acc[5]); acc[6] = fmaf(d, b.z, acc[6]); acc[7] = fmaf(d, b.w, acc[7]);
+        }
+        __syncthreads();
+    }
+    float* dst = partial + ((long long)blockIdx.x * COUT + co) * KP + grp * 8;
+    reinterpret_cast<float4*>(dst)[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    reinterpret_cast<float4*>(dst)[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+}
+
+__global__ void __launch_bounds__(256) dw_reduce_kernel(float* __restrict__ dW, const float* __restrict__ partial, int blocks, int Cout) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= Cout * K) return;
+    const int co = i / K, k = i % K;
+    double acc = 0.0;
+    for (int b = 0; b < blocks; b++) acc += (double)partial[((long long)b * Cout + co) * KP + k];
+    dW[i] = (float)acc;
+}
+
+bool eligible(int Cin, int kH, int kW, int stride, int Cout) {
+    return Cin == 3 && kH == 3 && kW == 3 && stride == 1 && Cout % 16 == 0 && Cout >= 16 && Cout <= 256;
+}
+
+int forward(float* y, const float* x, const long long xs[4], const float* w, const float* bias, int N, int H, int W, int Cout, int pad,
+            cudaStream_t st) {
+    Geo g{N, H, W, Cout, pad, H + 2 * pad - 2, W + 2 * pad - 2, {xs[0], xs[1], xs[2], xs[3]}};
+    if (g.Ho <= 0 || g.Wo <= 0) return NC_CUDA_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(y) & 15u) != 0) return NC_CUDA_ERR_UNSUPPORTED;
+    const long long pixels = (long long)N * g.Ho * g.Wo;
+    const int ppb = 256 / (Cout / 16);
+    long long need = (pixels + ppb - 1) / ppb;
+    const long long cap = (long long)ncc::sm_count() * 8;
+    const int grid = (int)(need < cap ? need : cap);
+    const size_t smem = sizeof(float) * (size_t)(K + 1) * Cout;
+    fwd_kernel<<<grid, 256, smem, st>>>(y, x, w, bias, g, pixels);
+    NCC_COUNT_LAUNCH();
+    return ncc::launch_status("conv_first forward");
+}
+
+int weight_grad(float* dW, const float* dy, const float* x, const long long xs[4], int N, int H, int W, int Cout, int pad, cudaStream_t st) {
+    if (Cout != 64 && Cout != 32) return NC_CUDA_ERR_UNSUPPORTED;
+    Geo g{N, H, W, Cout, pad, H + 2 * pad - 2, W + 2 * pad - 2, {xs[0], xs[1], xs[2], xs[3]}};
+    if (g.Ho <= 0 || g.Wo <= 0) return NC_CUDA_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(dy) & 15u) != 0) return NC_CUDA_ERR_UNSUPPORTED;
+    const long long pixels = (long long)N * g.Ho * g.Wo;
+    long long blocks = (long long)ncc::sm_count() * 4;
+    long long per = (pixels + blocks - 1) / blocks;
+    per = ((per + TP - 1) / TP) * TP;
+    blocks = (pixels + per - 1) / per;
+    float* partial = (float*)ncc::scratch(2, sizeof(float) * (size_t)blocks * Cout * KP, st);
+    if (!partial) return NC_CUDA_ERR_RUNTIME;
+    if (Cout == 64) dw_kernel<64><<<(int)blocks, 256, 0, st>>>(partial, dy, x, g, pixels, per);
+    else dw_kernel<32><<<(int)blocks, 128, 0, st>>>(partial, dy, x, g, pixels, per);
+    NCC_COUNT_LAUNCH();
+    dw_reduce_kernel<<<ncc::ceil_div(Cout * K, 256), 256, 0, st>>>(dW, partial, (int)blocks, Cout);
+    NCC_COUNT_LAUNCH();
+    return ncc::launch_status("conv_first weight_grad");
+}
+
+}  // namespace convfirst

@@ -12,6 +12,13 @@
 
 using namespace ncc;
 
+namespace convfirst {
+bool eligible(int Cin, int kH, int kW, int stride, int Cout);
+int forward(float* y, const float* x, const long long xs[4], const float* w, const float* bias, int N, int H, int W, int Cout, int pad,
+            cudaStream_t st);
+int weight_grad(float* dW, const float* dy, const float* x, const long long xs[4], int N, int H, int W, int Cout, int pad, cudaStream_t st);
+}  // namespace convfirst
+
 namespace {
 
 // ---------------- SIMT loaders / epilogues ----------------
@@ -316,6 +323,10 @@ int nc_cuda_conv2d_forward_f32_ex(float* y, const size_t ys[4], const float* x, 
         rc = tc::conv_nhwc(y, x, wp, bias, N, H, W, Cin, Cout, kH, kW, pad, tc_mode(), st);
         if (rc != NC_CUDA_ERR_UNSUPPORTED) return rc;
     }
+    if (convfirst::eligible(Cin, kH, kW, stride, Cout) && is_nhwc(g.ys, Cout, g.Ho, g.Wo)) {
+        rc = convfirst::forward(y, x, g.xs, w, bias, N, H, W, Cout, pad, st);
+        if (rc != NC_CUDA_ERR_UNSUPPORTED) return rc;
+    }
     const int M = N * g.Ho * g.Wo, K = Cin * kH * kW;
     return simt::launch<false, true>(M, Cout, K, 1, ConvFwdA{x, g}, MatLoad{w, K, 1}, ConvFwdStore{y, bias, g}, st,
                                      "conv2d_forward(simt)");
@@ -371,6 +382,10 @@ int nc_cuda_conv2d_backward_weight_f32_ex(float* dW, float* db, const float* dy,
     if (!dW) return NC_CUDA_OK;
     if (tc_enabled() && stride == 1 && is_nhwc(g.xs, Cin, H, W) && is_nhwc(g.ys, Cout, g.Ho, g.Wo)) {
         rc = tc::conv_dw_nhwc(dW, dy, x, N, H, W, Cin, Cout, kH, kW, pad, tc_mode(), st);
+        if (rc != NC_CUDA_ERR_UNSUPPORTED) return rc;
+    }
+    if (convfirst::eligible(Cin, kH, kW, stride, Cout) && is_nhwc(g.ys, Cout, g.Ho, g.Wo)) {
+        rc = convfirst::weight_grad(dW, dy, x, g.xs, N, H, W, Cout, pad, st);
         if (rc != NC_CUDA_ERR_UNSUPPORTED) return rc;
     }
     const int Kred = N * g.Ho * g.Wo, Ncols = Cin * kH * kW;

@@ -222,6 +222,51 @@ __global__ void __launch_bounds__(256) colreduce_kernel(double* __restrict__ par
     }
 }
 
+// Same reduction for cols % 4 == 0: each thread owns FOUR consecutive columns (one float4 per row and
+// operand), TX threads span the columns of the block and 256 / TX thread rows walk the slab two rows
+// at a time, so a warp issues full 128-byte (or wider) requests and several are in flight.
+template <class F>
+__global__ void __launch_bounds__(256) colreduce4_kernel(double* __restrict__ partial, size_t rows, int cols, size_t rows_per_slab,
+                                                         int TX, F f) {
+    __shared__ double sh[256][9];
+    const int tx = threadIdx.x % TX, ty = threadIdx.x / TX, TY = 256 / TX;
+    const int c = (blockIdx.x * TX + tx) * 4;
+    const size_t r0 = (size_t)blockIdx.y * rows_per_slab;
+    size_t r1 = r0 + rows_per_slab;
+    if (r1 > rows) r1 = rows;
+    double a[4] = {0, 0, 0, 0}, b[4] = {0, 0, 0, 0};
+    if (c < cols) {
+        size_t r = r0 + ty;
+        for (; r + TY < r1; r += 2 * TY) {
+            float4 u1, u2, w1, w2;
+            f.vec(r, c, u1, u2);
+            f.vec(r + TY, c, w1, w2);
+            a[0] += (double)u1.x + (double)w1.x; a[1] += (double)u1.y + (double)w1.y;
+            a[2] += (double)u1.z + (double)w1.z; a[3] += (double)u1.w + (double)w1.w;
+            b[0] += (double)u2.x + (double)w2.x; b[1] += (double)u2.y + (double)w2.y;
+            b[2] += (double)u2.z + (double)w2.z; b[3] += (double)u2.w + (double)w2.w;
+        }
+        for (; r < r1; r += TY) {
+            float4 u1, u2;
+            f.vec(r, c, u1, u2);
+            a[0] += u1.x; a[1] += u1.y; a[2] += u1.z; a[3] += u1.w;
+            b[0] += u2.x; b[1] += u2.y; b[2] += u2.z; b[3] += u2.w;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; j++) { sh[threadIdx.x][j] = a[j]; sh[threadIdx.x][4 + j] = b[j]; }
+    __syncthreads();
+    if (ty == 0 && c < cols) {
+        double s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int k = 0; k < TY; k++)
+#pragma unroll
+            for (int j = 0; j < 8; j++) s[j] += sh[k * TX + tx][j];
+        double* p = partial + ((size_t)blockIdx.y * cols + c) * 2;
+#pragma unroll
+        for (int j = 0; j < 4; j++) { p[2 * j] = s[j]; p[2 * j + 1] = s[4 + j]; }
+    }
+}
+
 // NCHW channel reduce: block (c, j) walks images n = j, j+J, ... of channel c, each a contiguous run
 // of `spatial` floats.
 template <class F>
@@ -252,6 +297,10 @@ struct BnFwdSum {  // (x, x^2)
     __device__ void operator()(size_t r, int c, float& v1, float& v2) const {
         float t = x[r * cols + c]; v1 = t; v2 = t * t;
     }
+    __device__ void vec(size_t r, int c, float4& v1, float4& v2) const {
+        v1 = *reinterpret_cast<const float4*>(x + r * cols + c);
+        v2 = make_float4(v1.x * v1.x, v1.y * v1.y, v1.z * v1.z, v1.w * v1.w);
+    }
 };
 struct BnFwdSumFlat {  // NCHW flavour: flat index supplied
     const float* x;
@@ -266,6 +315,23 @@ struct BnBwdSum {
         if (y && !(y[i] > 0.f)) g = 0.f;
         float xh = (x[i] - mean[c]) * rsqrtf(var[c] + eps);
         v1 = g; v2 = g * xh;
+    }
+    __device__ void vec(size_t r, int c, float4& v1, float4& v2) const {
+        const size_t i = r * cols + c;
+        float4 g = *reinterpret_cast<const float4*>(dy + i);
+        const float4 xv = *reinterpret_cast<const float4*>(x + i);
+        if (y) {
+            const float4 yv = *reinterpret_cast<const float4*>(y + i);
+            if (!(yv.x > 0.f)) g.x = 0.f;
+            if (!(yv.y > 0.f)) g.y = 0.f;
+            if (!(yv.z > 0.f)) g.z = 0.f;
+            if (!(yv.w > 0.f)) g.w = 0.f;
+        }
+        const float4 m = *reinterpret_cast<const float4*>(mean + c);
+        const float4 vr = *reinterpret_cast<const float4*>(var + c);
+        v1 = g;
+        v2 = make_float4(g.x * ((xv.x - m.x) * rsqrtf(vr.x + eps)), g.y * ((xv.y - m.y) * rsqrtf(vr.y + eps)),
+                         g.z * ((xv.z - m.z) * rsqrtf(vr.z + eps)), g.w * ((xv.w - m.w) * rsqrtf(vr.w + eps)));
     }
 };
 struct BnBwdSumFlat {
@@ -286,20 +352,62 @@ struct LnParamSum {
         float gv = g[i];
         v1 = gv * ((x[i] - s.x) * s.y); v2 = gv;
     }
+    __device__ void vec(size_t r, int c, float4& v1, float4& v2) const {
+        const size_t i = r * cols + c;
+        const float2 s = stats[r];
+        const float4 gv = *reinterpret_cast<const float4*>(g + i);
+        const float4 xv = *reinterpret_cast<const float4*>(x + i);
+        v1 = make_float4(gv.x * ((xv.x - s.x) * s.y), gv.y * ((xv.y - s.x) * s.y), gv.z * ((xv.z - s.x) * s.y), gv.w * ((xv.w - s.x) * s.y));
+        v2 = gv;
+    }
 };
+
+// Launch the column reduction of a dense (rows x cols) problem; picks the float4 kernel when the
+// columns and every operand pointer allow it.  Returns the slab count through *slabs_out.
+template <class F>
+int launch_colreduce(double** partial_out, int* slabs_out, size_t rows, int cols, bool vec_ok, F f, cudaStream_t st) {
+    const bool vec = vec_ok && (cols % 4 == 0);
+    int TX = 32, col_tiles;
+    if (vec) {
+        int c4 = cols / 4;
+        TX = c4 >= 32 ? 32 : (c4 >= 16 ? 16 : (c4 >= 8 ? 8 : (c4 >= 4 ? 4 : (c4 >= 2 ? 2 : 1))));
+        col_tiles = ceil_div(c4, TX);
+    } else {
+        col_tiles = ceil_div(cols, 32);
+    }
+    const size_t min_rows = vec ? (size_t)(256 / TX) * 4 : 64;
+    int want = (sm_count() * 4 + col_tiles - 1) / col_tiles;
+    size_t rps = (rows + want - 1) / want;
+    if (rps < min_rows) rps = min_rows;
+    int slabs = (int)((rows + rps - 1) / rps);
+    if (slabs > 65535) { slabs = 65535; rps = (rows + slabs - 1) / slabs; slabs = (int)((rows + rps - 1) / rps); }
+    double* partial = (double*)scratch(7, sizeof(double) * 2 * (size_t)slabs * cols, st);
+    if (!partial) return NC_CUDA_ERR_RUNTIME;
+    if (vec) colreduce4_kernel<<<dim3(col_tiles, slabs), 256, 0, st>>>(partial, rows, cols, rps, TX, f);
+    else colreduce_kernel<<<dim3(col_tiles, slabs), 256, 0, st>>>(partial, rows, cols, rps, f);
+    NCC_COUNT_LAUNCH();
+    *partial_out = partial;
+    *slabs_out = slabs;
+    return launch_status("column reduce");
+}
+inline bool al16(const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Stage 2 for BatchNorm forward: combine slabs in order, derive mean / biased variance, update the
 // running statistics (unbiased variance, src/nn/batchnorm.c:307-314).
 __global__ void bn_fwd_finalize_kernel(const double* __restrict__ partial, int slabs, int C, double M,
                                        float* __restrict__ save_mean, float* __restrict__ save_var,
                                        float* __restrict__ run_mean, float* __restrict__ run_var, double momentum) {
-    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    // one warp per channel: lanes stride over the slabs, then a fixed-order shuffle tree
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (c >= C) return;
     double s1 = 0.0, s2 = 0.0;
-    for (int s = 0; s < slabs; s++) {
+    for (int s = lane; s < slabs; s += 32) {
         s1 += partial[((size_t)s * C + c) * 2];
         s2 += partial[((size_t)s * C + c) * 2 + 1];
     }
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    if (lane != 0) return;
     double mean = s1 / M;
     double var_sum = s2 - s1 * mean;  // sum (x - mean)^2
     if (var_sum < 0.0) var_sum = 0.0;
@@ -353,13 +461,16 @@ __global__ void __launch_bounds__(kThreads) bn_apply_kernel(float* __restrict__ 
 
 __global__ void bn_bwd_finalize_kernel(const double* __restrict__ partial, int slabs, int C,
                                        float* __restrict__ dgamma, float* __restrict__ dbeta, float* __restrict__ sums) {
-    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (c >= C) return;
     double s1 = 0.0, s2 = 0.0;
-    for (int s = 0; s < slabs; s++) {
+    for (int s = lane; s < slabs; s += 32) {
         s1 += partial[((size_t)s * C + c) * 2];
         s2 += partial[((size_t)s * C + c) * 2 + 1];
     }
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    if (lane != 0) return;
     if (dbeta) dbeta[c] = (float)s1;
     if (dgamma) dgamma[c] = (float)s2;
     sums[2 * c] = (float)s1;
@@ -409,21 +520,10 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_apply_kernel(float* __restric
 // Launch stage 1 for a (N, C, spatial) tensor in either layout; returns the slab count.
 template <class FR, class FF>
 int channel_reduce(double** partial_out, int* slabs_out, int N, int C, int spatial, int layout, FR frows, FF fflat,
-                   cudaStream_t st) {
+                   bool vec_ok, cudaStream_t st) {
     if (layout == 1) {
-        const size_t rows = (size_t)N * spatial;
-        int col_tiles = ceil_div(C, 32);
-        int want = (sm_count() * 4 + col_tiles - 1) / col_tiles;
-        size_t rps = (rows + want - 1) / want;
-        if (rps < 64) rps = 64;
-        int slabs = (int)((rows + rps - 1) / rps);
-        if (slabs > 65535) { slabs = 65535; rps = (rows + slabs - 1) / slabs; slabs = (int)((rows + rps - 1) / rps); }
-        double* partial = (double*)scratch(7, sizeof(double) * 2 * (size_t)slabs * C, st);
-        if (!partial) return NC_CUDA_ERR_RUNTIME;
-        colreduce_kernel<<<dim3(col_tiles, slabs), 256, 0, st>>>(partial, rows, C, rps, frows);
-        NCC_COUNT_LAUNCH();
-        *partial_out = partial;
-        *slabs_out = slabs;
+        int rc = launch_colreduce(partial_out, slabs_out, (size_t)N * spatial, C, vec_ok, frows, st);
+        if (rc) return rc;
     } else {
         int J = (sm_count() * 4 + C - 1) / C;
         if (J > N) J = N;
@@ -506,13 +606,16 @@ __global__ void __launch_bounds__(kThreads) ln_bwd_rows_kernel(float* __restrict
 
 __global__ void ln_param_finalize_kernel(const double* __restrict__ partial, int slabs, int cols,
                                          float* __restrict__ dgamma, float* __restrict__ dbeta) {
-    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (c >= cols) return;
     double s1 = 0.0, s2 = 0.0;
-    for (int s = 0; s < slabs; s++) {
+    for (int s = lane; s < slabs; s += 32) {
         s1 += partial[((size_t)s * cols + c) * 2];
         s2 += partial[((size_t)s * cols + c) * 2 + 1];
     }
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    if (lane != 0) return;
     if (dgamma) dgamma[c] = (float)s1;
     if (dbeta) dbeta[c] = (float)s2;
 }
@@ -520,6 +623,10 @@ __global__ void ln_param_finalize_kernel(const double* __restrict__ partial, int
 struct ColSum {  // (x, 0)
     const float* x; int cols;
     __device__ void operator()(size_t r, int c, float& v1, float& v2) const { v1 = x[r * cols + c]; v2 = 0.f; }
+    __device__ void vec(size_t r, int c, float4& v1, float4& v2) const {
+        v1 = *reinterpret_cast<const float4*>(x + r * cols + c);
+        v2 = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
 };
 
 }  // namespace
@@ -528,17 +635,11 @@ int ncc::column_sums(float* out, const float* in, size_t rows, int cols, cudaStr
     if (cols <= 0) return NC_CUDA_OK;
     NCC_REQUIRE(out && (in || rows == 0), "column_sums: null pointer");
     if (rows == 0) { NCC_TRY(cudaMemsetAsync(out, 0, sizeof(float) * cols, st)); return NC_CUDA_OK; }
-    int col_tiles = ceil_div(cols, 32);
-    int want = (sm_count() * 4 + col_tiles - 1) / col_tiles;
-    size_t rps = (rows + want - 1) / want;
-    if (rps < 64) rps = 64;
-    int slabs = (int)((rows + rps - 1) / rps);
-    if (slabs > 65535) { slabs = 65535; rps = (rows + slabs - 1) / slabs; slabs = (int)((rows + rps - 1) / rps); }
-    double* partial = (double*)scratch(7, sizeof(double) * 2 * (size_t)slabs * cols, st);
-    if (!partial) return NC_CUDA_ERR_RUNTIME;
-    colreduce_kernel<<<dim3(col_tiles, slabs), 256, 0, st>>>(partial, rows, cols, rps, ColSum{in, cols});
-    NCC_COUNT_LAUNCH();
-    ln_param_finalize_kernel<<<ceil_div(cols, 128), 128, 0, st>>>(partial, slabs, cols, out, nullptr);
+    double* partial = nullptr;
+    int slabs = 0;
+    int rc = launch_colreduce(&partial, &slabs, rows, cols, al16(in), ColSum{in, cols}, st);
+    if (rc) return rc;
+    ln_param_finalize_kernel<<<ceil_div(cols * 32, 128), 128, 0, st>>>(partial, slabs, cols, out, nullptr);
     NCC_COUNT_LAUNCH();
     return launch_status("column_sums");
 }
@@ -588,9 +689,9 @@ int nc_cuda_batchnorm_forward_f32_ex(float* y, const float* x, const float* gamm
     if (training) {
         double* partial = nullptr;
         int slabs = 0;
-        int rc = channel_reduce(&partial, &slabs, N, C, spatial, layout, BnFwdSum{x, C}, BnFwdSumFlat{x}, st);
+        int rc = channel_reduce(&partial, &slabs, N, C, spatial, layout, BnFwdSum{x, C}, BnFwdSumFlat{x}, al16(x), st);
         if (rc) return rc;
-        bn_fwd_finalize_kernel<<<ceil_div(C, 128), 128, 0, st>>>(partial, slabs, C, (double)N * spatial, save_mean,
+        bn_fwd_finalize_kernel<<<ceil_div(C * 32, 128), 128, 0, st>>>(partial, slabs, C, (double)N * spatial, save_mean,
                                                                 save_var, run_mean, run_var, momentum);
     } else {
         bn_eval_stats_kernel<<<ceil_div(C, 128), 128, 0, st>>>(C, save_mean, save_var, run_mean, run_var);
@@ -624,11 +725,12 @@ int nc_cuda_batchnorm_backward_f32_ex(float* dx, float* dgamma, float* dbeta, co
     int slabs = 0;
     int rc = channel_reduce(&partial, &slabs, N, C, spatial, layout,
                             BnBwdSum{dy, x, relu_out, save_mean, save_var, fe, C},
-                            BnBwdSumFlat{dy, x, relu_out, save_mean, save_var, fe}, st);
+                            BnBwdSumFlat{dy, x, relu_out, save_mean, save_var, fe},
+                            al16(dy) && al16(x) && al16(relu_out) && al16(save_mean) && al16(save_var), st);
     if (rc) return rc;
     float* sums = (float*)scratch(6, sizeof(float) * 2 * (size_t)C, st);
     if (!sums) return NC_CUDA_ERR_RUNTIME;
-    bn_bwd_finalize_kernel<<<ceil_div(C, 128), 128, 0, st>>>(partial, slabs, C, dgamma, dbeta, sums);
+    bn_bwd_finalize_kernel<<<ceil_div(C * 32, 128), 128, 0, st>>>(partial, slabs, C, dgamma, dbeta, sums);
     NCC_COUNT_LAUNCH();
     const bool al = ((uintptr_t)dx % 16 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)dy % 16 == 0) &&
                     (!relu_out || (uintptr_t)relu_out % 16 == 0);
@@ -684,16 +786,11 @@ int nc_cuda_layernorm_backward_f32_ex(float* dx, float* dgamma, float* dbeta, co
     NCC_COUNT_LAUNCH();
     if (params) {
         int C = (int)cols;
-        int col_tiles = ceil_div(C, 32);
-        int want = (sm_count() * 4 + col_tiles - 1) / col_tiles;
-        size_t rps = (rows + want - 1) / want;
-        if (rps < 32) rps = 32;
-        int slabs = (int)((rows + rps - 1) / rps);
-        double* partial = (double*)scratch(7, sizeof(double) * 2 * (size_t)slabs * C, st);
-        if (!partial) return NC_CUDA_ERR_RUNTIME;
-        colreduce_kernel<<<dim3(col_tiles, slabs), 256, 0, st>>>(partial, rows, C, rps, LnParamSum{dy, x, stats, C});
-        NCC_COUNT_LAUNCH();
-        ln_param_finalize_kernel<<<ceil_div(C, 128), 128, 0, st>>>(partial, slabs, C, dgamma, dbeta);
+        double* partial = nullptr;
+        int slabs = 0;
+        int rc = launch_colreduce(&partial, &slabs, rows, C, al16(dy) && al16(x), LnParamSum{dy, x, stats, C}, st);
+        if (rc) return rc;
+        ln_param_finalize_kernel<<<ceil_div(C * 32, 128), 128, 0, st>>>(partial, slabs, C, dgamma, dbeta);
         NCC_COUNT_LAUNCH();
     }
     return launch_status("layernorm_backward");

