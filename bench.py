@@ -200,20 +200,34 @@ def run_ours(args):
     tensors = configs.upload(r, kind, data)
 
     # data parallel: one flat gradient arena, one all-reduce, 1/world folded into the update
-    arena = None
+    sync = None
+    hook_keepalive = None
     if world > 1:
+        from nocta_b200.dist import BucketedAllReduce
         lib.nc_optimizer_flatten_grads.restype = C.c_void_p
         lib.nc_optimizer_flatten_grads.argtypes = [capi.OptimizerP, C.POINTER(C.c_size_t)]
         n = C.c_size_t(0)
         ptr = lib.nc_optimizer_flatten_grads(net.optimizer, C.byref(n))
         assert ptr, "gradient arena allocation failed"
         arena = torch.as_tensor(_DevMem(ptr, n.value), device=f"cuda:{local_rank}")
+        opt = net.optimizer.contents
+        entries, off = [], 0
+        for i in range(opt.n_params):
+            pt = opt.params[i]
+            entries.append((C.addressof(pt.contents), off, pt.contents.numel))
+            off += (pt.contents.numel + 63) // 64 * 64
+        assert off == n.value
+        sync = BucketedAllReduce(arena, entries, bucket_floats=1 << 20)
+        HOOK = C.CFUNCTYPE(None, capi.TensorP, C.c_void_p)
+        hook_keepalive = HOOK(lambda leaf, ctx: sync.on_ready(C.addressof(leaf.contents)))
+        lib.nc_set_grad_ready_hook.argtypes = [HOOK, C.c_void_p]
+        lib.nc_set_grad_ready_hook(hook_keepalive, None)
         lib.nc_optimizer_set_grad_scale.argtypes = [capi.OptimizerP, C.c_double]
         lib.nc_optimizer_set_grad_scale(net.optimizer, 1.0 / world)
 
     def allreduce():
-        if arena is not None:
-            dist.all_reduce(arena)
+        if sync is not None:
+            sync.finish()
 
     def step(ts):
         loss = configs.train_step(r, net, forward, kind, ts, after_backward=allreduce)
@@ -313,7 +327,7 @@ def run_ours(args):
             "scaling": "weak", "vs_baseline": None, "dtype": {"tf32": "tf32", "3xtf32": "3xtf32", "simt": "f32"}[args.math],
             "data": "synthetic",
             "config": {"workload": w["name"], "per_gpu_batch": images, "global_batch": images * world,
-                       "parallelism": f"dp{world}", "optimizer": "sgd_momentum_0.9" if args.workload in ("vgg", "lenet") else "adam",
+                       "parallelism": f"dp{world}", "grad_buckets": (len(sync.buckets) if sync else 0), "optimizer": "sgd_momentum_0.9" if args.workload in ("vgg", "lenet") else "adam",
                        "l2": "per-step working set (~3 GB of activations) exceeds the 126 MB L2; no explicit flush"},
             "clocks": clocks,
             "e2e": {"value": images * world * args.steps / (ms_e2e / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d,

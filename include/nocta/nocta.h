@@ -225,6 +225,11 @@ void nc_node_free(nc_node* node);
 nc_error nc_backward(nc_tensor* t, nc_tensor* grad_output);
 nc_error nc_backward_scalar(nc_tensor* loss);
 nc_node** nc_build_topo(nc_tensor* t, size_t* n_nodes);
+/* new: called during nc_backward each time a leaf tensor's gradient has been accumulated (its kernel is
+ * queued on the stream).  Data-parallel code uses it to start the all-reduce of a gradient bucket while
+ * the backward sweep continues.  Pass NULL to remove the hook. */
+typedef void (*nc_grad_ready_fn)(nc_tensor* leaf, void* ctx);
+void nc_set_grad_ready_hook(nc_grad_ready_fn fn, void* ctx);
 typedef enum { NC_GRAD_REPLACE, NC_GRAD_ACCUMULATE } nc_grad_mode;
 void nc_set_grad_mode(nc_grad_mode mode);
 nc_grad_mode nc_get_grad_mode(void);

@@ -114,6 +114,10 @@ static nc_tensor* add_into(nc_tensor* a, nc_tensor* b) {
     return a;
 }
 
+static nc_grad_ready_fn g_ready_fn = NULL;
+static void* g_ready_ctx = NULL;
+void nc_set_grad_ready_hook(nc_grad_ready_fn fn, void* ctx) { g_ready_fn = fn; g_ready_ctx = ctx; }
+
 static void accumulate_leaf(nc_tensor* leaf, nc_tensor* g) {
     if (!leaf->requires_grad || leaf->numel != g->numel) return;
     if (!leaf->grad) {
@@ -122,6 +126,9 @@ static void accumulate_leaf(nc_tensor* leaf, nc_tensor* g) {
         nc_tensor_fill_(leaf->grad, 0.0);
     }
     nc_add_(leaf->grad, g);
+    /* the accumulate kernel is queued: a data-parallel caller may now queue this gradient's all-reduce
+     * behind it while the rest of the backward sweep keeps the device busy */
+    if (g_ready_fn) g_ready_fn(leaf, g_ready_ctx);
 }
 
 nc_error nc_backward(nc_tensor* t, nc_tensor* grad_output) {
