@@ -7,6 +7,11 @@
 //          one reduction step is ONE 4-D TMA box at shifted (w, h) coordinates; out-of-bounds
 //          elements are zero-filled by TMA, which is the padding.  Used for forward and, with
 //          flipped / channel-transposed weights, for dX.
+//   CONVT  the same convolution with the operand roles swapped: rows = 128 output channels (the weight
+//          tile is the A operand), cols = 256 output pixels (one 4-D TMA box is the B operand).  Every
+//          tcgen05.mma with M = 128 occupies the tensor pipe for at least 128 cycles (the A operand is
+//          read from shared memory at 32 B per cycle), so only N = 256 keeps the pipe full; with pixels
+//          on N that holds for any channel count, while channels on N runs at Cout/256 of peak.
 //   DW     weight gradient: rows = output channels, cols = (kh, kw, ci), reduction = 32-pixel
 //          boxes; both operands MN-major; split over the reduction with an ordered second stage.
 //
@@ -22,7 +27,7 @@
 
 namespace tc {
 
-enum { KIND_GEMM = 0, KIND_CONV = 1, KIND_DW = 2 };
+enum { KIND_GEMM = 0, KIND_CONV = 1, KIND_DW = 2, KIND_CONVT = 3 };
 
 struct TcParams {
     int kind;
@@ -43,6 +48,9 @@ struct TcParams {
     int wrows;             // CONV: rows per (kh,kw) block of the packed weights (= output channels)
     int Cin;               // DW: input channels (column index -> (shift, ci))
     int desc_variant;
+    int lbw, lbh;                  // CONVT: log2 of the pixel box width / height
+    int tiles_m, tiles_n, splits;  // persistent tile walk
+    int stages;                    // operand ring depth
     unsigned int* err;
 };
 
@@ -161,7 +169,7 @@ constexpr int BK = 32;                 // 32 floats = one 128-byte swizzle row
 constexpr int A_BYTES = BM * BK * 4;   // 16 KB
 constexpr int CHUNK_BYTES = 32 * BK * 4;  // one 32 x 32 MN-major chunk: 4 KB
 constexpr int kMaxStages = 8;
-constexpr int kSmemBudget = 196 * 1024;
+constexpr int kSmemBudget = 196 * 1024;  // one persistent CTA per SM
 
 template <int BN, int MODE>
 struct TileCfg {
@@ -176,19 +184,24 @@ struct TileCfg {
     // in FP32 in the epilogue: the tensor core's own accumulation is the largest error term left in
     // that mode and it grows with the number of additions into one accumulator.
     static constexpr int NACC = MODE == 2 ? (512 / ACC_COLS > 4 ? 4 : 512 / ACC_COLS) : 1;
-    static constexpr int TMEM_COLS = ACC_COLS * NACC;
+    // plain TF32 keeps two accumulator buffers so the epilogue of one tile overlaps the MMAs of the next;
+    // the converting modes use the epilogue warps during the main loop, so one buffer is enough there
+    static constexpr int NBUF = MODE == 0 ? 2 : 1;
+    static constexpr int TMEM_COLS = ACC_COLS * NACC * NBUF;
 };
 
 template <int BN, bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(192, 1)
 tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
     using Cfg = TileCfg<BN, MODE>;
-    constexpr int STAGES = Cfg::STAGES;
+    constexpr int NBUF = Cfg::NBUF;  // accumulator buffers in tensor memory (2 = epilogue overlaps the next tile)
+    const int STAGES = p.stages;
     extern __shared__ uint8_t dyn_smem[];
     __shared__ __align__(8) uint64_t bar_full[kMaxStages];
     __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
     __shared__ __align__(8) uint64_t bar_conv[kMaxStages];
-    __shared__ __align__(8) uint64_t bar_acc;
+    __shared__ __align__(8) uint64_t bar_acc_full[2];
+    __shared__ __align__(8) uint64_t bar_acc_empty[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -196,30 +209,16 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     const uint32_t tiles_base = (smem_u32(dyn_smem) + 1023u) & ~1023u;
     uint8_t* tiles_generic = dyn_smem + (tiles_base - smem_u32(dyn_smem));
 
-    const int n_tile = blockIdx.x, m_tile = blockIdx.y, z = blockIdx.z;
-    const int kt_begin = z * p.k_tiles_per_split;
-    int kt_end = kt_begin + p.k_tiles_per_split;
-    if (kt_end > p.num_k_tiles) kt_end = p.num_k_tiles;
-    const int nk = kt_end - kt_begin;
-
-    const int m0 = m_tile * BM, n0 = n_tile * BN;
-    // CONV: decode the output pixel box of this m tile
-    int cw0 = 0, ch0 = 0, cn0 = 0;
-    if (p.kind == KIND_CONV) {
-        int tw = m_tile % p.tiles_w;
-        int t = m_tile / p.tiles_w;
-        int th = t % p.tiles_h;
-        int tn = t / p.tiles_h;
-        cw0 = tw * p.bw; ch0 = th * p.bh; cn0 = tn * p.bn;
-    }
-
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(smem_u32(&bar_full[s]), 1);
             mbar_init(smem_u32(&bar_empty[s]), 1);
             mbar_init(smem_u32(&bar_conv[s]), 128);
         }
-        mbar_init(smem_u32(&bar_acc), 1);
+        for (int b = 0; b < 2; b++) {
+            mbar_init(smem_u32(&bar_acc_full[b]), 1);
+            mbar_init(smem_u32(&bar_acc_empty[b]), 128);
+        }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -236,50 +235,88 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     const uint32_t tmem_base = tmem_slot;
     volatile int* abortp = &abort_flag;
 
+    // Persistent CTA: walks output tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...
+    // t -> (n_tile fastest, then m_tile, then reduction split z).
+    const int total_tiles = p.tiles_m * p.tiles_n * p.splits;
+
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
-            for (int i = 0; i < nk; i++) {
-                const int s = i % STAGES, it = i / STAGES;
-                if (!mbar_wait(smem_u32(&bar_empty[s]), (uint32_t)((it & 1) ^ 1), p.err, 0x100u + s, abortp)) break;
-                const uint32_t full = smem_u32(&bar_full[s]);
-                mbar_expect_tx(full, (uint32_t)Cfg::OPER_BYTES);
-                const uint32_t a_dst = tiles_base + (uint32_t)s * Cfg::STAGE_BYTES;
-                const uint32_t b_dst = a_dst + A_BYTES;
-                const int kt = kt_begin + i;
-                if (p.kind == KIND_GEMM) {
-                    const int k0 = kt * BK;
-                    if (!A_MN) {
-                        tma_2d(a_dst, &tmA, k0, m0, full);
+            // One thread feeds the whole CTA, so its loop is kept free of divisions and runtime modulo:
+            // ring slot / phase, filter tap and channel chunk are running counters.
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int n_tile = t % p.tiles_n, r_ = t / p.tiles_n, m_tile = r_ % p.tiles_m, z = r_ / p.tiles_m;
+                const int kt_begin = z * p.k_tiles_per_split;
+                int kt_end = kt_begin + p.k_tiles_per_split;
+                if (kt_end > p.num_k_tiles) kt_end = p.num_k_tiles;
+                const int m0 = m_tile * BM, n0 = n_tile * BN;
+                // pixel box of this tile (CONV: the m tile, CONVT: the n tile)
+                int pw0 = 0, ph0 = 0, pn0 = 0;
+                if (p.kind == KIND_CONV || p.kind == KIND_CONVT) {
+                    const int pt = p.kind == KIND_CONV ? m_tile : n_tile;
+                    const int tw = pt % p.tiles_w, tt = pt / p.tiles_w;
+                    pw0 = tw * p.bw; ph0 = (tt % p.tiles_h) * p.bh; pn0 = (tt / p.tiles_h) * p.bn;
+                }
+                // running decomposition of kt: CONV/CONVT (tap kh,kw ; chunk cc), DW (box tw,th,tn)
+                int cc = 0, kh = 0, kw = 0, shift = 0, dtw = 0, dth = 0, dtn = 0, dw_ci0 = 0, dw_kh0 = 0, dw_kw0 = 0;
+                if (p.kind == KIND_CONV || p.kind == KIND_CONVT) {
+                    shift = kt_begin / p.cchunks; cc = kt_begin - shift * p.cchunks;
+                    kh = shift / p.kW; kw = shift - kh * p.kW;
+                } else if (p.kind == KIND_DW) {
+                    dtw = kt_begin % p.tiles_w;
+                    const int tt = kt_begin / p.tiles_w;
+                    dth = tt % p.tiles_h; dtn = tt / p.tiles_h;
+                    const int dshift = n0 / p.Cin;
+                    dw_ci0 = n0 - dshift * p.Cin;
+                    dw_kh0 = dshift / p.kW; dw_kw0 = dshift - dw_kh0 * p.kW;
+                }
+                for (int kt = kt_begin; kt < kt_end; kt++) {
+                    if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, p.err, 0x100u + s, abortp)) { ok = false; break; }
+                    const uint32_t full = smem_u32(&bar_full[s]);
+                    mbar_expect_tx(full, (uint32_t)Cfg::OPER_BYTES);
+                    const uint32_t a_dst = tiles_base + (uint32_t)s * Cfg::STAGE_BYTES;
+                    const uint32_t b_dst = a_dst + A_BYTES;
+                    if (p.kind == KIND_GEMM) {
+                        const int k0 = kt * BK;
+                        if (!A_MN) {
+                            tma_2d(a_dst, &tmA, k0, m0, full);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < BM / 32; c++) tma_2d(a_dst + c * CHUNK_BYTES, &tmA, m0 + 32 * c, k0, full);
+                        }
+                        if (!B_MN) {
+                            tma_2d(b_dst, &tmB, k0, n0, full);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < BN / 32; c++) tma_2d(b_dst + c * CHUNK_BYTES, &tmB, n0 + 32 * c, k0, full);
+                        }
+                    } else if (p.kind == KIND_CONV) {
+                        tma_4d(a_dst, &tmA, cc * 32, pw0 + kw - p.pad, ph0 + kh - p.pad, pn0, full);
+                        tma_2d(b_dst, &tmB, cc * 32, shift * p.wrows + n0, full);
+                    } else if (p.kind == KIND_CONVT) {
+                        tma_2d(a_dst, &tmA, cc * 32, shift * p.wrows + m0, full);
+                        tma_4d(b_dst, &tmB, cc * 32, pw0 + kw - p.pad, ph0 + kh - p.pad, pn0, full);
                     } else {
+                        const int w0 = dtw * p.bw, h0 = dth * p.bh, nn0 = dtn * p.bn;
 #pragma unroll
-                        for (int c = 0; c < BM / 32; c++) tma_2d(a_dst + c * CHUNK_BYTES, &tmA, m0 + 32 * c, k0, full);
+                        for (int c = 0; c < BM / 32; c++) tma_4d(a_dst + c * CHUNK_BYTES, &tmA, m0 + 32 * c, w0, h0, nn0, full);
+                        // column chunk c covers columns n0 + 32c .. : (tap, ci0) advance by 32 channels per chunk
+                        int ci0 = dw_ci0, dkh = dw_kh0, dkw = dw_kw0;
+#pragma unroll
+                        for (int c = 0; c < BN / 32; c++) {
+                            tma_4d(b_dst + c * CHUNK_BYTES, &tmB, ci0, w0 + dkw - p.pad, h0 + dkh - p.pad, nn0, full);
+                            ci0 += 32;
+                            if (ci0 >= p.Cin) { ci0 = 0; if (++dkw == p.kW) { dkw = 0; dkh++; } }
+                        }
+                        if (++dtw == p.tiles_w) { dtw = 0; if (++dth == p.tiles_h) { dth = 0; dtn++; } }
                     }
-                    if (!B_MN) {
-                        tma_2d(b_dst, &tmB, k0, n0, full);
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < BN / 32; c++) tma_2d(b_dst + c * CHUNK_BYTES, &tmB, n0 + 32 * c, k0, full);
+                    if (p.kind == KIND_CONV || p.kind == KIND_CONVT) {
+                        if (++cc == p.cchunks) { cc = 0; shift++; if (++kw == p.kW) { kw = 0; kh++; } }
                     }
-                } else if (p.kind == KIND_CONV) {
-                    const int shift = kt / p.cchunks, cc = kt - shift * p.cchunks;
-                    const int kh = shift / p.kW, kw = shift - kh * p.kW;
-                    tma_4d(a_dst, &tmA, cc * 32, cw0 + kw - p.pad, ch0 + kh - p.pad, cn0, full);
-                    tma_2d(b_dst, &tmB, cc * 32, shift * p.wrows + n0, full);
-                } else {
-                    const int tw = kt % p.tiles_w;
-                    const int t = kt / p.tiles_w;
-                    const int th = t % p.tiles_h, tn = t / p.tiles_h;
-                    const int w0 = tw * p.bw, h0 = th * p.bh, nn0 = tn * p.bn;
-#pragma unroll
-                    for (int c = 0; c < BM / 32; c++) tma_4d(a_dst + c * CHUNK_BYTES, &tmA, m0 + 32 * c, w0, h0, nn0, full);
-#pragma unroll
-                    for (int c = 0; c < BN / 32; c++) {
-                        const int j = n0 + 32 * c;
-                        const int shift = j / p.Cin, ci0 = j - shift * p.Cin;
-                        const int kh = shift / p.kW, kw = shift - kh * p.kW;
-                        tma_4d(b_dst + c * CHUNK_BYTES, &tmB, ci0, w0 + kw - p.pad, h0 + kh - p.pad, nn0, full);
-                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
             }
         }
@@ -293,77 +330,162 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
             // MN-major: rows are reduction indices, 128 B (32 elements of M/N) each; the swizzle atom is
             // 4 rows (SBO = 512 B between atoms along k), 32-element chunks are CHUNK_BYTES apart (LBO);
             // a k-step of 8 rows advances 1024 B.
-            uint32_t lbo_a = A_MN ? CHUNK_BYTES : 16u, sbo_a = A_MN ? 512u : 1024u;
-            uint32_t lbo_b = B_MN ? CHUNK_BYTES : 16u, sbo_b = B_MN ? 512u : 1024u;
-            if (p.desc_variant == 1) {  // bring-up alternative: swapped roles for MN-major operands
-                if (A_MN) { lbo_a = 512u; sbo_a = CHUNK_BYTES; }
-                if (B_MN) { lbo_b = 512u; sbo_b = CHUNK_BYTES; }
-            }
+            const uint32_t lbo_a = A_MN ? CHUNK_BYTES : 16u, sbo_a = A_MN ? 512u : 1024u;
+            const uint32_t lbo_b = B_MN ? CHUNK_BYTES : 16u, sbo_b = B_MN ? 512u : 1024u;
             const uint32_t lay_a = A_MN ? 1u : 2u, lay_b = B_MN ? 1u : 2u;
             const uint32_t kstep_a = A_MN ? 1024u : 32u, kstep_b = B_MN ? 1024u : 32u;
+            // descriptors are built once; a ring slot or k-step only moves the 14-bit start-address field
+            const uint64_t da0 = smem_desc(tiles_base, lbo_a, sbo_a, lay_a);
+            const uint64_t db0 = smem_desc(tiles_base + A_BYTES, lbo_b, sbo_b, lay_b);
+            int s = 0;
+            uint32_t ph = 0, tile_iter = 0;
             bool ok = true;
-            for (int i = 0; i < nk && ok; i++) {
-                const int s = i % STAGES, it = i / STAGES;
-                const uint32_t ready = MODE == 0 ? smem_u32(&bar_full[s]) : smem_u32(&bar_conv[s]);
-                if (!mbar_wait(ready, (uint32_t)(it & 1), p.err, 0x200u + s, abortp)) { ok = false; break; }
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, tile_iter++) {
+                const int z = (t / p.tiles_n) / p.tiles_m;
+                const int kt_begin = z * p.k_tiles_per_split;
+                int kt_end = kt_begin + p.k_tiles_per_split;
+                if (kt_end > p.num_k_tiles) kt_end = p.num_k_tiles;
+                const int nk = kt_end - kt_begin;
+                const uint32_t ab = tile_iter % NBUF;
+                // wait until the epilogue has drained this accumulator buffer (first use passes at once)
+                if (!mbar_wait(smem_u32(&bar_acc_empty[ab]), ((tile_iter / NBUF) & 1u) ^ 1u, p.err, 0x500u + ab, abortp)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t a_base = tiles_base + (uint32_t)s * Cfg::STAGE_BYTES;
-                const uint32_t b_base = a_base + A_BYTES;
+                const uint32_t acc_base = tmem_base + ab * (uint32_t)(Cfg::NACC * Cfg::ACC_COLS);
+                for (int i = 0; i < nk; i++) {
+                    const uint32_t ready = MODE == 0 ? smem_u32(&bar_full[s]) : smem_u32(&bar_conv[s]);
+                    if (!mbar_wait(ready, ph, p.err, 0x200u + s, abortp)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t soff = (uint64_t)(((uint32_t)s * (uint32_t)Cfg::STAGE_BYTES) >> 4);
 #pragma unroll
-                for (int ks = 0; ks < BK / 8; ks++) {
-                    const uint64_t da = smem_desc(a_base + ks * kstep_a, lbo_a, sbo_a, lay_a);
-                    const uint64_t db = smem_desc(b_base + ks * kstep_b, lbo_b, sbo_b, lay_b);
-                    if (MODE == 2) {
-                        // accumulator (ks % NACC); small cross terms first, then the main product
-                        const uint32_t acc = tmem_base + (uint32_t)((ks % Cfg::NACC) * Cfg::ACC_COLS);
-                        const bool first = (i == 0) && (ks < Cfg::NACC);
-                        const uint64_t da_lo = smem_desc(a_base + Cfg::OPER_BYTES + ks * kstep_a, lbo_a, sbo_a, lay_a);
-                        const uint64_t db_lo = smem_desc(b_base + Cfg::OPER_BYTES + ks * kstep_b, lbo_b, sbo_b, lay_b);
-                        umma_tf32(acc, da_lo, db, idesc, first ? 0u : 1u);
-                        umma_tf32(acc, da, db_lo, idesc, 1u);
-                        umma_tf32(acc, da, db, idesc, 1u);
-                    } else {
-                        umma_tf32(tmem_base, da, db, idesc, (uint32_t)((i | ks) != 0));
+                    for (int ks = 0; ks < BK / 8; ks++) {
+                        const uint64_t da = da0 + soff + (uint64_t)((ks * kstep_a) >> 4);
+                        const uint64_t db = db0 + soff + (uint64_t)((ks * kstep_b) >> 4);
+                        if (MODE == 2) {
+                            // accumulator (ks % NACC); small cross terms first, then the main product
+                            const uint32_t acc = acc_base + (uint32_t)((ks % Cfg::NACC) * Cfg::ACC_COLS);
+                            const bool first = (i == 0) && (ks < Cfg::NACC);
+                            const uint64_t da_lo = da + (uint64_t)(Cfg::OPER_BYTES >> 4);
+                            const uint64_t db_lo = db + (uint64_t)(Cfg::OPER_BYTES >> 4);
+                            umma_tf32(acc, da_lo, db, idesc, first ? 0u : 1u);
+                            umma_tf32(acc, da, db_lo, idesc, 1u);
+                            umma_tf32(acc, da, db, idesc, 1u);
+                        } else {
+                            umma_tf32(acc_base, da, db, idesc, (uint32_t)((i | ks) != 0));
+                        }
                     }
+                    umma_commit(smem_u32(&bar_empty[s]));
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
-                umma_commit(smem_u32(&bar_empty[s]));
+                if (ok) umma_commit(smem_u32(&bar_acc_full[ab]));
             }
-            umma_commit(smem_u32(&bar_acc));
         }
     } else {
         // ------------------------------ converter + epilogue warps ------------------------------
         const int te = threadIdx.x - 64;  // 0..127
+        const int q = warp & 3;           // TMEM lane quadrant this warp may read
+        const int r = q * 32 + lane;
+        int s = 0;
+        uint32_t ph = 0, tile_iter = 0;
         bool ok = true;
-        if (MODE != 0) {
-            constexpr int NV = Cfg::OPER_BYTES / 16;
-            for (int i = 0; i < nk && ok; i++) {
-                const int s = i % STAGES, it = i / STAGES;
-                if (!mbar_wait(smem_u32(&bar_full[s]), (uint32_t)(it & 1), p.err, 0x300u + s, abortp)) { ok = false; break; }
-                float4* buf = reinterpret_cast<float4*>(tiles_generic + (size_t)s * Cfg::STAGE_BYTES);
-                float4* lo = reinterpret_cast<float4*>(tiles_generic + (size_t)s * Cfg::STAGE_BYTES + Cfg::OPER_BYTES);
-                for (int j = te; j < NV; j += 128) {
-                    float4 v = buf[j];
-                    float4 h = make_float4(ncc::round_tf32(v.x), ncc::round_tf32(v.y), ncc::round_tf32(v.z), ncc::round_tf32(v.w));
-                    buf[j] = h;
-                    if (MODE == 2)
-                        lo[j] = make_float4(ncc::round_tf32(v.x - h.x), ncc::round_tf32(v.y - h.y),
-                                            ncc::round_tf32(v.z - h.z), ncc::round_tf32(v.w - h.w));
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, tile_iter++) {
+            const int n_tile = t % p.tiles_n, r_ = t / p.tiles_n, m_tile = r_ % p.tiles_m, z = r_ / p.tiles_m;
+            const int kt_begin = z * p.k_tiles_per_split;
+            int kt_end = kt_begin + p.k_tiles_per_split;
+            if (kt_end > p.num_k_tiles) kt_end = p.num_k_tiles;
+            const int nk = kt_end - kt_begin;
+            const int m0 = m_tile * BM, n0 = n_tile * BN;
+            if (MODE != 0) {
+                constexpr int NV = Cfg::OPER_BYTES / 16;
+                for (int i = 0; i < nk && ok; i++) {
+                    if (!mbar_wait(smem_u32(&bar_full[s]), ph, p.err, 0x300u + s, abortp)) { ok = false; break; }
+                    float4* buf = reinterpret_cast<float4*>(tiles_generic + (size_t)s * Cfg::STAGE_BYTES);
+                    float4* lo = reinterpret_cast<float4*>(tiles_generic + (size_t)s * Cfg::STAGE_BYTES + Cfg::OPER_BYTES);
+                    for (int j = te; j < NV; j += 128) {
+                        float4 v = buf[j];
+                        float4 h = make_float4(ncc::round_tf32(v.x), ncc::round_tf32(v.y), ncc::round_tf32(v.z), ncc::round_tf32(v.w));
+                        buf[j] = h;
+                        if (MODE == 2)
+                            lo[j] = make_float4(ncc::round_tf32(v.x - h.x), ncc::round_tf32(v.y - h.y),
+                                                ncc::round_tf32(v.z - h.z), ncc::round_tf32(v.w - h.w));
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    mbar_arrive(smem_u32(&bar_conv[s]));
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive(smem_u32(&bar_conv[s]));
             }
-        }
-        if (ok) ok = mbar_wait(smem_u32(&bar_acc), 0u, p.err, 0x400u, abortp);
-        // all 32 lanes of a warp must agree before the aligned tcgen05.ld
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
+            const uint32_t ab = tile_iter % NBUF;
+            if (ok) ok = mbar_wait(smem_u32(&bar_acc_full[ab]), (tile_iter / NBUF) & 1u, p.err, 0x400u + ab, abortp);
+            // all 32 lanes of a warp must agree before the aligned tcgen05.ld
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
             tc_fence_after();
-            const int q = warp & 3;  // TMEM lane quadrant this warp may read
-            const int r = q * 32 + lane;
+            const uint32_t acc_base = tmem_base + ab * (uint32_t)(Cfg::NACC * Cfg::ACC_COLS);
+            if (p.kind == KIND_CONVT) {
+                // lane = output channel, column = pixel of the box; channels-last store: for one column the
+                // 32 lanes of a warp write 32 consecutive floats
+                const int co = m0 + r;
+                const bool co_ok = co < p.M;
+                const float bv = (co_ok && p.bias) ? p.bias[co] : 0.f;
+                const int tw = n_tile % p.tiles_w, tt = n_tile / p.tiles_w;
+                const int pw0 = tw * p.bw, ph0 = (tt % p.tiles_h) * p.bh, pn0 = (tt / p.tiles_h) * p.bn;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(acc_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+                    tmem_ld_wait();
+                    if (Cfg::NACC > 1) {
+#pragma unroll 1
+                        for (int a = 1; a < Cfg::NACC; a++) {
+                            uint32_t u[32];
+                            tmem_ld32(acc_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * Cfg::ACC_COLS + c0), u);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(u[j]));
+                        }
+                    }
+                    if (c0 + 32 >= BN) {
+                        tc_fence_before();
+                        mbar_arrive(smem_u32(&bar_acc_empty[ab]));
+                    }
+                    // the 32 columns of a chunk are runs of consecutive w inside one image row: the 64-bit
+                    // address is formed once per run, each store then adds a small constant multiple of ldd
+                    const int ldd = (int)p.ldd;
+                    if (p.bw >= 32) {
+                        const int w = pw0 + (c0 & (p.bw - 1));
+                        const int h = ph0 + ((c0 >> p.lbw) & (p.bh - 1));
+                        const int n = pn0 + (c0 >> (p.lbw + p.lbh));
+                        if (co_ok && h < p.Ho && n < p.Nimg) {
+                            float* dst = p.D + (((long long)n * p.Ho + h) * p.Wo + w) * p.ldd + co;
+                            const int lim = p.Wo - w;  // columns j < lim are inside the image
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (j < lim) dst[j * ldd] = __uint_as_float(v[j]) + bv;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j0 = 0; j0 < 32; j0 += 8) {  // bw is 8 or 16: runs of 8 never cross a row
+                            const int pj = c0 + j0;
+                            const int w = pw0 + (pj & (p.bw - 1));
+                            const int h = ph0 + ((pj >> p.lbw) & (p.bh - 1));
+                            const int n = pn0 + (pj >> (p.lbw + p.lbh));
+                            if (co_ok && h < p.Ho && n < p.Nimg) {
+                                float* dst = p.D + (((long long)n * p.Ho + h) * p.Wo + w) * p.ldd + co;
+                                const int lim = p.Wo - w;
+#pragma unroll
+                                for (int j = 0; j < 8; j++)
+                                    if (j < lim) dst[j * ldd] = __uint_as_float(v[j0 + j]) + bv;
+                            }
+                        }
+                    }
+                }
+                continue;
+            }
             // where does this row go?
             long long row_off = -1;
             if (p.kind == KIND_CONV) {
-                const int iw = r % p.bw, t = r / p.bw, ih = t % p.bh, in_ = t / p.bh;
+                const int tw = m_tile % p.tiles_w, tt = m_tile / p.tiles_w;
+                const int cw0 = tw * p.bw, ch0 = (tt % p.tiles_h) * p.bh, cn0 = (tt / p.tiles_h) * p.bn;
+                const int iw = r % p.bw, t2 = r / p.bw, ih = t2 % p.bh, in_ = t2 / p.bh;
                 const int w = cw0 + iw, h = ch0 + ih, n = cn0 + in_;
                 if (w < p.Wo && h < p.Ho && n < p.Nimg) row_off = (((long long)n * p.Ho + h) * p.Wo + w) * p.ldd;
             } else {
@@ -377,17 +499,22 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 if (n0 + c0 >= p.N) break;  // uniform across the CTA
                 uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+                tmem_ld32(acc_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
                 tmem_ld_wait();
                 if (Cfg::NACC > 1) {
 #pragma unroll 1
                     for (int a = 1; a < Cfg::NACC; a++) {
                         uint32_t u[32];
-                        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * Cfg::ACC_COLS + c0), u);
+                        tmem_ld32(acc_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * Cfg::ACC_COLS + c0), u);
                         tmem_ld_wait();
 #pragma unroll
                         for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(u[j]));
                     }
+                }
+                if (c0 + 32 >= BN || n0 + c0 + 32 >= p.N) {
+                    // last chunk read: the accumulator buffer may be overwritten by the tile after next
+                    tc_fence_before();
+                    mbar_arrive(smem_u32(&bar_acc_empty[ab]));
                 }
                 if (row_off < 0) continue;
                 float* dst = base + row_off + n0 + c0;
@@ -562,8 +689,14 @@ struct ProfState {
 static ProfState g_prof;
 
 template <int BN, bool A_MN, bool B_MN, int MODE>
-static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const TcParams& p, dim3 grid, cudaStream_t st) {
+static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const TcParams& p_in, dim3 tiles, cudaStream_t st) {
     using Cfg = TileCfg<BN, MODE>;
+    TcParams p = p_in;
+    p.tiles_n = (int)tiles.x; p.tiles_m = (int)tiles.y; p.splits = (int)tiles.z;
+    p.stages = Cfg::STAGES;
+    const long long total = (long long)tiles.x * tiles.y * tiles.z;
+    const int sms = ncc::sm_count();
+    dim3 grid((unsigned)(total < sms ? total : sms), 1, 1);
     static bool attr_set = false;
     auto kern = tc_kernel<BN, A_MN, B_MN, MODE>;
     if (!attr_set) {
@@ -643,7 +776,6 @@ int gemm(float* D, int ldd, const float* A, int lda, bool a_mn, const float* B, 
     p.desc_variant = g_desc_variant;
     p.err = ncc::device_error_word();
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + bn - 1) / bn;
-    if (tiles_m > 65535) return NC_CUDA_ERR_UNSUPPORTED;
     int splits, kps;
     pick_splits(tiles_m * tiles_n, p.num_k_tiles, &splits, &kps);
     p.k_tiles_per_split = kps;
@@ -668,9 +800,9 @@ int gemm(float* D, int ldd, const float* A, int lda, bool a_mn, const float* B, 
 }
 
 // Pixel box (bw, bh, bn) with bw*bh*bn == pixels that wastes the fewest rows for this image size.
-static void pick_box(int pixels, int Wd, int Hd, int Nd, int* bw, int* bh, int* bn) {
+static void pick_box(int pixels, int Wd, int Hd, int Nd, int* bw, int* bh, int* bn, int min_w = 1) {
     long long best = -1;
-    for (int w = 1; w <= pixels; w *= 2)
+    for (int w = min_w; w <= pixels; w *= 2)
         for (int h = 1; w * h <= pixels; h *= 2) {
             int n = pixels / (w * h);
             if (w * h * n != pixels || w > 256 || h > 256 || n > 256) continue;
@@ -688,6 +820,39 @@ int conv_nhwc(float* y, const float* x, const float* wpacked, const float* bias,
     if (Ho <= 0 || Wo <= 0) return NC_CUDA_ERR_UNSUPPORTED;
     if ((Cin & 3) || (Cout & 3) || Cin < 16 || Cout < 16) return NC_CUDA_ERR_UNSUPPORTED;
     if ((long long)N * Ho * Wo < 128) return NC_CUDA_ERR_UNSUPPORTED;
+    if ((long long)N * Ho * Wo >= 1024 && kH * kW * Cout >= 128) {
+        // pixels on the N side (256 per tile), channels on the M side
+        int bw = 1, bh = 1, bnn = 1;
+        pick_box(256, Wo, Ho, N, &bw, &bh, &bnn, 8);
+        CUtensorMap ta, tb;
+        unsigned long long wd[2] = {(unsigned long long)Cin, (unsigned long long)kH * kW * Cout};
+        unsigned long long ws[1] = {(unsigned long long)Cin};
+        unsigned wb[2] = {32, 128};
+        if (!make_map(&ta, wpacked, 2, wd, ws, wb, false)) return NC_CUDA_ERR_UNSUPPORTED;
+        unsigned long long dims[4] = {(unsigned long long)Cin, (unsigned long long)W, (unsigned long long)H, (unsigned long long)N};
+        unsigned long long str[3] = {(unsigned long long)Cin, (unsigned long long)W * Cin, (unsigned long long)H * W * Cin};
+        unsigned box[4] = {32, (unsigned)bw, (unsigned)bh, (unsigned)bnn};
+        if (!make_map(&tb, x, 4, dims, str, box, false)) return NC_CUDA_ERR_UNSUPPORTED;
+        TcParams p = {};
+        p.kind = KIND_CONVT;
+        p.M = Cout;
+        p.cchunks = (Cin + 31) / 32;
+        p.num_k_tiles = kH * kW * p.cchunks;
+        p.k_tiles_per_split = p.num_k_tiles;
+        p.D = y; p.ldd = Cout; p.bias = bias; p.alpha = 1.f; p.beta = 0.f;
+        p.bw = bw; p.bh = bh; p.bn = bnn;
+        for (p.lbw = 0; (1 << p.lbw) < bw; p.lbw++) {}
+        for (p.lbh = 0; (1 << p.lbh) < bh; p.lbh++) {}
+        p.tiles_w = (Wo + bw - 1) / bw; p.tiles_h = (Ho + bh - 1) / bh;
+        p.Ho = Ho; p.Wo = Wo; p.Nimg = N;
+        p.kW = kW; p.pad = pad; p.wrows = Cout;
+        p.err = ncc::device_error_word();
+        const long long tiles_px = (long long)p.tiles_w * p.tiles_h * ((N + bnn - 1) / bnn);
+        p.N = (int)(tiles_px * 256 < 0x7fffffffLL ? tiles_px * 256 : 0x7fffffff);
+        dim3 tiles((unsigned)tiles_px, (unsigned)((Cout + BM - 1) / BM), 1);
+        g_prof.next_flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
+        return launch_mode<256, false, false>(mode, ta, tb, p, tiles, st);
+    }
     const int bn_cols = pick_bn(Cout, mode);
     int bw = 1, bh = 1, bnn = 1;
     pick_box(128, Wo, Ho, N, &bw, &bh, &bnn);
@@ -716,7 +881,6 @@ int conv_nhwc(float* y, const float* x, const float* wpacked, const float* bias,
     p.desc_variant = g_desc_variant;
     p.err = ncc::device_error_word();
     const long long tiles_m = (long long)p.tiles_w * p.tiles_h * ((N + bnn - 1) / bnn);
-    if (tiles_m > 65535) return NC_CUDA_ERR_UNSUPPORTED;
     dim3 grid((Cout + bn_cols - 1) / bn_cols, (unsigned)tiles_m, 1);
     g_prof.next_flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
     return launch_bn<false, false>(bn_cols, mode, ta, tb, p, grid, st);
