@@ -226,8 +226,10 @@ void nc_cuda_batchnorm_backward_f32(float* grad_input, float* grad_gamma, float*
                                     const float* save_mean, const float* save_var,
                                     int N, int C, int spatial, float eps);                               /* :137-147 */
 /* new: layout 0 = NCHW (N, C, spatial), 1 = NHWC (N*spatial, C).  save_var holds the biased batch
- * variance (as on the reference CPU path).  relu != 0 fuses max(0, .) into the forward output;
- * the backward then takes the forward OUTPUT y as `relu_out` and masks grad_output where y <= 0. */
+ * variance (as on the reference CPU path).  relu != 0 fuses max(0, .) into the forward output; the
+ * backward then masks grad_output where that output was <= 0, either by reading it (`relu_out` = the
+ * forward output y) or, with relu_out == NULL and relu_recompute != 0, by re-evaluating
+ * gamma * x_hat + beta from x (`relu_beta` = the forward beta, may be NULL), which reads no extra tensor. */
 int nc_cuda_batchnorm_forward_f32_ex(float* output, const float* input, const float* gamma, const float* beta,
                                      float* running_mean, float* running_var, float* save_mean, float* save_var,
                                      int N, int C, int spatial, double momentum, double eps, int training,
@@ -235,6 +237,7 @@ int nc_cuda_batchnorm_forward_f32_ex(float* output, const float* input, const fl
 int nc_cuda_batchnorm_backward_f32_ex(float* grad_input, float* grad_gamma, float* grad_beta,
                                       const float* grad_output, const float* input, const float* gamma,
                                       const float* save_mean, const float* save_var, const float* relu_out,
+                                      const float* relu_beta, int relu_recompute,
                                       int N, int C, int spatial, double eps, int layout, void* stream);
 
 /* ---------------- layer norm (new; CPU semantics src/nn/batchnorm.c:600-702,946-1026) ---------- */

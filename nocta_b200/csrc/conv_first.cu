@@ -15,26 +15,28 @@ constexpr int KP = 32;  // padded patch width
 
 struct Geo {
     int N, H, W, Cout, pad, Ho, Wo;
-    long long xs[4];  // input strides (n, c, h, w) in elements
+    int xs[4];  // input strides (n, c, h, w) in elements (the whole input is < 2^31 elements)
 };
 
 __device__ __forceinline__ void load_patch(float (&x)[K], const float* __restrict__ in, const Geo& g, int n, int ho, int wo) {
+    // one base offset per pixel; the 27 tap offsets are small loop-invariant integers
+    const int h0 = ho - g.pad, w0 = wo - g.pad;
+    const float* base = in + (n * g.xs[0] + h0 * g.xs[2] + w0 * g.xs[3]);
+    bool hok[3], wok[3];
+#pragma unroll
+    for (int t = 0; t < 3; t++) { hok[t] = (unsigned)(h0 + t) < (unsigned)g.H; wok[t] = (unsigned)(w0 + t) < (unsigned)g.W; }
 #pragma unroll
     for (int ci = 0; ci < 3; ci++)
 #pragma unroll
         for (int kh = 0; kh < 3; kh++)
 #pragma unroll
-            for (int kw = 0; kw < 3; kw++) {
-                const int h = ho + kh - g.pad, w = wo + kw - g.pad;
-                float v = 0.f;
-                if (h >= 0 && h < g.H && w >= 0 && w < g.W) v = in[n * g.xs[0] + ci * g.xs[1] + h * g.xs[2] + w * g.xs[3]];
-                x[(ci * 3 + kh) * 3 + kw] = v;
-            }
+            for (int kw = 0; kw < 3; kw++)
+                x[(ci * 3 + kh) * 3 + kw] = (hok[kh] && wok[kw]) ? base[ci * g.xs[1] + kh * g.xs[2] + kw * g.xs[3]] : 0.f;
 }
 
 // y (N,Ho,Wo,Cout) channels-last; weights (Cout, 27)
 __global__ void __launch_bounds__(256) fwd_kernel(float* __restrict__ y, const float* __restrict__ in, const float* __restrict__ w,
-                                                  const float* __restrict__ bias, Geo g, long long pixels) {
+                                                  const float* __restrict__ bias, Geo g, int pixels) {
     extern __shared__ float ws[];  // [K][Cout] then bias [Cout]
     float* bs = ws + K * g.Cout;
     for (int i = threadIdx.x; i < K * g.Cout; i += blockDim.x) {
@@ -46,10 +48,10 @@ __global__ void __launch_bounds__(256) fwd_kernel(float* __restrict__ y, const f
     const int tpp = g.Cout / 16;  // threads per pixel
     const int ppb = blockDim.x / tpp;
     const int lp = threadIdx.x / tpp, cq = threadIdx.x % tpp;
-    for (long long p = (long long)blockIdx.x * ppb + lp; p < pixels; p += (long long)gridDim.x * ppb) {
-        const int wo = (int)(p % g.Wo);
-        const long long t = p / g.Wo;
-        const int ho = (int)(t % g.Ho), n = (int)(t / g.Ho);
+    for (int p = blockIdx.x * ppb + lp; p < pixels; p += gridDim.x * ppb) {
+        const int wo = p % g.Wo;
+        const int t = p / g.Wo;
+        const int ho = t % g.Ho, n = t / g.Ho;
         float x[K];
         load_patch(x, in, g, n, ho, wo);
         float acc[16];
@@ -67,7 +69,7 @@ __global__ void __launch_bounds__(256) fwd_kernel(float* __restrict__ y, const f
                 acc[4 * q + 3] = fmaf(x[k], wv.w, acc[4 * q + 3]);
             }
         }
-        float4* dst = reinterpret_cast<float4*>(y + p * g.Cout + cq * 16);
+        float4* dst = reinterpret_cast<float4*>(y + (size_t)p * g.Cout + cq * 16);
 #pragma unroll
         for (int q = 0; q < 4; q++) dst[q] = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
     }
@@ -77,39 +79,41 @@ __global__ void __launch_bounds__(256) fwd_kernel(float* __restrict__ y, const f
 constexpr int TP = 64;  // pixels per shared-memory tile
 template <int COUT>
 __global__ void __launch_bounds__(COUT * 4) dw_kernel(float* __restrict__ partial, const float* __restrict__ dy,
-                                                      const float* __restrict__ in, Geo g, long long pixels, long long per_block) {
+                                                      const float* __restrict__ in, Geo g, int pixels, int per_block) {
     __shared__ __align__(16) float sdy[TP][COUT];
     __shared__ __align__(16) float sx[TP][KP];
     const int co = threadIdx.x % COUT, grp = threadIdx.x / COUT;  // grp 0..3 -> patch positions grp*8 .. +7
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; j++) acc[j] = 0.f;
-    const long long p0 = (long long)blockIdx.x * per_block;
-    long long p1 = p0 + per_block;
+    const int p0 = blockIdx.x * per_block;
+    int p1 = p0 + per_block;
     if (p1 > pixels) p1 = pixels;
-    for (long long base = p0; base < p1; base += TP) {
-        const int cnt = (int)((p1 - base) < TP ? (p1 - base) : TP);
+    const int kk = threadIdx.x % KP;  // this thread's patch position while staging
+    const int kkw = kk % 3, kkh = (kk / 3) % 3, kci = kk / 9;
+    const int koff = kci * g.xs[1] + kkh * g.xs[2] + kkw * g.xs[3];
+    for (int base = p0; base < p1; base += TP) {
+        const int cnt = (p1 - base) < TP ? (p1 - base) : TP;
         // dY tile: rows are contiguous in channels-last memory
         for (int i = threadIdx.x; i < TP * COUT / 4; i += blockDim.x) {
             const int r = i / (COUT / 4), c4 = i % (COUT / 4);
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (r < cnt) v = reinterpret_cast<const float4*>(dy + (base + r) * COUT)[c4];
+            if (r < cnt) v = reinterpret_cast<const float4*>(dy + (size_t)(base + r) * COUT)[c4];
             reinterpret_cast<float4*>(&sdy[r][0])[c4] = v;
         }
         // patches: one (pixel, position) per thread-iteration
-        for (int i = threadIdx.x; i < TP * KP; i += blockDim.x) {
-            const int r = i / KP, k = i % KP;
+        for (int r = threadIdx.x / KP; r < TP; r += blockDim.x / KP) {
             float v = 0.f;
-            if (r < cnt && k < K) {
-                const long long p = base + r;
-                const int wo = (int)(p % g.Wo);
-                const long long t = p / g.Wo;
-                const int ho = (int)(t % g.Ho), n = (int)(t / g.Ho);
-                const int kw = k % 3, kh = (k / 3) % 3, ci = k / 9;
-                const int h = ho + kh - g.pad, w = wo + kw - g.pad;
-                if (h >= 0 && h < g.H && w >= 0 && w < g.W) v = in[n * g.xs[0] + ci * g.xs[1] + h * g.xs[2] + w * g.xs[3]];
+            if (r < cnt && kk < K) {
+                const int p = base + r;
+                const int wo = p % g.Wo;
+                const int t = p / g.Wo;
+                const int ho = t % g.Ho, n = t / g.Ho;
+                const int h = ho + kkh - g.pad, w = wo + kkw - g.pad;
+                if ((unsigned)h < (unsigned)g.H && (unsigned)w < (unsigned)g.W)
+                    v = in[n * g.xs[0] + (ho - g.pad) * g.xs[2] + (wo - g.pad) * g.xs[3] + koff];
             }
-            sx[r][k] = v;
+            sx[r][kk] = v;
         }
         __syncthreads();
 #pragma unroll 4
@@ -122,18 +126,27 @@ __global__ void __launch_bounds__(COUT * 4) dw_kernel(float* __restrict__ partia
         }
         __syncthreads();
     }
-    float* dst = partial + ((long long)blockIdx.x * COUT + co) * KP + grp * 8;
+    float* dst = partial + ((size_t)blockIdx.x * COUT + co) * KP + grp * 8;
     reinterpret_cast<float4*>(dst)[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
     reinterpret_cast<float4*>(dst)[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
 }
 
 __global__ void __launch_bounds__(256) dw_reduce_kernel(float* __restrict__ dW, const float* __restrict__ partial, int blocks, int Cout) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    // one warp per weight: lanes stride over the per-CTA partials, fixed-order shuffle tree
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (i >= Cout * K) return;
     const int co = i / K, k = i % K;
     double acc = 0.0;
-    for (int b = 0; b < blocks; b++) acc += (double)partial[((long long)b * Cout + co) * KP + k];
-    dW[i] = (float)acc;
+    for (int b = lane; b < blocks; b += 32) acc += (double)partial[((long long)b * Cout + co) * KP + k];
+    acc = ncc::warp_sum(acc);
+    if (lane == 0) dW[i] = (float)acc;
+}
+
+// 32-bit index arithmetic is used throughout: everything addressed must stay below 2^31 elements
+static bool fits_int(int N, int H, int W, const long long xs[4], int Ho, int Wo) {
+    long long span = 1 + (long long)(N - 1) * xs[0] + 2 * xs[1] + (long long)(H - 1) * xs[2] + (long long)(W - 1) * xs[3];
+    for (int i = 0; i < 4; i++) if (xs[i] < 0 || xs[i] > 0x3fffffffLL) return false;
+    return span < 0x7fffffffLL && (long long)N * Ho * Wo < 0x7fffffffLL / 256;
 }
 
 bool eligible(int Cin, int kH, int kW, int stride, int Cout) {
@@ -142,12 +155,13 @@ bool eligible(int Cin, int kH, int kW, int stride, int Cout) {
 
 int forward(float* y, const float* x, const long long xs[4], const float* w, const float* bias, int N, int H, int W, int Cout, int pad,
             cudaStream_t st) {
-    Geo g{N, H, W, Cout, pad, H + 2 * pad - 2, W + 2 * pad - 2, {xs[0], xs[1], xs[2], xs[3]}};
+    Geo g{N, H, W, Cout, pad, H + 2 * pad - 2, W + 2 * pad - 2, {(int)xs[0], (int)xs[1], (int)xs[2], (int)xs[3]}};
     if (g.Ho <= 0 || g.Wo <= 0) return NC_CUDA_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(y) & 15u) != 0) return NC_CUDA_ERR_UNSUPPORTED;
-    const long long pixels = (long long)N * g.Ho * g.Wo;
+    if (!fits_int(N, H, W, xs, g.Ho, g.Wo)) return NC_CUDA_ERR_UNSUPPORTED;
+    const int pixels = N * g.Ho * g.Wo;
     const int ppb = 256 / (Cout / 16);
-    long long need = (pixels + ppb - 1) / ppb;
+    long long need = ((long long)pixels + ppb - 1) / ppb;
     const long long cap = (long long)ncc::sm_count() * 8;
     const int grid = (int)(need < cap ? need : cap);
     const size_t smem = sizeof(float) * (size_t)(K + 1) * Cout;
@@ -158,20 +172,21 @@ int forward(float* y, const float* x, const long long xs[4], const float* w, con
 
 int weight_grad(float* dW, const float* dy, const float* x, const long long xs[4], int N, int H, int W, int Cout, int pad, cudaStream_t st) {
     if (Cout != 64 && Cout != 32) return NC_CUDA_ERR_UNSUPPORTED;
-    Geo g{N, H, W, Cout, pad, H + 2 * pad - 2, W + 2 * pad - 2, {xs[0], xs[1], xs[2], xs[3]}};
+    Geo g{N, H, W, Cout, pad, H + 2 * pad - 2, W + 2 * pad - 2, {(int)xs[0], (int)xs[1], (int)xs[2], (int)xs[3]}};
     if (g.Ho <= 0 || g.Wo <= 0) return NC_CUDA_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(dy) & 15u) != 0) return NC_CUDA_ERR_UNSUPPORTED;
-    const long long pixels = (long long)N * g.Ho * g.Wo;
+    if (!fits_int(N, H, W, xs, g.Ho, g.Wo)) return NC_CUDA_ERR_UNSUPPORTED;
+    const int pixels = N * g.Ho * g.Wo;
     long long blocks = (long long)ncc::sm_count() * 4;
-    long long per = (pixels + blocks - 1) / blocks;
+    long long per = ((long long)pixels + blocks - 1) / blocks;
     per = ((per + TP - 1) / TP) * TP;
     blocks = (pixels + per - 1) / per;
     float* partial = (float*)ncc::scratch(2, sizeof(float) * (size_t)blocks * Cout * KP, st);
     if (!partial) return NC_CUDA_ERR_RUNTIME;
-    if (Cout == 64) dw_kernel<64><<<(int)blocks, 256, 0, st>>>(partial, dy, x, g, pixels, per);
-    else dw_kernel<32><<<(int)blocks, 128, 0, st>>>(partial, dy, x, g, pixels, per);
+    if (Cout == 64) dw_kernel<64><<<(int)blocks, 256, 0, st>>>(partial, dy, x, g, pixels, (int)per);
+    else dw_kernel<32><<<(int)blocks, 128, 0, st>>>(partial, dy, x, g, pixels, (int)per);
     NCC_COUNT_LAUNCH();
-    dw_reduce_kernel<<<ncc::ceil_div(Cout * K, 256), 256, 0, st>>>(dW, partial, (int)blocks, Cout);
+    dw_reduce_kernel<<<ncc::ceil_div(Cout * K * 32, 256), 256, 0, st>>>(dW, partial, (int)blocks, Cout);
     NCC_COUNT_LAUNCH();
     return ncc::launch_status("conv_first weight_grad");
 }

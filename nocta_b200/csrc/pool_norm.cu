@@ -307,39 +307,47 @@ struct BnFwdSumFlat {  // NCHW flavour: flat index supplied
     __device__ void operator()(size_t i, int, float& v1, float& v2) const { float t = x[i]; v1 = t; v2 = t * t; }
 };
 // (dy, dy * xhat) with optional ReLU mask taken from the forward output
+// ReLU mask of a fused BatchNorm+ReLU: either read from the saved forward output y, or recomputed from x with
+// exactly the forward expression gamma * ((x - mean) * inv_std) + beta (saves reading y at all)
+struct ReluMask {
+    const float* y; const float* gamma; const float* beta; int recompute;
+    __device__ bool dead(size_t i, float xh, int c) const {
+        if (y) return !(y[i] > 0.f);
+        if (recompute) return !(((gamma ? gamma[c] : 1.f) * xh + (beta ? beta[c] : 0.f)) > 0.f);
+        return false;
+    }
+};
 struct BnBwdSum {
-    const float* dy; const float* x; const float* y; const float* mean; const float* var; float eps; int cols;
+    const float* dy; const float* x; ReluMask m; const float* mean; const float* var; float eps; int cols;
     __device__ void operator()(size_t r, int c, float& v1, float& v2) const {
         size_t i = r * cols + c;
         float g = dy[i];
-        if (y && !(y[i] > 0.f)) g = 0.f;
         float xh = (x[i] - mean[c]) * rsqrtf(var[c] + eps);
+        if (m.dead(i, xh, c)) g = 0.f;
         v1 = g; v2 = g * xh;
     }
     __device__ void vec(size_t r, int c, float4& v1, float4& v2) const {
         const size_t i = r * cols + c;
         float4 g = *reinterpret_cast<const float4*>(dy + i);
         const float4 xv = *reinterpret_cast<const float4*>(x + i);
-        if (y) {
-            const float4 yv = *reinterpret_cast<const float4*>(y + i);
-            if (!(yv.x > 0.f)) g.x = 0.f;
-            if (!(yv.y > 0.f)) g.y = 0.f;
-            if (!(yv.z > 0.f)) g.z = 0.f;
-            if (!(yv.w > 0.f)) g.w = 0.f;
-        }
-        const float4 m = *reinterpret_cast<const float4*>(mean + c);
+        const float4 mu = *reinterpret_cast<const float4*>(mean + c);
         const float4 vr = *reinterpret_cast<const float4*>(var + c);
+        const float4 xh = make_float4((xv.x - mu.x) * rsqrtf(vr.x + eps), (xv.y - mu.y) * rsqrtf(vr.y + eps),
+                                      (xv.z - mu.z) * rsqrtf(vr.z + eps), (xv.w - mu.w) * rsqrtf(vr.w + eps));
+        if (m.dead(i, xh.x, c)) g.x = 0.f;
+        if (m.dead(i + 1, xh.y, c + 1)) g.y = 0.f;
+        if (m.dead(i + 2, xh.z, c + 2)) g.z = 0.f;
+        if (m.dead(i + 3, xh.w, c + 3)) g.w = 0.f;
         v1 = g;
-        v2 = make_float4(g.x * ((xv.x - m.x) * rsqrtf(vr.x + eps)), g.y * ((xv.y - m.y) * rsqrtf(vr.y + eps)),
-                         g.z * ((xv.z - m.z) * rsqrtf(vr.z + eps)), g.w * ((xv.w - m.w) * rsqrtf(vr.w + eps)));
+        v2 = make_float4(g.x * xh.x, g.y * xh.y, g.z * xh.z, g.w * xh.w);
     }
 };
 struct BnBwdSumFlat {
-    const float* dy; const float* x; const float* y; const float* mean; const float* var; float eps;
+    const float* dy; const float* x; ReluMask m; const float* mean; const float* var; float eps;
     __device__ void operator()(size_t i, int c, float& v1, float& v2) const {
         float g = dy[i];
-        if (y && !(y[i] > 0.f)) g = 0.f;
         float xh = (x[i] - mean[c]) * rsqrtf(var[c] + eps);
+        if (m.dead(i, xh, c)) g = 0.f;
         v1 = g; v2 = g * xh;
     }
 };
@@ -480,34 +488,29 @@ __global__ void bn_bwd_finalize_kernel(const double* __restrict__ partial, int s
 // dx = gamma * inv_std / M * (M * g - sum_g - xhat * sum_gx)   (src/nn/batchnorm.c:145-158)
 template <int LAYOUT, int VEC>
 __global__ void __launch_bounds__(kThreads) bn_bwd_apply_kernel(float* __restrict__ dx, const float* __restrict__ dy,
-                                                                const float* __restrict__ x, const float* __restrict__ yrelu,
+                                                                const float* __restrict__ x, ReluMask mask,
                                                                 const float* __restrict__ gamma, const float* __restrict__ mean,
                                                                 const float* __restrict__ var, const float* __restrict__ sums,
                                                                 float eps, float Mf, int C, int spatial, size_t nvec, int rnd) {
     const size_t gstride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += gstride) {
         const size_t e = i * VEC;
-        float xv[VEC], gv[VEC], yv[VEC], out[VEC];
+        float xv[VEC], gv[VEC], out[VEC];
         if (VEC == 4) {
             float4 t = *reinterpret_cast<const float4*>(x + e);
             float4 u = *reinterpret_cast<const float4*>(dy + e);
             xv[0] = t.x; xv[1 % VEC] = t.y; xv[2 % VEC] = t.z; xv[3 % VEC] = t.w;
             gv[0] = u.x; gv[1 % VEC] = u.y; gv[2 % VEC] = u.z; gv[3 % VEC] = u.w;
-            if (yrelu) {
-                float4 w = *reinterpret_cast<const float4*>(yrelu + e);
-                yv[0] = w.x; yv[1 % VEC] = w.y; yv[2 % VEC] = w.z; yv[3 % VEC] = w.w;
-            }
         } else {
             xv[0] = x[e]; gv[0] = dy[e];
-            if (yrelu) yv[0] = yrelu[e];
         }
 #pragma unroll
         for (int v = 0; v < VEC; v++) {
             int c = LAYOUT == 0 ? (int)((e / spatial) % C) : (int)((e + v) % C);
             float is = rsqrtf(var[c] + eps);
             float g = gv[v];
-            if (yrelu && !(yv[v] > 0.f)) g = 0.f;
             float xh = (xv[v] - mean[c]) * is;
+            if (mask.dead(e + v, xh, c)) g = 0.f;
             float coeff = (gamma ? gamma[c] : 1.f) * is / Mf;
             float o = coeff * (Mf * g - sums[2 * c] - xh * sums[2 * c + 1]);
             out[v] = rnd ? round_tf32(o) : o;
@@ -715,17 +718,18 @@ int nc_cuda_batchnorm_forward_f32_ex(float* y, const float* x, const float* gamm
 
 int nc_cuda_batchnorm_backward_f32_ex(float* dx, float* dgamma, float* dbeta, const float* dy, const float* x,
                                       const float* gamma, const float* save_mean, const float* save_var,
-                                      const float* relu_out, int N, int C, int spatial, double eps, int layout,
-                                      void* stream) {
+                                      const float* relu_out, const float* relu_beta, int relu_recompute, int N, int C,
+                                      int spatial, double eps, int layout, void* stream) {
     NCC_REQUIRE(dx && dy && x && save_mean && save_var && N > 0 && C > 0 && spatial > 0, "batchnorm_backward: bad argument");
     cudaStream_t st = (cudaStream_t)stream;
     const size_t total = (size_t)N * C * spatial;
     const float fe = (float)eps;
     double* partial = nullptr;
     int slabs = 0;
+    const ReluMask mask{relu_out, gamma, relu_beta, relu_out ? 0 : (relu_recompute ? 1 : 0)};
     int rc = channel_reduce(&partial, &slabs, N, C, spatial, layout,
-                            BnBwdSum{dy, x, relu_out, save_mean, save_var, fe, C},
-                            BnBwdSumFlat{dy, x, relu_out, save_mean, save_var, fe},
+                            BnBwdSum{dy, x, mask, save_mean, save_var, fe, C},
+                            BnBwdSumFlat{dy, x, mask, save_mean, save_var, fe},
                             al16(dy) && al16(x) && al16(relu_out) && al16(save_mean) && al16(save_var), st);
     if (rc) return rc;
     float* sums = (float*)scratch(6, sizeof(float) * 2 * (size_t)C, st);
@@ -739,11 +743,11 @@ int nc_cuda_batchnorm_backward_f32_ex(float* dx, float* dgamma, float* dbeta, co
     const int grid = grid_for((long long)nvec, kThreads);
     const float Mf = (float)((double)N * spatial);
     if (layout == 0) {
-        if (vec) bn_bwd_apply_kernel<0, 4><<<grid, kThreads, 0, st>>>(dx, dy, x, relu_out, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec, round_outputs() ? 1 : 0);
-        else bn_bwd_apply_kernel<0, 1><<<grid, kThreads, 0, st>>>(dx, dy, x, relu_out, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec, round_outputs() ? 1 : 0);
+        if (vec) bn_bwd_apply_kernel<0, 4><<<grid, kThreads, 0, st>>>(dx, dy, x, mask, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec, round_outputs() ? 1 : 0);
+        else bn_bwd_apply_kernel<0, 1><<<grid, kThreads, 0, st>>>(dx, dy, x, mask, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec, round_outputs() ? 1 : 0);
     } else {
-        if (vec) bn_bwd_apply_kernel<1, 4><<<grid, kThreads, 0, st>>>(dx, dy, x, relu_out, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec, round_outputs() ? 1 : 0);
-        else bn_bwd_apply_kernel<1, 1><<<grid, kThreads, 0, st>>>(dx, dy, x, relu_out, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec, round_outputs() ? 1 : 0);
+        if (vec) bn_bwd_apply_kernel<1, 4><<<grid, kThreads, 0, st>>>(dx, dy, x, mask, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec, round_outputs() ? 1 : 0);
+        else bn_bwd_apply_kernel<1, 1><<<grid, kThreads, 0, st>>>(dx, dy, x, mask, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec, round_outputs() ? 1 : 0);
     }
     NCC_COUNT_LAUNCH();
     return launch_status("batchnorm_backward");
@@ -758,8 +762,8 @@ void nc_cuda_batchnorm_forward_f32(float* y, const float* x, const float* gamma,
 void nc_cuda_batchnorm_backward_f32(float* dx, float* dgamma, float* dbeta, const float* dy, const float* x,
                                     const float* gamma, const float* save_mean, const float* save_var, int N, int C,
                                     int spatial, float eps) {
-    nc_cuda_batchnorm_backward_f32_ex(dx, dgamma, dbeta, dy, x, gamma, save_mean, save_var, nullptr, N, C, spatial, eps,
-                                      0, current_stream());
+    nc_cuda_batchnorm_backward_f32_ex(dx, dgamma, dbeta, dy, x, gamma, save_mean, save_var, nullptr, nullptr, 0, N, C, spatial,
+                                      eps, 0, current_stream());
 }
 
 int nc_cuda_layernorm_forward_f32_ex(float* y, const float* x, const float* gamma, const float* beta, size_t rows,

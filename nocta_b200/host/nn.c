@@ -438,7 +438,8 @@ static nc_tensor** bwd_batchnorm2d(nc_tensor* g, nc_tensor** saved, size_t n) {
     nc_tensor* var = saved[3];
     const double eps = nc_tensor_get_flat(saved[4], 0);
     const int layout = (int)nc_tensor_get_flat(saved[4], 1);
-    nc_tensor* yrelu = (n > 6) ? saved[6] : NULL; /* fused ReLU: the forward output doubles as the mask */
+    const bool fused_relu = n > 6;                 /* fused ReLU: the mask is recomputed from x, gamma and beta */
+    nc_tensor* beta = fused_relu ? saved[6] : NULL; /* may be NULL for a layer without affine parameters */
     nc_tensor* gd = nci_match_layout(g, x);
     if (!gd) return out;
     const int N = (int)x->shape[0], C = (int)x->shape[1], S = (int)(x->shape[2] * x->shape[3]);
@@ -449,8 +450,8 @@ static nc_tensor** bwd_batchnorm2d(nc_tensor* g, nc_tensor** saved, size_t n) {
     if (gamma) { out[1] = nci_empty_on(&cs, 1, NC_F32, NC_DEVICE_CUDA); out[2] = nci_empty_on(&cs, 1, NC_F32, NC_DEVICE_CUDA); }
     if (out[0] && (!gamma || (out[1] && out[2])))
         nci_ok(nc_cuda_batchnorm_backward_f32_ex(nci_fptr(out[0]), gamma ? nci_fptr(out[1]) : NULL, gamma ? nci_fptr(out[2]) : NULL, nci_fptr(gd), nci_fptr(x),
-                                                 gamma ? nci_fptr(gamma) : NULL, nci_fptr(mean), nci_fptr(var), yrelu ? nci_fptr(yrelu) : NULL, N, C, S,
-                                                 eps, layout, nci_stream()), "batchnorm backward");
+                                                 gamma ? nci_fptr(gamma) : NULL, nci_fptr(mean), nci_fptr(var), NULL, beta ? nci_fptr(beta) : NULL,
+                                                 fused_relu ? 1 : 0, N, C, S, eps, layout, nci_stream()), "batchnorm backward");
     if (gd != g) nc_tensor_free(gd);
     return out;
 }
@@ -494,7 +495,7 @@ static nc_tensor* bn_forward(nc_tensor* input, nc_tensor* running_mean, nc_tenso
             if (hp) { nc_tensor_set_flat(hp, 0, eps); nc_tensor_set_flat(hp, 1, (double)layout); }
             nc_node_save_owned_tensor(nd, hp);
             nc_node_save_tensor(nd, input);
-            if (relu) nc_node_save_tensor(nd, y); /* borrowed: y owns this node */
+            if (relu) nc_node_save_tensor(nd, bias); /* backward recomputes the ReLU mask from x, gamma, beta */
             wired = true;
         }
     }

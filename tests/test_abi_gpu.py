@@ -273,7 +273,7 @@ def test_batchnorm(abi, N, Cc, H, W, layout):
     g = rng.standard_normal(x.shape).astype(np.float32)
     ddx, ddg, ddb = torch.empty_like(dx_in), torch.empty(Cc, device="cuda"), torch.empty(Cc, device="cuda")
     ok(abi, abi.nc_cuda_batchnorm_backward_f32_ex(P(ddx), P(ddg), P(ddb), P(dev(to_l(g))), P(dx_in), P(dev(gam)), P(dsm), P(dsv),
-                                                  None, N, Cc, H * W, 1e-5, layout, None))
+                                                  None, None, 0, N, Cc, H * W, 1e-5, layout, None))
     dxo, dgo, dbo = O.batchnorm2d_backward(g, x, gam, mean, var, 1e-5)
     close(from_l(host(ddx)), dxo, TOL_F32)
     close(host(ddg), dgo, TOL_F32)
@@ -283,12 +283,13 @@ def test_batchnorm(abi, N, Cc, H, W, layout):
                                                  N, Cc, H * W, 0.1, 1e-5, 1, layout, 1, None))
     yr = O.relu_forward(yo)
     close(from_l(host(dy)), yr, TOL_F32)
-    ok(abi, abi.nc_cuda_batchnorm_backward_f32_ex(P(ddx), P(ddg), P(ddb), P(dev(to_l(g))), P(dx_in), P(dev(gam)), P(dsm), P(dsv),
-                                                  P(dy), N, Cc, H * W, 1e-5, layout, None))
     gm = np.where(from_l(host(dy)) > 0, g, 0).astype(np.float32)
     dxo, dgo, dbo = O.batchnorm2d_backward(gm, x, gam, mean, var, 1e-5)
-    close(from_l(host(ddx)), dxo, TOL_F32)
-    close(host(ddg), dgo, TOL_F32)
+    for relu_out, beta_p, recompute in ((P(dy), None, 0), (None, P(dev(bet)), 1)):  # mask read back / recomputed from x
+        ok(abi, abi.nc_cuda_batchnorm_backward_f32_ex(P(ddx), P(ddg), P(ddb), P(dev(to_l(g))), P(dx_in), P(dev(gam)), P(dsm), P(dsv),
+                                                      relu_out, beta_p, recompute, N, Cc, H * W, 1e-5, layout, None))
+        close(from_l(host(ddx)), dxo, TOL_F32)
+        close(host(ddg), dgo, TOL_F32)
     # eval mode (legacy name, NCHW): running statistics
     if layout == 0:
         abi.nc_cuda_batchnorm_forward_f32(P(dy), P(dx_in), P(dev(gam)), P(dev(bet)), P(drm), P(drv), P(dsm), P(dsv),
