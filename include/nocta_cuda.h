@@ -255,6 +255,16 @@ void nc_cuda_cross_entropy_backward_f32(float* grad_logits, const float* logits,
  * Out-of-range labels contribute nothing, as on the CPU path (loss.c:278-281, 86-91). */
 int nc_cuda_cross_entropy_fused_f32_ex(float* loss, float* grad_logits, const float* logits,
                                        const int64_t* targets, int N, int C, float grad_scale, void* stream);
+/* No counterpart in the reference.  Same computation and same bits as nc_cuda_cross_entropy_fused_f32_ex,
+ * for callers that must not trigger a device allocation (all memory already handed to their own arena;
+ * a collective in flight on another stream that an allocation's device-wide synchronisation would stall):
+ * the partial sums live in a fixed array inside the library, so no allocating routine is ever called.
+ * At most NC_CUDA_CE_STATIC_MAX_ROWS rows per call (more: NC_CUDA_ERR_ARG).  The first call on each
+ * device resolves the array's address; make that call before beginning a stream capture.  All calls on a
+ * device share the array: calls that may run concurrently race and must be serialised by the caller. */
+#define NC_CUDA_CE_STATIC_MAX_ROWS 4096
+int nc_cuda_cross_entropy_fused_static_f32_ex(float* loss, float* grad_logits, const float* logits,
+                                              const int64_t* targets, int N, int C, float grad_scale, void* stream);
 /* new: mean squared error; grad_pred = 2*(p-t)*grad_scale/numel, grad_target = -grad_pred (either may be NULL) */
 int nc_cuda_mse_fused_f32_ex(float* loss, float* grad_pred, float* grad_target, const float* pred,
                              const float* target, size_t n, float grad_scale, void* stream);

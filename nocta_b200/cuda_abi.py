@@ -119,6 +119,7 @@ SIGNATURES = {
     "nc_cuda_cross_entropy_forward_f32": (None, [_p, _p, _p, _i, _i]),
     "nc_cuda_cross_entropy_backward_f32": (None, [_p, _p, _p, _i, _i]),
     "nc_cuda_cross_entropy_fused_f32_ex": (_i, [_p, _p, _p, _p, _i, _i, _f, _p]),
+    "nc_cuda_cross_entropy_fused_static_f32_ex": (_i, [_p, _p, _p, _p, _i, _i, _f, _p]),
     "nc_cuda_mse_fused_f32_ex": (_i, [_p, _p, _p, _p, _p, _z, _f, _p]),
     # optimizers
     "nc_cuda_sgd_step_f32": (None, [_p, _p, _f, _z]),
