@@ -1,7 +1,7 @@
 // First-layer convolution (3 input channels, 3x3, stride 1) with a channels-last output: the case the
 // tensor-core implicit GEMM cannot tile (reduction length 27) and that is bound by writing the output,
-// not by arithmetic.  Forward: 4..16 threads per output pixel, 16 output channels each, the 27 patch
-// values in registers and the weights in shared memory.  Weight gradient: the reduction over all
+// not by arithmetic.  Forward: a shared-memory tiled kernel for the common channel counts (below), else
+// 4..16 threads per output pixel, 16 output channels each, the 27 patch values in registers.  Weight gradient: the reduction over all
 // pixels is split over CTAs; each CTA stages 64-pixel tiles of dY and of the 27-wide patches in shared
 // memory, every thread owns one output channel and 8 of the (padded to 32) patch positions; per-CTA
 // partial sums are combined in a fixed order.  No input gradient: the network input needs none.
@@ -73,6 +73,109 @@ __global__ void __launch_bounds__(256) fwd_kernel(float* __restrict__ y, const f
 #pragma unroll
         for (int q = 0; q < 4; q++) dst[q] = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
     }
+}
+
+// Tiled forward for Cout in {16, 32, 64, 128}.  A CTA owns a strip of TR output rows x 64 output columns
+// of one image: the 3 x (TR+2) x 66 input halo is staged in shared memory once (coalesced reads, zero
+// fill = padding), every thread computes 4 consecutive pixels x 8 output channels (channels cg*4..+3 and
+// Cout/2 + cg*4..+3, so that the lanes of a warp store whole 128-byte lines), reading its 6 input
+// values per (ci, kh) with one float4 + one float2 and the weights with two float4: 8 shared loads per
+// 96 FMAs.
+constexpr int TW = 64, TWP = 68;
+template <int COUT>
+struct TileGeo {
+    static constexpr int CG = COUT / 8;     // channel groups
+    static constexpr int PG = 256 / CG;     // 4-pixel groups per CTA
+    static constexpr int TR = PG / (TW / 4);  // output rows per CTA
+};
+template <int COUT>
+__global__ void __launch_bounds__(256) fwd_tile_kernel(float* __restrict__ y, const float* __restrict__ in,
+                                                       const float* __restrict__ w, const float* __restrict__ bias, Geo g,
+                                                       int tiles_h, int tiles_w, int ntiles) {
+    using T = TileGeo<COUT>;
+    constexpr int CG = T::CG, TR = T::TR, ROWS = TR + 2;
+    __shared__ __align__(16) float ws[K * COUT];
+    __shared__ __align__(16) float bs[COUT];
+    __shared__ __align__(16) float tile[3][ROWS][TWP];
+    for (int i = threadIdx.x; i < K * COUT; i += 256) {
+        const int co = i % COUT, k = i / COUT;
+        ws[i] = w[co * K + k];
+    }
+    for (int i = threadIdx.x; i < COUT; i += 256) bs[i] = bias ? bias[i] : 0.f;
+    const int cg = threadIdx.x % CG, pg = threadIdx.x / CG;
+    const int prow = pg / (TW / 4), pcol = (pg % (TW / 4)) * 4;
+    const float* wlo = ws + cg * 4;
+    const float* whi = ws + COUT / 2 + cg * 4;
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+        const int tw = t % tiles_w;
+        const int t2 = t / tiles_w;
+        const int th = t2 % tiles_h, n = t2 / tiles_h;
+        const int ho0 = th * TR, wo0 = tw * TW;
+        __syncthreads();  // the previous tile is no longer read (also orders the weight staging)
+        for (int i = threadIdx.x; i < 3 * ROWS * 66; i += 256) {
+            const int cc = i % 66;
+            const int q = i / 66;
+            const int r = q % ROWS, ci = q / ROWS;
+            const int h = ho0 - g.pad + r, wc = wo0 - g.pad + cc;
+            float v = 0.f;
+            if ((unsigned)h < (unsigned)g.H && (unsigned)wc < (unsigned)g.W)
+                v = in[n * g.xs[0] + ci * g.xs[1] + h * g.xs[2] + wc * g.xs[3]];
+            tile[ci][r][cc] = v;
+        }
+        __syncthreads();
+        float acc[4][8];
+        {
+            const float4 b0 = *reinterpret_cast<const float4*>(bs + cg * 4);
+            const float4 b1 = *reinterpret_cast<const float4*>(bs + COUT / 2 + cg * 4);
+#pragma unroll
+            for (int p = 0; p < 4; p++) {
+                acc[p][0] = b0.x; acc[p][1] = b0.y; acc[p][2] = b0.z; acc[p][3] = b0.w;
+                acc[p][4] = b1.x; acc[p][5] = b1.y; acc[p][6] = b1.z; acc[p][7] = b1.w;
+            }
+        }
+#pragma unroll
+        for (int ci = 0; ci < 3; ci++)
+#pragma unroll
+            for (int kh = 0; kh < 3; kh++) {
+                const float* row = &tile[ci][prow + kh][pcol];
+                const float4 xa = *reinterpret_cast<const float4*>(row);
+                const float2 xb = *reinterpret_cast<const float2*>(row + 4);
+                const float xv[6] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y};
+#pragma unroll
+                for (int kw = 0; kw < 3; kw++) {
+                    const int k = (ci * 3 + kh) * 3 + kw;
+                    const float4 w0 = *reinterpret_cast<const float4*>(wlo + k * COUT);
+                    const float4 w1 = *reinterpret_cast<const float4*>(whi + k * COUT);
+#pragma unroll
+                    for (int p = 0; p < 4; p++) {
+                        const float xx = xv[p + kw];
+                        acc[p][0] = fmaf(xx, w0.x, acc[p][0]); acc[p][1] = fmaf(xx, w0.y, acc[p][1]);
+                        acc[p][2] = fmaf(xx, w0.z, acc[p][2]); acc[p][3] = fmaf(xx, w0.w, acc[p][3]);
+                        acc[p][4] = fmaf(xx, w1.x, acc[p][4]); acc[p][5] = fmaf(xx, w1.y, acc[p][5]);
+                        acc[p][6] = fmaf(xx, w1.z, acc[p][6]); acc[p][7] = fmaf(xx, w1.w, acc[p][7]);
+                    }
+                }
+            }
+        const int ho = ho0 + prow;
+        if (ho < g.Ho) {
+            float* dst = y + ((size_t)(n * g.Ho + ho) * g.Wo + wo0 + pcol) * COUT;
+#pragma unroll
+            for (int p = 0; p < 4; p++) {
+                if (wo0 + pcol + p < g.Wo) {
+                    *reinterpret_cast<float4*>(dst + (size_t)p * COUT + cg * 4) = make_float4(acc[p][0], acc[p][1], acc[p][2], acc[p][3]);
+                    *reinterpret_cast<float4*>(dst + (size_t)p * COUT + COUT / 2 + cg * 4) = make_float4(acc[p][4], acc[p][5], acc[p][6], acc[p][7]);
+                }
+            }
+        }
+    }
+}
+
+template <int COUT>
+static void launch_fwd_tile(float* y, const float* x, const float* w, const float* bias, const Geo& g, cudaStream_t st) {
+    const int tiles_h = (g.Ho + TileGeo<COUT>::TR - 1) / TileGeo<COUT>::TR, tiles_w = (g.Wo + TW - 1) / TW;
+    const long long ntiles = (long long)g.N * tiles_h * tiles_w;
+    const long long cap = (long long)ncc::sm_count() * 3;  // 3 CTAs of 71 registers x 256 threads fit an SM
+    fwd_tile_kernel<COUT><<<(int)(ntiles < cap ? ntiles : cap), 256, 0, st>>>(y, x, w, bias, g, tiles_h, tiles_w, (int)ntiles);
 }
 
 // partial[block][co][KP]; block handles pixels [blockIdx.x * per_block, +per_block)
@@ -160,6 +263,14 @@ int forward(float* y, const float* x, const long long xs[4], const float* w, con
     if ((reinterpret_cast<uintptr_t>(y) & 15u) != 0) return NC_CUDA_ERR_UNSUPPORTED;
     if (!fits_int(N, H, W, xs, g.Ho, g.Wo)) return NC_CUDA_ERR_UNSUPPORTED;
     const int pixels = N * g.Ho * g.Wo;
+    if (Cout == 16 || Cout == 32 || Cout == 64 || Cout == 128) {
+        if (Cout == 16) launch_fwd_tile<16>(y, x, w, bias, g, st);
+        else if (Cout == 32) launch_fwd_tile<32>(y, x, w, bias, g, st);
+        else if (Cout == 64) launch_fwd_tile<64>(y, x, w, bias, g, st);
+        else launch_fwd_tile<128>(y, x, w, bias, g, st);
+        NCC_COUNT_LAUNCH();
+        return ncc::launch_status("conv_first forward");
+    }
     const int ppb = 256 / (Cout / 16);
     long long need = ((long long)pixels + ppb - 1) / ppb;
     const long long cap = (long long)ncc::sm_count() * 8;

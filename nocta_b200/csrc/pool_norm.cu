@@ -236,15 +236,20 @@ __global__ void __launch_bounds__(256) colreduce4_kernel(double* __restrict__ pa
     if (r1 > rows) r1 = rows;
     double a[4] = {0, 0, 0, 0}, b[4] = {0, 0, 0, 0};
     if (c < cols) {
+        // four rows per step: four independent loads in flight, their values added in f32 (4 terms)
+        // before the running sums continue in double (the f32 -> f64 conversions would otherwise
+        // limit the kernel, not the memory system)
         size_t r = r0 + ty;
-        for (; r + TY < r1; r += 2 * TY) {
-            float4 u1, u2, w1, w2;
+        for (; r + 3 * (size_t)TY < r1; r += 4 * (size_t)TY) {
+            float4 u1, u2, w1, w2, p1, p2, q1, q2;
             f.vec(r, c, u1, u2);
             f.vec(r + TY, c, w1, w2);
-            a[0] += (double)u1.x + (double)w1.x; a[1] += (double)u1.y + (double)w1.y;
-            a[2] += (double)u1.z + (double)w1.z; a[3] += (double)u1.w + (double)w1.w;
-            b[0] += (double)u2.x + (double)w2.x; b[1] += (double)u2.y + (double)w2.y;
-            b[2] += (double)u2.z + (double)w2.z; b[3] += (double)u2.w + (double)w2.w;
+            f.vec(r + 2 * (size_t)TY, c, p1, p2);
+            f.vec(r + 3 * (size_t)TY, c, q1, q2);
+            a[0] += (double)((u1.x + w1.x) + (p1.x + q1.x)); a[1] += (double)((u1.y + w1.y) + (p1.y + q1.y));
+            a[2] += (double)((u1.z + w1.z) + (p1.z + q1.z)); a[3] += (double)((u1.w + w1.w) + (p1.w + q1.w));
+            b[0] += (double)((u2.x + w2.x) + (p2.x + q2.x)); b[1] += (double)((u2.y + w2.y) + (p2.y + q2.y));
+            b[2] += (double)((u2.z + w2.z) + (p2.z + q2.z)); b[3] += (double)((u2.w + w2.w) + (p2.w + q2.w));
         }
         for (; r < r1; r += TY) {
             float4 u1, u2;
@@ -465,6 +470,92 @@ __global__ void __launch_bounds__(kThreads) bn_apply_kernel(float* __restrict__ 
         if (VEC == 4) *reinterpret_cast<float4*>(y + e) = make_float4(out[0], out[1 % VEC], out[2 % VEC], out[3 % VEC]);
         else y[e] = out[0];
     }
+}
+
+// Channels-last fast path (C % 4 == 0, 16-byte aligned operands).  The launch makes the total thread
+// count times 4 a multiple of C, so a thread meets the same four channels on every grid-stride step:
+// their statistics and affine parameters are read once into registers and the loop body is three
+// flops per element around one float4 load and one float4 store.  The expression is the one of
+// bn_apply_kernel, term by term.
+template <int RELU>
+__global__ void __launch_bounds__(kThreads) bn_apply_nhwc4_kernel(float4* __restrict__ y, const float4* __restrict__ x,
+                                                                  const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                                  const float* __restrict__ mean, const float* __restrict__ var,
+                                                                  float eps, int C, size_t nvec, int rnd) {
+    const unsigned tid = blockIdx.x * kThreads + threadIdx.x, total = gridDim.x * kThreads;
+    const int c = (int)((tid * 4ull) % (unsigned)C);
+    float mu[4], is[4], g[4], b[4];
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+        mu[v] = mean[c + v];
+        is[v] = rsqrtf(var[c + v] + eps);
+        g[v] = gamma ? gamma[c + v] : 1.f;
+        b[v] = beta ? beta[c + v] : 0.f;
+    }
+#pragma unroll 4
+    for (size_t i = tid; i < nvec; i += total) {
+        const float4 t = x[i];
+        float o[4] = {g[0] * ((t.x - mu[0]) * is[0]) + b[0], g[1] * ((t.y - mu[1]) * is[1]) + b[1],
+                      g[2] * ((t.z - mu[2]) * is[2]) + b[2], g[3] * ((t.w - mu[3]) * is[3]) + b[3]};
+#pragma unroll
+        for (int v = 0; v < 4; v++) {
+            if (RELU && !(o[v] > 0.f)) o[v] = 0.f;
+            if (rnd) o[v] = round_tf32(o[v]);
+        }
+        y[i] = make_float4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+// MASK: 0 none, 1 read the forward output, 2 recompute the fused ReLU's sign from x.
+template <int MASK>
+__global__ void __launch_bounds__(kThreads) bn_bwd_apply_nhwc4_kernel(float4* __restrict__ dx, const float4* __restrict__ dy,
+                                                                      const float4* __restrict__ x, const float4* __restrict__ yfwd,
+                                                                      const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                                      const float* __restrict__ mean, const float* __restrict__ var,
+                                                                      const float* __restrict__ sums, float eps, float Mf, int C,
+                                                                      size_t nvec, int rnd) {
+    const unsigned tid = blockIdx.x * kThreads + threadIdx.x, total = gridDim.x * kThreads;
+    const int c = (int)((tid * 4ull) % (unsigned)C);
+    float mu[4], is[4], g[4], b[4], coeff[4], s1[4], s2[4];
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+        mu[v] = mean[c + v];
+        is[v] = rsqrtf(var[c + v] + eps);
+        g[v] = gamma ? gamma[c + v] : 1.f;
+        b[v] = beta ? beta[c + v] : 0.f;
+        coeff[v] = g[v] * is[v] / Mf;
+        s1[v] = sums[2 * (c + v)];
+        s2[v] = sums[2 * (c + v) + 1];
+    }
+#pragma unroll 2
+    for (size_t i = tid; i < nvec; i += total) {
+        const float4 t = x[i];
+        const float4 u = dy[i];
+        float4 yv = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (MASK == 1) yv = yfwd[i];
+        const float xv[4] = {t.x, t.y, t.z, t.w}, yy[4] = {yv.x, yv.y, yv.z, yv.w};
+        float gv[4] = {u.x, u.y, u.z, u.w}, o[4];
+#pragma unroll
+        for (int v = 0; v < 4; v++) {
+            const float xh = (xv[v] - mu[v]) * is[v];
+            if (MASK == 1 && !(yy[v] > 0.f)) gv[v] = 0.f;
+            if (MASK == 2 && !((g[v] * xh + b[v]) > 0.f)) gv[v] = 0.f;
+            o[v] = coeff[v] * (Mf * gv[v] - s1[v] - xh * s2[v]);
+            if (rnd) o[v] = round_tf32(o[v]);
+        }
+        dx[i] = make_float4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+// Grid for the channels-last fast path: blocks * kThreads * 4 must be a multiple of C.
+inline int nhwc4_grid(size_t nvec, int C) {
+    int a = C, b = kThreads * 4;
+    while (b) { int t = a % b; a = b; b = t; }
+    const int unit = C / a;  // C / gcd(C, 1024)
+    long long want = grid_for((long long)nvec, kThreads);
+    long long g = (want / unit) * unit;
+    if (g < unit) g = unit;
+    return (int)g;
 }
 
 __global__ void bn_bwd_finalize_kernel(const double* __restrict__ partial, int slabs, int C,
@@ -709,8 +800,11 @@ int nc_cuda_batchnorm_forward_f32_ex(float* y, const float* x, const float* gamm
         if (vec) bn_apply_kernel<0, 4><<<grid, kThreads, 0, st>>>(y, x, gamma, beta, save_mean, save_var, fe, C, spatial, nvec, relu, round_outputs() ? 1 : 0);
         else bn_apply_kernel<0, 1><<<grid, kThreads, 0, st>>>(y, x, gamma, beta, save_mean, save_var, fe, C, spatial, nvec, relu, round_outputs() ? 1 : 0);
     } else {
-        if (vec) bn_apply_kernel<1, 4><<<grid, kThreads, 0, st>>>(y, x, gamma, beta, save_mean, save_var, fe, C, spatial, nvec, relu, round_outputs() ? 1 : 0);
-        else bn_apply_kernel<1, 1><<<grid, kThreads, 0, st>>>(y, x, gamma, beta, save_mean, save_var, fe, C, spatial, nvec, relu, round_outputs() ? 1 : 0);
+        if (vec) {
+            const int g4 = nhwc4_grid(nvec, C);
+            if (relu) bn_apply_nhwc4_kernel<1><<<g4, kThreads, 0, st>>>((float4*)y, (const float4*)x, gamma, beta, save_mean, save_var, fe, C, nvec, round_outputs() ? 1 : 0);
+            else bn_apply_nhwc4_kernel<0><<<g4, kThreads, 0, st>>>((float4*)y, (const float4*)x, gamma, beta, save_mean, save_var, fe, C, nvec, round_outputs() ? 1 : 0);
+        } else bn_apply_kernel<1, 1><<<grid, kThreads, 0, st>>>(y, x, gamma, beta, save_mean, save_var, fe, C, spatial, nvec, relu, round_outputs() ? 1 : 0);
     }
     NCC_COUNT_LAUNCH();
     return launch_status("batchnorm_forward");
@@ -746,8 +840,13 @@ int nc_cuda_batchnorm_backward_f32_ex(float* dx, float* dgamma, float* dbeta, co
         if (vec) bn_bwd_apply_kernel<0, 4><<<grid, kThreads, 0, st>>>(dx, dy, x, mask, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec, round_outputs() ? 1 : 0);
         else bn_bwd_apply_kernel<0, 1><<<grid, kThreads, 0, st>>>(dx, dy, x, mask, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec, round_outputs() ? 1 : 0);
     } else {
-        if (vec) bn_bwd_apply_kernel<1, 4><<<grid, kThreads, 0, st>>>(dx, dy, x, mask, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec, round_outputs() ? 1 : 0);
-        else bn_bwd_apply_kernel<1, 1><<<grid, kThreads, 0, st>>>(dx, dy, x, mask, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec, round_outputs() ? 1 : 0);
+        if (vec) {
+            const int g4 = nhwc4_grid(nvec, C);
+            const int rnd = round_outputs() ? 1 : 0;
+            if (relu_out) bn_bwd_apply_nhwc4_kernel<1><<<g4, kThreads, 0, st>>>((float4*)dx, (const float4*)dy, (const float4*)x, (const float4*)relu_out, gamma, relu_beta, save_mean, save_var, sums, fe, Mf, C, nvec, rnd);
+            else if (relu_recompute) bn_bwd_apply_nhwc4_kernel<2><<<g4, kThreads, 0, st>>>((float4*)dx, (const float4*)dy, (const float4*)x, nullptr, gamma, relu_beta, save_mean, save_var, sums, fe, Mf, C, nvec, rnd);
+            else bn_bwd_apply_nhwc4_kernel<0><<<g4, kThreads, 0, st>>>((float4*)dx, (const float4*)dy, (const float4*)x, nullptr, gamma, relu_beta, save_mean, save_var, sums, fe, Mf, C, nvec, rnd);
+        } else bn_bwd_apply_kernel<1, 1><<<grid, kThreads, 0, st>>>(dx, dy, x, mask, gamma, save_mean, save_var, sums, fe, Mf, C, spatial, nvec, round_outputs() ? 1 : 0);
     }
     NCC_COUNT_LAUNCH();
     return launch_status("batchnorm_backward");
