@@ -3,8 +3,7 @@
 // not by arithmetic.  Forward: a shared-memory tiled kernel for the common channel counts (below), else
 // 4..16 threads per output pixel, 16 output channels each, the 27 patch values in registers.  Weight gradient: the reduction over all
 // pixels is split over CTAs; each CTA stages 64-pixel tiles of dY and of the 27-wide patches in shared
-// memory, every thread owns one output channel and 8 of the (padded to 32) patch positions; per-CTA
-// partial sums are combined in a fixed order.  No input gradient: the network input needs none.
+// memory (see dw_tile_kernel); per-CTA partial sums are combined in a fixed order.  No input gradient: the network input needs none.
 // Semantics: src/nn/conv.c:269-299 (dW), :381-586 (forward) of the reference.
 #include "nc_common.cuh"
 
@@ -178,60 +177,95 @@ static void launch_fwd_tile(float* y, const float* x, const float* w, const floa
     fwd_tile_kernel<COUT><<<(int)(ntiles < cap ? ntiles : cap), 256, 0, st>>>(y, x, w, bias, g, tiles_h, tiles_w, (int)ntiles);
 }
 
-// partial[block][co][KP]; block handles pixels [blockIdx.x * per_block, +per_block)
-constexpr int TP = 64;  // pixels per shared-memory tile
+// Tiled weight gradient for Cout in {32, 64}.  A CTA walks strips of 4 output rows x 64 columns; the
+// input halo of a strip is staged in shared memory, dY is read straight from global memory (every
+// element is needed by exactly one thread; a warp reads whole 128/256-byte pixel rows).  A warp takes
+// groups of 4 consecutive pixels; lane l owns output channels l*CPT..+CPT-1 and ALL 27 taps, so the six
+// input values of a (ci, kh) row (one float4 + one float2, broadcast) feed 12*CPT FMAs.  The 8 warps'
+// sums are combined in warp order at the end, then the per-CTA partials by dw_reduce_kernel.
+// partial[block][co][KP]
 template <int COUT>
-__global__ void __launch_bounds__(COUT * 4) dw_kernel(float* __restrict__ partial, const float* __restrict__ dy,
-                                                      const float* __restrict__ in, Geo g, int pixels, int per_block) {
-    __shared__ __align__(16) float sdy[TP][COUT];
-    __shared__ __align__(16) float sx[TP][KP];
-    const int co = threadIdx.x % COUT, grp = threadIdx.x / COUT;  // grp 0..3 -> patch positions grp*8 .. +7
-    float acc[8];
+__global__ void __launch_bounds__(256) dw_tile_kernel(float* __restrict__ partial, const float* __restrict__ dy,
+                                                      const float* __restrict__ in, Geo g, int tiles_h, int tiles_w, int ntiles) {
+    constexpr int CPT = COUT / 32, TR = 4, ROWS = TR + 2, RS = (K * CPT) | 1;
+    __shared__ __align__(16) float tile[3][ROWS][TWP];
+    __shared__ float red[32][RS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float acc[CPT][K];
 #pragma unroll
-    for (int j = 0; j < 8; j++) acc[j] = 0.f;
-    const int p0 = blockIdx.x * per_block;
-    int p1 = p0 + per_block;
-    if (p1 > pixels) p1 = pixels;
-    const int kk = threadIdx.x % KP;  // this thread's patch position while staging
-    const int kkw = kk % 3, kkh = (kk / 3) % 3, kci = kk / 9;
-    const int koff = kci * g.xs[1] + kkh * g.xs[2] + kkw * g.xs[3];
-    for (int base = p0; base < p1; base += TP) {
-        const int cnt = (p1 - base) < TP ? (p1 - base) : TP;
-        // dY tile: rows are contiguous in channels-last memory
-        for (int i = threadIdx.x; i < TP * COUT / 4; i += blockDim.x) {
-            const int r = i / (COUT / 4), c4 = i % (COUT / 4);
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (r < cnt) v = reinterpret_cast<const float4*>(dy + (size_t)(base + r) * COUT)[c4];
-            reinterpret_cast<float4*>(&sdy[r][0])[c4] = v;
-        }
-        // patches: one (pixel, position) per thread-iteration
-        for (int r = threadIdx.x / KP; r < TP; r += blockDim.x / KP) {
+    for (int j = 0; j < CPT; j++)
+#pragma unroll
+        for (int k = 0; k < K; k++) acc[j][k] = 0.f;
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+        const int tw = t % tiles_w;
+        const int t2 = t / tiles_w;
+        const int th = t2 % tiles_h, n = t2 / tiles_h;
+        const int ho0 = th * TR, wo0 = tw * TW;
+        __syncthreads();
+        for (int i = threadIdx.x; i < 3 * ROWS * 66; i += 256) {
+            const int cc = i % 66;
+            const int q = i / 66;
+            const int r = q % ROWS, ci = q / ROWS;
+            const int h = ho0 - g.pad + r, wc = wo0 - g.pad + cc;
             float v = 0.f;
-            if (r < cnt && kk < K) {
-                const int p = base + r;
-                const int wo = p % g.Wo;
-                const int t = p / g.Wo;
-                const int ho = t % g.Ho, n = t / g.Ho;
-                const int h = ho + kkh - g.pad, w = wo + kkw - g.pad;
-                if ((unsigned)h < (unsigned)g.H && (unsigned)w < (unsigned)g.W)
-                    v = in[n * g.xs[0] + (ho - g.pad) * g.xs[2] + (wo - g.pad) * g.xs[3] + koff];
+            if ((unsigned)h < (unsigned)g.H && (unsigned)wc < (unsigned)g.W)
+                v = in[n * g.xs[0] + ci * g.xs[1] + h * g.xs[2] + wc * g.xs[3]];
+            tile[ci][r][cc] = v;
+        }
+        __syncthreads();
+#pragma unroll 1
+        for (int grp = warp; grp < TR * (TW / 4); grp += 8) {
+            const int prow = grp / (TW / 4), pcol = (grp % (TW / 4)) * 4;
+            const int ho = ho0 + prow;
+            if (ho >= g.Ho || wo0 + pcol >= g.Wo) continue;  // warp-uniform
+            const float* src = dy + ((size_t)(n * g.Ho + ho) * g.Wo + wo0 + pcol) * COUT + lane * CPT;
+            float d[4][CPT];
+#pragma unroll
+            for (int p = 0; p < 4; p++) {
+                const bool ok = wo0 + pcol + p < g.Wo;
+                if (CPT == 2) {
+                    float2 v = ok ? *reinterpret_cast<const float2*>(src + (size_t)p * COUT) : make_float2(0.f, 0.f);
+                    d[p][0] = v.x; d[p][CPT - 1] = v.y;
+                } else {
+                    d[p][0] = ok ? src[(size_t)p * COUT] : 0.f;
+                }
             }
-            sx[r][kk] = v;
+#pragma unroll
+            for (int ci = 0; ci < 3; ci++)
+#pragma unroll
+                for (int kh = 0; kh < 3; kh++) {
+                    const float* row = &tile[ci][prow + kh][pcol];
+                    const float4 xa = *reinterpret_cast<const float4*>(row);
+                    const float2 xb = *reinterpret_cast<const float2*>(row + 4);
+                    const float xv[6] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y};
+#pragma unroll
+                    for (int kw = 0; kw < 3; kw++)
+#pragma unroll
+                        for (int p = 0; p < 4; p++)
+#pragma unroll
+                            for (int j = 0; j < CPT; j++)
+                                acc[j][(ci * 3 + kh) * 3 + kw] = fmaf(d[p][j], xv[p + kw], acc[j][(ci * 3 + kh) * 3 + kw]);
+                }
         }
-        __syncthreads();
-#pragma unroll 4
-        for (int r = 0; r < TP; r++) {
-            const float d = sdy[r][co];
-            const float4 a = *reinterpret_cast<const float4*>(&sx[r][grp * 8]);
-            const float4 b = *reinterpret_cast<const float4*>(&sx[r][grp * 8 + 4]);
-            acc[0] = fmaf(d, a.x, acc[0]); acc[1] = fmaf(d, a.y, acc[1]); acc[2] = fmaf(d, a.z, acc[2]); acc[3] = fmaf(d, a.w, acc[3]);
-            acc[4] = fmaf(d, b.x, acc[4]); acc[5] = fmaf(d, b.y, acc[5]); acc[6] = fmaf(d, b.z, acc[6]); acc[7] = fmaf(d, b.w, acc[7]);
-        }
-        __syncthreads();
     }
-    float* dst = partial + ((size_t)blockIdx.x * COUT + co) * KP + grp * 8;
-    reinterpret_cast<float4*>(dst)[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    reinterpret_cast<float4*>(dst)[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    // combine the 8 warps in warp order
+    for (int wq = 0; wq < 8; wq++) {
+        __syncthreads();
+        if (warp == wq) {
+#pragma unroll
+            for (int j = 0; j < CPT; j++)
+#pragma unroll
+                for (int k = 0; k < K; k++) {
+                    if (wq == 0) red[lane][j * K + k] = acc[j][k];
+                    else red[lane][j * K + k] += acc[j][k];
+                }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < COUT * K; i += 256) {
+        const int co = i / K, k = i % K;
+        partial[((size_t)blockIdx.x * COUT + co) * KP + k] = red[co / CPT][(co % CPT) * K + k];
+    }
 }
 
 __global__ void __launch_bounds__(256) dw_reduce_kernel(float* __restrict__ dW, const float* __restrict__ partial, int blocks, int Cout) {
@@ -287,15 +321,15 @@ int weight_grad(float* dW, const float* dy, const float* x, const long long xs[4
     if (g.Ho <= 0 || g.Wo <= 0) return NC_CUDA_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(dy) & 15u) != 0) return NC_CUDA_ERR_UNSUPPORTED;
     if (!fits_int(N, H, W, xs, g.Ho, g.Wo)) return NC_CUDA_ERR_UNSUPPORTED;
-    const int pixels = N * g.Ho * g.Wo;
-    long long blocks = (long long)ncc::sm_count() * 4;
-    long long per = ((long long)pixels + blocks - 1) / blocks;
-    per = ((per + TP - 1) / TP) * TP;
-    blocks = (pixels + per - 1) / per;
+    constexpr int TRW = 4;  // rows per strip of dw_tile_kernel
+    const int tiles_h = (g.Ho + TRW - 1) / TRW, tiles_w = (g.Wo + TW - 1) / TW;
+    const long long ntiles = (long long)N * tiles_h * tiles_w;
+    long long blocks = (long long)ncc::sm_count() * 3;
+    if (blocks > ntiles) blocks = ntiles;
     float* partial = (float*)ncc::scratch(2, sizeof(float) * (size_t)blocks * Cout * KP, st);
     if (!partial) return NC_CUDA_ERR_RUNTIME;
-    if (Cout == 64) dw_kernel<64><<<(int)blocks, 256, 0, st>>>(partial, dy, x, g, pixels, (int)per);
-    else dw_kernel<32><<<(int)blocks, 128, 0, st>>>(partial, dy, x, g, pixels, (int)per);
+    if (Cout == 64) dw_tile_kernel<64><<<(int)blocks, 256, 0, st>>>(partial, dy, x, g, tiles_h, tiles_w, (int)ntiles);
+    else dw_tile_kernel<32><<<(int)blocks, 256, 0, st>>>(partial, dy, x, g, tiles_h, tiles_w, (int)ntiles);
     NCC_COUNT_LAUNCH();
     dw_reduce_kernel<<<ncc::ceil_div(Cout * K * 32, 256), 256, 0, st>>>(dW, partial, (int)blocks, Cout);
     NCC_COUNT_LAUNCH();

@@ -236,16 +236,17 @@ __global__ void __launch_bounds__(256) colreduce4_kernel(double* __restrict__ pa
     if (r1 > rows) r1 = rows;
     double a[4] = {0, 0, 0, 0}, b[4] = {0, 0, 0, 0};
     if (c < cols) {
+        const typename F::Ctx ctx = f.prepare(c);  // per-column constants, read once
         // four rows per step: four independent loads in flight, their values added in f32 (4 terms)
         // before the running sums continue in double (the f32 -> f64 conversions would otherwise
         // limit the kernel, not the memory system)
         size_t r = r0 + ty;
         for (; r + 3 * (size_t)TY < r1; r += 4 * (size_t)TY) {
             float4 u1, u2, w1, w2, p1, p2, q1, q2;
-            f.vec(r, c, u1, u2);
-            f.vec(r + TY, c, w1, w2);
-            f.vec(r + 2 * (size_t)TY, c, p1, p2);
-            f.vec(r + 3 * (size_t)TY, c, q1, q2);
+            f.vec(ctx, r, c, u1, u2);
+            f.vec(ctx, r + TY, c, w1, w2);
+            f.vec(ctx, r + 2 * (size_t)TY, c, p1, p2);
+            f.vec(ctx, r + 3 * (size_t)TY, c, q1, q2);
             a[0] += (double)((u1.x + w1.x) + (p1.x + q1.x)); a[1] += (double)((u1.y + w1.y) + (p1.y + q1.y));
             a[2] += (double)((u1.z + w1.z) + (p1.z + q1.z)); a[3] += (double)((u1.w + w1.w) + (p1.w + q1.w));
             b[0] += (double)((u2.x + w2.x) + (p2.x + q2.x)); b[1] += (double)((u2.y + w2.y) + (p2.y + q2.y));
@@ -253,7 +254,7 @@ __global__ void __launch_bounds__(256) colreduce4_kernel(double* __restrict__ pa
         }
         for (; r < r1; r += TY) {
             float4 u1, u2;
-            f.vec(r, c, u1, u2);
+            f.vec(ctx, r, c, u1, u2);
             a[0] += u1.x; a[1] += u1.y; a[2] += u1.z; a[3] += u1.w;
             b[0] += u2.x; b[1] += u2.y; b[2] += u2.z; b[3] += u2.w;
         }
@@ -302,7 +303,9 @@ struct BnFwdSum {  // (x, x^2)
     __device__ void operator()(size_t r, int c, float& v1, float& v2) const {
         float t = x[r * cols + c]; v1 = t; v2 = t * t;
     }
-    __device__ void vec(size_t r, int c, float4& v1, float4& v2) const {
+    struct Ctx {};
+    __device__ Ctx prepare(int) const { return Ctx{}; }
+    __device__ void vec(const Ctx&, size_t r, int c, float4& v1, float4& v2) const {
         v1 = *reinterpret_cast<const float4*>(x + r * cols + c);
         v2 = make_float4(v1.x * v1.x, v1.y * v1.y, v1.z * v1.z, v1.w * v1.w);
     }
@@ -331,20 +334,35 @@ struct BnBwdSum {
         if (m.dead(i, xh, c)) g = 0.f;
         v1 = g; v2 = g * xh;
     }
-    __device__ void vec(size_t r, int c, float4& v1, float4& v2) const {
+    struct Ctx { float mu[4], is[4], g[4], b[4]; };
+    __device__ Ctx prepare(int c) const {
+        Ctx k;
+#pragma unroll
+        for (int v = 0; v < 4; v++) {
+            k.mu[v] = mean[c + v];
+            k.is[v] = rsqrtf(var[c + v] + eps);
+            k.g[v] = m.gamma ? m.gamma[c + v] : 1.f;
+            k.b[v] = m.beta ? m.beta[c + v] : 0.f;
+        }
+        return k;
+    }
+    __device__ void vec(const Ctx& k, size_t r, int c, float4& v1, float4& v2) const {
         const size_t i = r * cols + c;
-        float4 g = *reinterpret_cast<const float4*>(dy + i);
-        const float4 xv = *reinterpret_cast<const float4*>(x + i);
-        const float4 mu = *reinterpret_cast<const float4*>(mean + c);
-        const float4 vr = *reinterpret_cast<const float4*>(var + c);
-        const float4 xh = make_float4((xv.x - mu.x) * rsqrtf(vr.x + eps), (xv.y - mu.y) * rsqrtf(vr.y + eps),
-                                      (xv.z - mu.z) * rsqrtf(vr.z + eps), (xv.w - mu.w) * rsqrtf(vr.w + eps));
-        if (m.dead(i, xh.x, c)) g.x = 0.f;
-        if (m.dead(i + 1, xh.y, c + 1)) g.y = 0.f;
-        if (m.dead(i + 2, xh.z, c + 2)) g.z = 0.f;
-        if (m.dead(i + 3, xh.w, c + 3)) g.w = 0.f;
-        v1 = g;
-        v2 = make_float4(g.x * xh.x, g.y * xh.y, g.z * xh.z, g.w * xh.w);
+        const float4 gq = *reinterpret_cast<const float4*>(dy + i);
+        const float4 xq = *reinterpret_cast<const float4*>(x + i);
+        float4 yq = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (m.y) yq = *reinterpret_cast<const float4*>(m.y + i);
+        const float xv[4] = {xq.x, xq.y, xq.z, xq.w}, yv[4] = {yq.x, yq.y, yq.z, yq.w};
+        float g[4] = {gq.x, gq.y, gq.z, gq.w}, gx[4];
+#pragma unroll
+        for (int v = 0; v < 4; v++) {
+            const float xh = (xv[v] - k.mu[v]) * k.is[v];
+            if (m.y) { if (!(yv[v] > 0.f)) g[v] = 0.f; }
+            else if (m.recompute && !((k.g[v] * xh + k.b[v]) > 0.f)) g[v] = 0.f;
+            gx[v] = g[v] * xh;
+        }
+        v1 = make_float4(g[0], g[1], g[2], g[3]);
+        v2 = make_float4(gx[0], gx[1], gx[2], gx[3]);
     }
 };
 struct BnBwdSumFlat {
@@ -365,7 +383,9 @@ struct LnParamSum {
         float gv = g[i];
         v1 = gv * ((x[i] - s.x) * s.y); v2 = gv;
     }
-    __device__ void vec(size_t r, int c, float4& v1, float4& v2) const {
+    struct Ctx {};
+    __device__ Ctx prepare(int) const { return Ctx{}; }
+    __device__ void vec(const Ctx&, size_t r, int c, float4& v1, float4& v2) const {
         const size_t i = r * cols + c;
         const float2 s = stats[r];
         const float4 gv = *reinterpret_cast<const float4*>(g + i);
@@ -389,7 +409,16 @@ int launch_colreduce(double** partial_out, int* slabs_out, size_t rows, int cols
         col_tiles = ceil_div(cols, 32);
     }
     const size_t min_rows = vec ? (size_t)(256 / TX) * 4 : 64;
-    int want = (sm_count() * 4 + col_tiles - 1) / col_tiles;
+    // one wave: as many CTAs as are resident at once for this functor's register use
+    static int occ4 = 0, occ1 = 0;  // per template instance
+    int& occ = vec ? occ4 : occ1;
+    if (occ == 0) {
+        cudaError_t e = vec ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, colreduce4_kernel<F>, 256, 0)
+                            : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, colreduce_kernel<F>, 256, 0);
+        if (e != cudaSuccess || occ < 1) { occ = 2; (void)cudaGetLastError(); }
+        if (occ > 4) occ = 4;
+    }
+    int want = (sm_count() * occ + col_tiles - 1) / col_tiles;
     size_t rps = (rows + want - 1) / want;
     if (rps < min_rows) rps = min_rows;
     int slabs = (int)((rows + rps - 1) / rps);
@@ -717,7 +746,9 @@ __global__ void ln_param_finalize_kernel(const double* __restrict__ partial, int
 struct ColSum {  // (x, 0)
     const float* x; int cols;
     __device__ void operator()(size_t r, int c, float& v1, float& v2) const { v1 = x[r * cols + c]; v2 = 0.f; }
-    __device__ void vec(size_t r, int c, float4& v1, float4& v2) const {
+    struct Ctx {};
+    __device__ Ctx prepare(int) const { return Ctx{}; }
+    __device__ void vec(const Ctx&, size_t r, int c, float4& v1, float4& v2) const {
         v1 = *reinterpret_cast<const float4*>(x + r * cols + c);
         v2 = make_float4(0.f, 0.f, 0.f, 0.f);
     }
