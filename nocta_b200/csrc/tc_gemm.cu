@@ -190,8 +190,21 @@ struct TileCfg {
     static constexpr int TMEM_COLS = ACC_COLS * NACC * NBUF;
 };
 
+// MN-major operands arrive as one copy per 32-wide chunk (up to 12 per stage) and a thread spends on the
+// order of a hundred cycles per copy it issues, so those kernels run extra producer warps (warps 6..,
+// lane 0 each): up to two producers share the A chunks and up to four the B chunks, round-robin.  Every
+// producer waits for the ring slot itself and arms the stage barrier with its own byte count.
+template <bool A_MN, bool B_MN, int BN>
+struct ProdCfg {
+    static constexpr bool MULTI = A_MN || B_MN;
+    static constexpr int NA_OWNERS = !MULTI ? 1 : (A_MN ? 2 : 1);
+    static constexpr int NB_OWNERS = !MULTI ? 0 : (B_MN ? (BN / 32 < 4 ? BN / 32 : 4) : 1);
+    static constexpr int NPROD = MULTI ? NA_OWNERS + NB_OWNERS : 1;
+    static constexpr int THREADS = 192 + 32 * (NPROD - 1);
+};
+
 template <int BN, bool A_MN, bool B_MN, int MODE>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(352, 1)
 tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
     using Cfg = TileCfg<BN, MODE>;
     constexpr int NBUF = Cfg::NBUF;  // accumulator buffers in tensor memory (2 = epilogue overlaps the next tile)
@@ -211,7 +224,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_full[s]), (uint32_t)ProdCfg<A_MN, B_MN, BN>::NPROD);
             mbar_init(smem_u32(&bar_empty[s]), 1);
             mbar_init(smem_u32(&bar_conv[s]), 128);
         }
@@ -239,7 +252,100 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     // t -> (n_tile fastest, then m_tile, then reduction split z).
     const int total_tiles = p.tiles_m * p.tiles_n * p.splits;
 
-    if (warp == 0) {
+    if (ProdCfg<A_MN, B_MN, BN>::MULTI && (warp == 0 || warp >= 6)) {
+        // ------------------------------ TMA producers (MN-major operands) ------------------------------
+        if (lane == 0) {
+            using PC = ProdCfg<A_MN, B_MN, BN>;
+            const int me = warp == 0 ? 0 : warp - 5;  // producer index
+            const bool forA = me < PC::NA_OWNERS;
+            const int own = forA ? me : me - PC::NA_OWNERS;         // first chunk this producer owns
+            const int step = forA ? PC::NA_OWNERS : PC::NB_OWNERS;  // and the stride to its next one
+            constexpr int NACH = A_MN ? BM / 32 : 1;  // copies of operand A per stage
+            constexpr int NBCH = B_MN ? BN / 32 : 1;  // copies of operand B per stage
+            int my_n = 0;                             // copies this producer issues per stage
+            for (int c = own; c < (forA ? NACH : NBCH); c += step) my_n++;
+            const uint32_t my_bytes = forA ? (A_MN ? (uint32_t)my_n * CHUNK_BYTES : (uint32_t)A_BYTES)
+                                           : (B_MN ? (uint32_t)my_n * CHUNK_BYTES : (uint32_t)Cfg::B_BYTES);
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int n_tile = t % p.tiles_n, r_ = t / p.tiles_n, m_tile = r_ % p.tiles_m, z = r_ / p.tiles_m;
+                const int kt_begin = z * p.k_tiles_per_split;
+                int kt_end = kt_begin + p.k_tiles_per_split;
+                if (kt_end > p.num_k_tiles) kt_end = p.num_k_tiles;
+                const int m0 = m_tile * BM, n0 = n_tile * BN;
+                int dtw = 0, dth = 0, dtn = 0;
+                // DW: (first channel, tap) of this producer's B chunks
+                int ci0[4] = {0, 0, 0, 0}, dkh[4] = {0, 0, 0, 0}, dkw[4] = {0, 0, 0, 0};
+                if (p.kind == KIND_DW) {
+                    dtw = kt_begin % p.tiles_w;
+                    const int tt = kt_begin / p.tiles_w;
+                    dth = tt % p.tiles_h; dtn = tt / p.tiles_h;
+                    if (!forA) {
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const int col = n0 + 32 * (own + i * step);
+                            const int sh = col / p.Cin;
+                            ci0[i] = col - sh * p.Cin;
+                            dkh[i] = sh / p.kW; dkw[i] = sh - dkh[i] * p.kW;
+                        }
+                    }
+                }
+                for (int kt = kt_begin; kt < kt_end; kt++) {
+                    if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, p.err, 0x100u + s, abortp)) { ok = false; break; }
+                    const uint32_t full = smem_u32(&bar_full[s]);
+                    const uint32_t a_dst = tiles_base + (uint32_t)s * Cfg::STAGE_BYTES;
+                    const uint32_t b_dst = a_dst + A_BYTES;
+                    if (p.desc_variant == 13) {
+                        mbar_arrive(full);
+                    } else {
+                        mbar_expect_tx(full, my_bytes);
+                        if (p.kind == KIND_GEMM) {
+                            const int k0 = kt * BK;
+                            if (forA) {
+                                if (!A_MN) tma_2d(a_dst, &tmA, k0, m0, full);
+                                else {
+#pragma unroll
+                                    for (int i = 0; i < 4; i++) {
+                                        const int c = own + i * step;
+                                        if (c < NACH) tma_2d(a_dst + c * CHUNK_BYTES, &tmA, m0 + 32 * c, k0, full);
+                                    }
+                                }
+                            } else if (!B_MN) {
+                                tma_2d(b_dst, &tmB, k0, n0, full);
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 4; i++) {
+                                    const int c = own + i * step;
+                                    if (c < NBCH) tma_2d(b_dst + c * CHUNK_BYTES, &tmB, n0 + 32 * c, k0, full);
+                                }
+                            }
+                        } else {  // KIND_DW (both operands MN-major)
+                            const int w0 = dtw * p.bw, h0 = dth * p.bh, nn0 = dtn * p.bn;
+                            if (forA) {
+#pragma unroll
+                                for (int i = 0; i < 4; i++) {
+                                    const int c = own + i * step;
+                                    if (c < NACH) tma_4d(a_dst + c * CHUNK_BYTES, &tmA, m0 + 32 * c, w0, h0, nn0, full);
+                                }
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 4; i++) {
+                                    const int c = own + i * step;
+                                    if (c < NBCH) tma_4d(b_dst + c * CHUNK_BYTES, &tmB, ci0[i], w0 + dkw[i] - p.pad, h0 + dkh[i] - p.pad, nn0, full);
+                                }
+                            }
+                        }
+                    }
+                    if (p.kind == KIND_DW) {
+                        if (++dtw == p.tiles_w) { dtw = 0; if (++dth == p.tiles_h) { dth = 0; dtn++; } }
+                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             // One thread feeds the whole CTA, so its loop is kept free of divisions and runtime modulo:
@@ -276,6 +382,11 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                 for (int kt = kt_begin; kt < kt_end; kt++) {
                     if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, p.err, 0x100u + s, abortp)) { ok = false; break; }
                     const uint32_t full = smem_u32(&bar_full[s]);
+                    if (p.desc_variant == 13) {  // timing experiment: no copies, the MMAs run on whatever is in shared memory
+                        mbar_arrive(full);
+                        if (++s == STAGES) { s = 0; ph ^= 1u; }
+                        continue;
+                    }
                     mbar_expect_tx(full, (uint32_t)Cfg::OPER_BYTES);
                     const uint32_t a_dst = tiles_base + (uint32_t)s * Cfg::STAGE_BYTES;
                     const uint32_t b_dst = a_dst + A_BYTES;
@@ -379,7 +490,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                 if (ok) umma_commit(smem_u32(&bar_acc_full[ab]));
             }
         }
-    } else {
+    } else if (warp < 6) {
         // ------------------------------ converter + epilogue warps ------------------------------
         const int te = threadIdx.x - 64;  // 0..127
         const int q = warp & 3;           // TMEM lane quadrant this warp may read
@@ -577,6 +688,229 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
 }
 
 // ------------------------------------------------------------------------------------------
+// CONVH: stride-1 convolution (filters up to 3 x 3) with the activation halo resident in shared memory
+// ------------------------------------------------------------------------------------------
+// The operand traffic from L2 into shared memory, not the tensor pipe, bounds the kernel above for
+// convolutions: every filter tap re-reads the same pixels.  Here a CTA owns a 16 x 16 pixel tile of one
+// image and up to 128 output channels.  Per 32-channel chunk it loads the (16+kH-1) x (16+kW-1) halo
+// ONCE (one 4-D TMA box, zero fill = padding) and issues the MMAs of all kH*kW taps against it: the B
+// operand of tap (kh, kw) is the same shared-memory buffer with the descriptor start moved by
+// (kh * pitch + kw) pixel rows of 128 bytes (the 128-byte swizzle is a function of the absolute shared
+// address, so a start that is not 1024-byte aligned needs no correction), 8-row groups one halo line
+// (pitch rows) apart.  The 16 x 16 tile is two MMAs of N = 128 (left and right 8 columns).  Only the
+// 16 KB weight tile of a tap streams per 512 MMA cycles: about 40 bytes per cycle instead of 96.
+constexpr int kConvhWStages = 6;
+struct ConvhParams {
+    float* D;
+    int ldd;
+    const float* bias;
+    int M;                 // output channels
+    int Ho, Wo;
+    int tiles_w, tiles_h;  // pixel tiles per image
+    int tiles_px;          // pixel tiles in total (images * tiles_h * tiles_w)
+    int tiles_m;           // 128-channel tiles
+    int kH, kW, pad;
+    int cchunks;           // 32-channel chunks of the input channels
+    int wrows;             // rows per tap in the packed weights
+    int pitch;             // halo line pitch in pixels
+    int halo_bytes, halo_stride;
+    int skip_loads;        // experiment: 1 = no weight copies, 2 = no halo copies, 3 = neither (timing only)
+    unsigned int* err;
+};
+
+template <int TW, int TH>  // pixel tile: 16 x 16 (two MMAs of N = 128 per k-step) or 8 x 32 (one MMA of N = 256)
+__global__ void __launch_bounds__(192, 1)
+convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const ConvhParams p) {
+    static_assert(TW * TH == 256 && TW % 8 == 0, "256 pixels per tile");
+    constexpr int WS = kConvhWStages;
+    constexpr int NSUB = TW / 8, NMMA = 8 * TH;  // MMAs per k-step and their N
+    extern __shared__ uint8_t dyn_smem[];
+    __shared__ __align__(8) uint64_t bar_hfull[2];
+    __shared__ __align__(8) uint64_t bar_hempty[2];
+    __shared__ __align__(8) uint64_t bar_wfull[WS];
+    __shared__ __align__(8) uint64_t bar_wempty[WS];
+    __shared__ __align__(8) uint64_t bar_acc_full[2];
+    __shared__ __align__(8) uint64_t bar_acc_empty[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t halo_base = (smem_u32(dyn_smem) + 1023u) & ~1023u;
+    const uint32_t w_base = halo_base + 2u * (uint32_t)p.halo_stride;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < 2; s++) {
+            mbar_init(smem_u32(&bar_hfull[s]), 1);
+            mbar_init(smem_u32(&bar_hempty[s]), 1);
+            mbar_init(smem_u32(&bar_acc_full[s]), 1);
+            mbar_init(smem_u32(&bar_acc_empty[s]), 128);
+        }
+        for (int s = 0; s < WS; s++) {
+            mbar_init(smem_u32(&bar_wfull[s]), 1);
+            mbar_init(smem_u32(&bar_wempty[s]), 1);
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    volatile int* abortp = &abort_flag;
+    const int total_tiles = p.tiles_px * p.tiles_m;  // t -> (pixel tile fastest, then channel tile)
+    const int ntaps = p.kH * p.kW;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------- producer: halo boxes (one chunk ahead) and weight tiles ----------------
+            int ht = blockIdx.x, hcc = 0;   // cursor of the next halo to request
+            uint32_t hcount = 0;
+            bool ok = true;
+            auto issue_halo = [&]() {
+                if (ht >= total_tiles || !ok) return;
+                const uint32_t slot = hcount & 1u;
+                if (!mbar_wait(smem_u32(&bar_hempty[slot]), ((hcount >> 1) & 1u) ^ 1u, p.err, 0x600u + slot, abortp)) { ok = false; return; }
+                const int pt = ht % p.tiles_px;
+                const int tw = pt % p.tiles_w, tt = pt / p.tiles_w;
+                const int th = tt % p.tiles_h, n = tt / p.tiles_h;
+                const uint32_t full = smem_u32(&bar_hfull[slot]);
+                if (p.skip_loads & 2) mbar_arrive(full);
+                else {
+                    mbar_expect_tx(full, (uint32_t)p.halo_bytes);
+                    tma_4d(halo_base + slot * (uint32_t)p.halo_stride, &tmX, hcc * 32, tw * TW - p.pad, th * TH - p.pad, n, full);
+                }
+                hcount++;
+                if (++hcc == p.cchunks) { hcc = 0; ht += gridDim.x; }
+            };
+            int lead = WS < ntaps - 1 ? WS : ntaps - 1;  // weight tap after which the next halo is requested
+            if (lead < 0) lead = 0;
+            int s = 0;
+            uint32_t ph = 0;
+            issue_halo();
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int m0 = (t / p.tiles_px) * BM;
+                for (int cc = 0; cc < p.cchunks && ok; cc++) {
+                    int wrow = m0;
+                    for (int tap = 0; tap < ntaps; tap++, wrow += p.wrows) {
+                        if (tap == lead) issue_halo();
+                        if (!ok) break;
+                        if (!mbar_wait(smem_u32(&bar_wempty[s]), ph ^ 1u, p.err, 0x100u + s, abortp)) { ok = false; break; }
+                        const uint32_t full = smem_u32(&bar_wfull[s]);
+                        if (p.skip_loads & 1) mbar_arrive(full);
+                        else {
+                            mbar_expect_tx(full, (uint32_t)A_BYTES);
+                            tma_2d(w_base + (uint32_t)s * A_BYTES, &tmW, cc * 32, wrow, full);
+                        }
+                        if (++s == WS) { s = 0; ph ^= 1u; }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---------------- MMA issuer ----------------
+            // D = f32, A = B = tf32, both K-major, M = 128
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(NMMA >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            const uint64_t da0 = smem_desc(w_base, 16u, 1024u, 2u);
+            const uint64_t db0 = smem_desc(halo_base, 16u, (uint32_t)p.pitch * 128u, 2u);
+            int s = 0;
+            uint32_t ph = 0, tile_iter = 0, hcount = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, tile_iter++) {
+                const uint32_t ab = tile_iter & 1u;
+                if (!mbar_wait(smem_u32(&bar_acc_empty[ab]), ((tile_iter >> 1) & 1u) ^ 1u, p.err, 0x500u + ab, abortp)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t acc = tmem_base + ab * 256u;
+                for (int cc = 0; cc < p.cchunks && ok; cc++, hcount++) {
+                    const uint32_t slot = hcount & 1u;
+                    if (!mbar_wait(smem_u32(&bar_hfull[slot]), (hcount >> 1) & 1u, p.err, 0x700u + slot, abortp)) { ok = false; break; }
+                    const uint64_t dbs = db0 + (uint64_t)((slot * (uint32_t)p.halo_stride) >> 4);
+                    int kh = 0, kw = 0;
+                    for (int tap = 0; tap < ntaps; tap++) {
+                        if (!mbar_wait(smem_u32(&bar_wfull[s]), ph, p.err, 0x200u + s, abortp)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint64_t da = da0 + (uint64_t)(((uint32_t)s * (uint32_t)A_BYTES) >> 4);
+                        const uint64_t db = dbs + (uint64_t)(((uint32_t)(kh * p.pitch + kw) * 128u) >> 4);
+#pragma unroll
+                        for (int ks = 0; ks < BK / 8; ks++) {
+                            const uint32_t accum = (uint32_t)((cc | tap | ks) != 0);
+#pragma unroll
+                            for (int sub = 0; sub < NSUB; sub++)  // sub-tile of 8 columns: + 8 pixel rows in the halo
+                                umma_tf32(acc + (uint32_t)(sub * NMMA), da + (uint64_t)(ks * 2), db + (uint64_t)(ks * 2 + sub * 64), idesc, accum);
+                        }
+                        umma_commit(smem_u32(&bar_wempty[s]));
+                        if (++s == WS) { s = 0; ph ^= 1u; }
+                        if (++kw == p.kW) { kw = 0; kh++; }
+                    }
+                    if (ok) umma_commit(smem_u32(&bar_hempty[slot]));
+                }
+                if (ok) umma_commit(smem_u32(&bar_acc_full[ab]));
+            }
+        }
+    } else {
+        // ---------------- epilogue warps: lane = output channel, column = pixel ----------------
+        const int q = warp & 3;
+        const int r = q * 32 + lane;
+        uint32_t tile_iter = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, tile_iter++) {
+            const int pt = t % p.tiles_px, m0 = (t / p.tiles_px) * BM;
+            const int tw = pt % p.tiles_w, tt = pt / p.tiles_w;
+            const int th = tt % p.tiles_h, n = tt / p.tiles_h;
+            const uint32_t ab = tile_iter & 1u;
+            ok = mbar_wait(smem_u32(&bar_acc_full[ab]), (tile_iter >> 1) & 1u, p.err, 0x400u + ab, abortp);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t acc = tmem_base + ab * 256u + ((uint32_t)(q * 32) << 16);
+            const int co = m0 + r;
+            const bool co_ok = co < p.M;
+            const float bv = (co_ok && p.bias) ? p.bias[co] : 0.f;
+            // first pixel of the tile; a column chunk of 32 = 4 lines x 8 pixels of one 8-column sub-tile
+            float* tile_dst = p.D + (((long long)n * p.Ho + th * TH) * p.Wo + tw * TW) * p.ldd + co;
+            const int line = p.Wo * p.ldd;  // elements between image rows (< 2^31 checked by the host)
+#pragma unroll 1
+            for (int c0 = 0; c0 < 256; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(acc + (uint32_t)c0, v);
+                tmem_ld_wait();
+                if (c0 == 224) {
+                    tc_fence_before();
+                    mbar_arrive(smem_u32(&bar_acc_empty[ab]));
+                }
+                if (!co_ok) continue;
+                const int sub = c0 / NMMA, h4 = (c0 % NMMA) >> 3;
+                float* dst = tile_dst + (long long)h4 * line + sub * 8 * p.ldd;
+#pragma unroll
+                for (int hh = 0; hh < 4; hh++) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) dst[j * p.ldd] = __uint_as_float(v[hh * 8 + j]) + bv;
+                    dst += line;
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) { }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // Second stages and weight packing
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(float* __restrict__ D, long long ldd, const float* __restrict__ partial,
@@ -694,6 +1028,7 @@ static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const TcPara
     TcParams p = p_in;
     p.tiles_n = (int)tiles.x; p.tiles_m = (int)tiles.y; p.splits = (int)tiles.z;
     p.stages = Cfg::STAGES;
+    if (g_desc_variant > 0 && g_desc_variant < p.stages) p.stages = g_desc_variant;  // experiment: shallower ring
     const long long total = (long long)tiles.x * tiles.y * tiles.z;
     const int sms = ncc::sm_count();
     dim3 grid((unsigned)(total < sms ? total : sms), 1, 1);
@@ -705,7 +1040,7 @@ static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const TcPara
     }
     const bool prof = g_prof.on && g_prof.n < g_prof.cap;
     if (prof) cudaEventRecord(g_prof.start[g_prof.n], st);
-    kern<<<grid, 192, Cfg::SMEM_BYTES, st>>>(ta, tb, p);
+    kern<<<grid, ProdCfg<A_MN, B_MN, BN>::THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, p);
     if (prof) {
         cudaEventRecord(g_prof.stop[g_prof.n], st);
         g_prof.n++;
@@ -814,12 +1149,86 @@ static void pick_box(int pixels, int Wd, int Hd, int Nd, int* bw, int* bh, int* 
         }
 }
 
+// Halo-resident convolution (convh_kernel): whole 8 x 32 or 16 x 16 pixel tiles, filters up to 3 x 3, plain TF32 mode.
+static bool convh_ok(int N, int H, int W, int Cin, int Cout, int kH, int kW, int pad, int mode) {
+    const int Ho = H + 2 * pad - kH + 1, Wo = W + 2 * pad - kW + 1;
+    if (g_desc_variant == 9) return false;  // experiment switch: use the per-tap kernel
+    if (mode != NC_CUDA_MATH_TF32) return false;
+    if (kH < 1 || kW < 1 || kH > 3 || kW > 3) return false;
+    if (Ho <= 0 || Wo <= 0) return false;
+    if (!((Ho % 32 == 0 && Wo % 8 == 0) || (Ho % 16 == 0 && Wo % 16 == 0))) return false;
+    if ((Cin % 32) || (Cout % 4) || Cout < 16) return false;
+    if ((long long)N * Ho * Wo * Cout >= 0x7fffffffLL) return false;
+    return true;
+}
+
+template <int TW, int TH>
+static int conv_halo_launch(float* y, const float* x, const float* wpacked, const float* bias, int N, int H, int W, int Cin,
+                            int Cout, int kH, int kW, int pad, cudaStream_t st) {
+    const int Ho = H + 2 * pad - kH + 1, Wo = W + 2 * pad - kW + 1;
+    CUtensorMap tw, tx;
+    unsigned long long wd[2] = {(unsigned long long)Cin, (unsigned long long)kH * kW * Cout};
+    unsigned long long ws[1] = {(unsigned long long)Cin};
+    unsigned wb[2] = {32, 128};
+    if (!make_map(&tw, wpacked, 2, wd, ws, wb, false)) return NC_CUDA_ERR_UNSUPPORTED;
+    unsigned long long dims[4] = {(unsigned long long)Cin, (unsigned long long)W, (unsigned long long)H, (unsigned long long)N};
+    unsigned long long str[3] = {(unsigned long long)Cin, (unsigned long long)W * Cin, (unsigned long long)H * W * Cin};
+    unsigned box[4] = {32, (unsigned)(TW + kW - 1), (unsigned)(TH + kH - 1), 1};
+    if (!make_map(&tx, x, 4, dims, str, box, false)) return NC_CUDA_ERR_UNSUPPORTED;
+    ConvhParams p = {};
+    p.D = y; p.ldd = Cout; p.bias = bias; p.M = Cout;
+    p.Ho = Ho; p.Wo = Wo;
+    p.tiles_w = Wo / TW; p.tiles_h = Ho / TH;
+    p.tiles_px = N * p.tiles_w * p.tiles_h;
+    p.tiles_m = (Cout + BM - 1) / BM;
+    p.kH = kH; p.kW = kW; p.pad = pad;
+    p.cchunks = Cin / 32;
+    p.wrows = Cout;
+    p.pitch = TW + kW - 1;
+    p.halo_bytes = p.pitch * (TH + kH - 1) * 128;
+    p.halo_stride = (p.halo_bytes + 1023) & ~1023;
+    p.skip_loads = (g_desc_variant >= 11 && g_desc_variant <= 13) ? g_desc_variant - 10 : 0;
+    p.err = ncc::device_error_word();
+    const int smem = 2 * p.halo_stride + kConvhWStages * A_BYTES + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        NCC_TRY(cudaFuncSetAttribute(convh_kernel<TW, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     2 * 44 * 1024 + kConvhWStages * A_BYTES + 1024));
+        attr_set = true;
+    }
+    const long long total = (long long)p.tiles_px * p.tiles_m;
+    const int sms = ncc::sm_count();
+    g_prof.next_flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
+    const bool prof = g_prof.on && g_prof.n < g_prof.cap;
+    if (prof) cudaEventRecord(g_prof.start[g_prof.n], st);
+    convh_kernel<TW, TH><<<(unsigned)(total < sms ? total : sms), 192, smem, st>>>(tw, tx, p);
+    if (prof) {
+        cudaEventRecord(g_prof.stop[g_prof.n], st);
+        g_prof.n++;
+        g_prof.flops += g_prof.next_flops;
+    }
+    NCC_COUNT_LAUNCH();
+    return ncc::launch_status("convh_kernel");
+}
+
+static int conv_halo_nhwc(float* y, const float* x, const float* wpacked, const float* bias, int N, int H, int W, int Cin,
+                          int Cout, int kH, int kW, int pad, cudaStream_t st) {
+    const int Ho = H + 2 * pad - kH + 1, Wo = W + 2 * pad - kW + 1;
+    const bool tall = (Ho % 32 == 0 && Wo % 8 == 0), square = (Ho % 16 == 0 && Wo % 16 == 0);
+    if (tall && !(square && g_desc_variant == 8)) return conv_halo_launch<8, 32>(y, x, wpacked, bias, N, H, W, Cin, Cout, kH, kW, pad, st);
+    return conv_halo_launch<16, 16>(y, x, wpacked, bias, N, H, W, Cin, Cout, kH, kW, pad, st);
+}
+
 int conv_nhwc(float* y, const float* x, const float* wpacked, const float* bias, int N, int H, int W, int Cin, int Cout,
               int kH, int kW, int pad, int mode, cudaStream_t st) {
     const int Ho = H + 2 * pad - kH + 1, Wo = W + 2 * pad - kW + 1;
     if (Ho <= 0 || Wo <= 0) return NC_CUDA_ERR_UNSUPPORTED;
     if ((Cin & 3) || (Cout & 3) || Cin < 16 || Cout < 16) return NC_CUDA_ERR_UNSUPPORTED;
     if ((long long)N * Ho * Wo < 128) return NC_CUDA_ERR_UNSUPPORTED;
+    if (convh_ok(N, H, W, Cin, Cout, kH, kW, pad, mode)) {
+        const int rc = conv_halo_nhwc(y, x, wpacked, bias, N, H, W, Cin, Cout, kH, kW, pad, st);
+        if (rc != NC_CUDA_ERR_UNSUPPORTED) return rc;
+    }
     if ((long long)N * Ho * Wo >= 1024 && kH * kW * Cout >= 128) {
         // pixels on the N side (256 per tile), channels on the M side
         int bw = 1, bh = 1, bnn = 1;
