@@ -1,0 +1,6 @@
+/* Forwarding header: code written against the reference's include layout (nocta/nn/batchnorm.h)
+ * finds the same declarations in the single public header of this library. */
+#ifndef NOCTA_FWD_NN_BATCHNORM_H
+#define NOCTA_FWD_NN_BATCHNORM_H
+#include "../nocta.h"
+#endif

@@ -1,0 +1,6 @@
+/* Forwarding header: code written against the reference's include layout (nocta/ops/activation.h)
+ * finds the same declarations in the single public header of this library. */
+#ifndef NOCTA_FWD_OPS_ACTIVATION_H
+#define NOCTA_FWD_OPS_ACTIVATION_H
+#include "../nocta.h"
+#endif

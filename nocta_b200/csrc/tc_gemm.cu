@@ -1156,7 +1156,10 @@ static bool convh_ok(int N, int H, int W, int Cin, int Cout, int kH, int kW, int
     if (mode != NC_CUDA_MATH_TF32) return false;
     if (kH < 1 || kW < 1 || kH > 3 || kW > 3) return false;
     if (Ho <= 0 || Wo <= 0) return false;
-    if (!((Ho % 32 == 0 && Wo % 8 == 0) || (Ho % 16 == 0 && Wo % 16 == 0))) return false;
+    // 8 x 32 tiles (one N = 256 MMA per k-step) beat the per-tap kernel; 16 x 16 tiles (two N = 128 MMAs,
+    // which read the A tile twice) do not, so images that only fit those stay on the per-tap kernel
+    // unless the experiment switch asks for them
+    if (!((Ho % 32 == 0 && Wo % 8 == 0) || (g_desc_variant == 8 && Ho % 16 == 0 && Wo % 16 == 0))) return false;
     if ((Cin % 32) || (Cout % 4) || Cout < 16) return false;
     if ((long long)N * Ho * Wo * Cout >= 0x7fffffffLL) return false;
     return true;
