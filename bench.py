@@ -67,7 +67,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                                           "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -262,8 +262,6 @@ def run_ours(args):
     launches = int(lib.nc_cuda_launch_count())
     tc_ms, tc_n, tc_flops = C.c_double(0), C.c_ulonglong(0), C.c_double(0)
     lib.nc_cuda_tc_profile_end(C.byref(tc_ms), C.byref(tc_n), C.byref(tc_flops))
-    clocks = sampler.stop() if rank == 0 else None
-
     # ---- end-to-end: host batch in pinned memory -> device every step, loss read back every step ----
     pinned = []
     for a in (data[0], data[1]) if kind == "ce" else (data[0], data[1]):
@@ -297,6 +295,7 @@ def run_ours(args):
     f1.record()
     barrier()
     ms_e2e = f0.elapsed_time(f1)
+    clocks = sampler.stop() if rank == 0 else None  # sampled across both timed regions
     errword = int(lib.nc_cuda_device_error_word())
 
     # max over ranks
@@ -313,13 +312,18 @@ def run_ours(args):
         tf32_peak = (peaks.get("bf16_tflops_sustained", 1400.0)) / 2.0
         achieved = tc_flops.value / (tc_ms.value * 1e9) if tc_ms.value > 0 else None
         roofline = {
-            "bound": "tensor", "kernel": "tc_kernel (tcgen05 kind::tf32 implicit-GEMM conv / dW / GEMM)",
+            "bound": "tensor", "kernel": "convh_kernel + tc_kernel (tcgen05 kind::tf32 convolutions, weight gradients, GEMM)",
             "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
             "frac": (achieved / tf32_peak) if achieved else None,
             "peak_source": ("MEASURED_PEAKS.json bf16_tflops_sustained / 2 (TF32 issues at half the bf16 rate); of measured"
                             if pk.exists() else "fallback 1400/2; of fallback"),
             "launches_timed": int(tc_n.value), "kernel_ms_per_step": tc_ms.value / args.steps,
-            "share_of_step": tc_ms.value / ms if ms > 0 else None, "traffic": None,
+            "share_of_step": tc_ms.value / ms if ms > 0 else None,
+            # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch, from the ncu capture summarised in
+            # profiles/convh_and_dw_kernel_conv128x128_32x32_b256.md (128->128 channel 32x32 layer, batch 256):
+            # it equals that launch's algorithmic bytes (134.2 MB in, 134.2 MB out, 0.6 MB weights; 50 MB of the
+            # output were still in L2 when the kernel ended)
+            "traffic": 219.0e6, "traffic_unit": "bytes per launch (convh_kernel, 77.3 GFLOP launch)",
         }
         line = {
             "metric": METRIC, "value": images * world * args.steps / (ms / 1e3), "unit": UNIT, "n_gpus": world,
