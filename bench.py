@@ -271,29 +271,52 @@ def run_ours(args):
         pinned.append((p, a.shape, a.dtype))
     h2d = sum(int(np.prod(s)) * np.dtype(d).itemsize for _, s, d in pinned)
 
-    def e2e_step():
-        ts = []
-        for p, shape, dtype in pinned:
-            nc_dt = capi.NC_I64 if np.dtype(dtype) == np.int64 else capi.NC_F32
-            ts.append(api.nc_tensor_from_data(C.c_void_p(p), capi.shape_arr(shape), len(shape), nc_dt))
-        full = tuple(ts) if kind == "ce" else (ts[0], ts[1], tensors[2])
-        loss = step(full)
-        val = float(api.nc_tensor_get_flat(loss, 0))  # device -> host read of the step's result
-        net.free_step_tensors()
-        for t in ts:
-            api.nc_tensor_free(t)
-        return val
+    # The batch of step i+1 is uploaded by the library's double-buffered feeder (copy stream) while step i
+    # runs; every step still copies its own inputs host -> device inside the timed region.
+    TP = C.POINTER(capi.Tensor)
+    lib.nc_feeder_create.restype = C.c_void_p
+    lib.nc_feeder_create.argtypes = [C.c_int, C.POINTER(C.c_size_t), C.c_size_t, C.c_int, C.POINTER(C.c_size_t), C.c_size_t, C.c_int]
+    lib.nc_feeder_submit.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+    lib.nc_feeder_acquire.argtypes = [C.c_void_p, C.c_int, C.POINTER(TP), C.POINTER(TP)]
+    lib.nc_feeder_release.argtypes = [C.c_void_p, C.c_int]
+    lib.nc_feeder_free.argtypes = [C.c_void_p]
+    lib.nc_feeder_free.restype = None
 
-    for _ in range(2):
-        e2e_step()
+    def nc_dt(dtype):
+        return capi.NC_I64 if np.dtype(dtype) == np.int64 else capi.NC_F32
+
+    (px, xshape, xdt), (py, yshape, ydt) = pinned
+    feeder = lib.nc_feeder_create(2, capi.shape_arr(xshape), len(xshape), nc_dt(xdt), capi.shape_arr(yshape), len(yshape), nc_dt(ydt))
+    if not feeder:
+        raise RuntimeError("nc_feeder_create failed")
+
+    def e2e_run(n):
+        """n steps; returns the last loss.  Slot i%2 holds the batch of step i."""
+        last = 0.0
+        if lib.nc_feeder_submit(feeder, 0, px, py) != 0:
+            raise RuntimeError("nc_feeder_submit failed")
+        for i in range(n):
+            slot = i & 1
+            xt, yt = TP(), TP()
+            if lib.nc_feeder_acquire(feeder, slot, C.byref(xt), C.byref(yt)) != 0:
+                raise RuntimeError("nc_feeder_acquire failed")
+            if i + 1 < n and lib.nc_feeder_submit(feeder, slot ^ 1, px, py) != 0:  # next batch: overlaps this step
+                raise RuntimeError("nc_feeder_submit failed")
+            full = (xt, yt) if kind == "ce" else (xt, yt, tensors[2])
+            loss = step(full)
+            last = float(api.nc_tensor_get_flat(loss, 0))  # device -> host read of the step's result
+            net.free_step_tensors()
+            lib.nc_feeder_release(feeder, slot)
+        return last
+
+    e2e_run(2)
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
-    last = 0.0
-    for _ in range(args.steps):
-        last = e2e_step()
+    last = e2e_run(args.steps)
     f1.record()
     barrier()
+    lib.nc_feeder_free(feeder)
     ms_e2e = f0.elapsed_time(f1)
     clocks = sampler.stop() if rank == 0 else None  # sampled across both timed regions
     errword = int(lib.nc_cuda_device_error_word())

@@ -382,6 +382,24 @@ void nc_optimizer_set_grad_scale(nc_optimizer* opt, double scale);
  * returns its device address and length in floats, so data-parallel code can all-reduce one range */
 void* nc_optimizer_flatten_grads(nc_optimizer* opt, size_t* n_floats);
 
+/* ---------------- input feeder (new; the reference assembles a batch element by element and copies it
+ * synchronously, examples/mnist.c:93-111) ----------------
+ * Double-buffered upload of (input, target) batches from pinned host memory on a copy stream, so the
+ * copy of batch i+1 overlaps the training step on batch i.  Per slot: submit() starts the asynchronous
+ * copy (after the work that last used the slot has finished), acquire() makes the compute stream wait
+ * for it and hands out the slot's device tensors (owned by the feeder: do not free them), release()
+ * marks the point in the compute stream after which the slot may be overwritten.  The host buffers
+ * given to submit() must be pinned (nc_cuda_host_alloc) and stay unchanged until acquire() of that
+ * slot has been followed by nc_feeder_wait() or by any synchronisation of the compute stream. */
+typedef struct nc_feeder nc_feeder;
+nc_feeder* nc_feeder_create(int slots, const size_t* x_shape, size_t x_ndim, nc_dtype x_dtype,
+                            const size_t* y_shape, size_t y_ndim, nc_dtype y_dtype);
+int nc_feeder_submit(nc_feeder* f, int slot, const void* x_host, const void* y_host);
+int nc_feeder_acquire(nc_feeder* f, int slot, nc_tensor** x, nc_tensor** y);
+int nc_feeder_release(nc_feeder* f, int slot);
+int nc_feeder_wait(nc_feeder* f, int slot);  /* blocks the host until the slot's copy has finished */
+void nc_feeder_free(nc_feeder* f);
+
 typedef struct {
     double momentum;
     double dampening;

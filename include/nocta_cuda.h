@@ -68,6 +68,15 @@ int   nc_cuda_memset_async(void* ptr, int value, size_t size, void* stream);
 void* nc_cuda_host_alloc(size_t size);
 void  nc_cuda_host_free(void* ptr);
 int   nc_cuda_stream_synchronize(void* stream);
+/* new: a second stream and events, for copies that overlap the compute stream (input prefetch).
+ * The stream does not synchronise implicitly with the legacy default stream. */
+void* nc_cuda_stream_create(void);
+void  nc_cuda_stream_destroy(void* stream);
+void* nc_cuda_event_create(void);
+void  nc_cuda_event_destroy(void* event);
+int   nc_cuda_event_record(void* event, void* stream);
+int   nc_cuda_stream_wait_event(void* stream, void* event);
+int   nc_cuda_event_synchronize(void* event);
 int   nc_cuda_last_status(void);
 const char* nc_cuda_last_message(void);
 void  nc_cuda_clear_status(void);

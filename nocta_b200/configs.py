@@ -296,6 +296,28 @@ def train_step(r: Runner, net: Net, forward, loss_kind, tensors, after_backward=
     return loss
 
 
+def eval_accuracy(r: Runner, net: Net, forward, x: np.ndarray, labels: np.ndarray):
+    """The inference half of the reference's training loop (examples/mnist.c:359-381): every module in
+    eval mode (BatchNorm normalises with its running statistics, src/nn/batchnorm.c:315-319), one forward,
+    row argmax (src/ops/reduction.c:473-513), count of correct predictions.  Returns (logits, predictions,
+    correct); the modules are put back into training mode."""
+    api = r.api
+    for m in net.modules.values():
+        api.nc_module_train(m, False)
+    xt = r.tensor(x)
+    try:
+        out = forward(net, xt)
+        pred_t = _k(net.keep, api.nc_argmax(out, 1, False))
+        logits = api.to_numpy(out)
+        pred = api.to_numpy(pred_t).astype(np.int64).reshape(-1)
+    finally:
+        net.free_step_tensors()
+        api.nc_tensor_free(xt)
+        for m in net.modules.values():
+            api.nc_module_train(m, True)
+    return logits, pred, int((pred == labels.reshape(-1)).sum())
+
+
 def upload(r: Runner, loss_kind, data):
     if loss_kind == "ce":
         x, y = data

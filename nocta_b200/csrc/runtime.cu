@@ -199,6 +199,43 @@ int nc_cuda_stream_synchronize(void* stream) {
     NCC_TRY(cudaStreamSynchronize((cudaStream_t)stream));
     return NC_CUDA_OK;
 }
+void* nc_cuda_stream_create(void) {
+    cudaStream_t st = nullptr;
+    if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) != cudaSuccess) {
+        set_status(NC_CUDA_ERR_RUNTIME, "cudaStreamCreate failed");
+        return nullptr;
+    }
+    return st;
+}
+void nc_cuda_stream_destroy(void* stream) {
+    if (stream) cudaStreamDestroy((cudaStream_t)stream);
+}
+void* nc_cuda_event_create(void) {
+    cudaEvent_t ev = nullptr;
+    if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) {
+        set_status(NC_CUDA_ERR_RUNTIME, "cudaEventCreate failed");
+        return nullptr;
+    }
+    return ev;
+}
+void nc_cuda_event_destroy(void* event) {
+    if (event) cudaEventDestroy((cudaEvent_t)event);
+}
+int nc_cuda_event_record(void* event, void* stream) {
+    NCC_REQUIRE(event, "event_record: null event");
+    NCC_TRY(cudaEventRecord((cudaEvent_t)event, (cudaStream_t)stream));
+    return NC_CUDA_OK;
+}
+int nc_cuda_stream_wait_event(void* stream, void* event) {
+    NCC_REQUIRE(event, "stream_wait_event: null event");
+    NCC_TRY(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)event, 0));
+    return NC_CUDA_OK;
+}
+int nc_cuda_event_synchronize(void* event) {
+    NCC_REQUIRE(event, "event_synchronize: null event");
+    NCC_TRY(cudaEventSynchronize((cudaEvent_t)event));
+    return NC_CUDA_OK;
+}
 int nc_cuda_last_status(void) { return g_status; }
 const char* nc_cuda_last_message(void) { return g_message; }
 void nc_cuda_clear_status(void) {

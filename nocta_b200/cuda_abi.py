@@ -44,6 +44,13 @@ SIGNATURES = {
     "nc_cuda_host_alloc": (_p, [_z]),
     "nc_cuda_host_free": (None, [_p]),
     "nc_cuda_stream_synchronize": (_i, [_p]),
+    "nc_cuda_stream_create": (_p, []),
+    "nc_cuda_stream_destroy": (None, [_p]),
+    "nc_cuda_event_create": (_p, []),
+    "nc_cuda_event_destroy": (None, [_p]),
+    "nc_cuda_event_record": (_i, [_p, _p]),
+    "nc_cuda_stream_wait_event": (_i, [_p, _p]),
+    "nc_cuda_event_synchronize": (_i, [_p]),
     "nc_cuda_last_status": (_i, []),
     "nc_cuda_last_message": (C.c_char_p, []),
     "nc_cuda_clear_status": (None, []),

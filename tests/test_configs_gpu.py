@@ -118,3 +118,37 @@ def test_training_step_matches_reference(ours, theirs, name, kw, steps, mode):
     worst = compare(got, expected, tol, adam_slack=2 * ADAM_LR.get(name, 0.0) * steps, loss_tol=loss_tol)
     print(f"{name} mode {mode}: worst {worst}")
     assert ours.api.lib.nc_cuda_device_error_word() == 0
+
+
+@pytest.mark.parametrize("name,kw", [("lenet", dict()), ("convbn", dict(batch=16)), ("vgg", dict(batch=8, size=16, widths=(32, 64, 128), classes=10))])
+def test_eval_mode_predictions_match_reference(ours, theirs, name, kw):
+    """Two training steps, then the inference half of the loop on a held-out batch: eval-mode logits at
+    2e-5 (3xTF32 mode), predicted classes and the correct-prediction count bit-exact."""
+    from nocta_b200 import configs
+
+    def go(r):
+        net, forward, kind, data = configs.BUILDERS[name](r, **kw)
+        tensors = configs.upload(r, kind, data)
+        for _ in range(2):
+            configs.train_step(r, net, forward, kind, tensors)
+            net.free_step_tensors()
+        rng = np.random.default_rng(77)
+        x = rng.standard_normal(data[0].shape).astype(np.float32)
+        y = rng.integers(0, 10, data[0].shape[0]).astype(np.int64)
+        res = configs.eval_accuracy(r, net, forward, x, y)
+        configs.free_inputs(r, kind, tensors)
+        return res
+
+    exp_logits, exp_pred, exp_correct = go(theirs)
+    ours.api.lib.nc_cuda_set_math_mode(MODE_3X)
+    try:
+        logits, pred, correct = go(ours)
+    finally:
+        ours.api.lib.nc_cuda_set_math_mode(MODE_TF32)
+    emax, el2 = O.rel_errors(logits, exp_logits)
+    assert max(emax, el2) <= 2e-5, (emax, el2)
+    # a flipped argmax would need two logits closer than the tolerance; make that visible if it ever happens
+    top2 = np.sort(exp_logits, axis=1)[:, -2:]
+    assert float((top2[:, 1] - top2[:, 0]).min()) > 1e-4 * float(np.abs(exp_logits).max())
+    assert np.array_equal(pred, exp_pred)
+    assert correct == exp_correct
