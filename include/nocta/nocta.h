@@ -382,6 +382,48 @@ void nc_optimizer_set_grad_scale(nc_optimizer* opt, double scale);
  * returns its device address and length in floats, so data-parallel code can all-reduce one range */
 void* nc_optimizer_flatten_grads(nc_optimizer* opt, size_t* n_floats);
 
+/* ------------------------------------------------------------------ .ncta files (core/serialize.h)
+ * Same byte layout as the reference (see nocta_b200/host/serialize.c); tensors may live on the CUDA device. */
+#define NC_FILE_MAGIC 0x4154434E /* "NCTA" */
+#define NC_FILE_VERSION 1
+nc_error nc_tensor_save(const nc_tensor* t, const char* path);
+nc_tensor* nc_tensor_load(const char* path);
+nc_error nc_tensor_save_fp(const nc_tensor* t, FILE* fp, const char* name);
+nc_tensor* nc_tensor_load_fp(FILE* fp, char* name_out);
+typedef struct {
+    char** names;
+    nc_tensor** tensors;
+    size_t n_tensors;
+    size_t capacity;
+} nc_state_dict;
+nc_state_dict* nc_state_dict_create(void);
+void nc_state_dict_free(nc_state_dict* sd);
+void nc_state_dict_add(nc_state_dict* sd, const char* name, nc_tensor* t); /* takes ownership of t */
+nc_tensor* nc_state_dict_get(nc_state_dict* sd, const char* name);
+nc_error nc_state_dict_save(nc_state_dict* sd, const char* path);
+nc_state_dict* nc_state_dict_load(const char* path);
+nc_state_dict* nc_module_state_dict(nc_module* m);
+nc_error nc_module_load_state_dict(nc_module* m, nc_state_dict* sd);
+nc_error nc_module_save(nc_module* m, const char* path);
+nc_error nc_module_load(nc_module* m, const char* path);
+nc_error nc_module_save_desc(nc_module* m, const char* path, const char* description);
+typedef struct {
+    nc_state_dict* model_state;
+    nc_state_dict* optimizer_state;
+    size_t epoch;
+    double loss;
+} nc_checkpoint;
+nc_error nc_checkpoint_save(nc_checkpoint* ckpt, const char* path);
+nc_checkpoint* nc_checkpoint_load(const char* path);
+void nc_checkpoint_free(nc_checkpoint* ckpt);
+void nc_file_info(const char* path);
+bool nc_file_verify(const char* path);
+/* new: the optimizer's own state as named tensors ("step" = the step counter as one i64; per parameter
+ * index i "velocity.i" for SGD with momentum, "m.i" / "v.i" / "vmax.i" for Adam), for the optimizer_state
+ * slot of a checkpoint, and the inverse.  The reference leaves building that dict to the caller. */
+nc_state_dict* nc_optimizer_state_dict(nc_optimizer* opt);
+nc_error nc_optimizer_load_state_dict(nc_optimizer* opt, nc_state_dict* sd);
+
 /* ---------------- input feeder (new; the reference assembles a batch element by element and copies it
  * synchronously, examples/mnist.c:93-111) ----------------
  * Double-buffered upload of (input, target) batches from pinned host memory on a copy stream, so the

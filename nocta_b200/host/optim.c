@@ -178,3 +178,63 @@ nc_optimizer* nc_adamw(nc_module* m, double lr, double weight_decay) {
     c.weight_decay = weight_decay;
     return nc_adam_from_module(m, lr, c);
 }
+
+/* ------------------------------------------------------------------ optimizer state <-> named tensors */
+static void sd_add_clone(nc_state_dict* sd, const char* prefix, size_t i, const nc_tensor* t) {
+    if (!t) return;
+    char name[NC_MAX_NAME_LEN];
+    snprintf(name, sizeof(name), "%s.%zu", prefix, i);
+    nc_tensor* c = nc_tensor_clone(t);
+    if (c) nc_state_dict_add(sd, name, c);
+}
+nc_state_dict* nc_optimizer_state_dict(nc_optimizer* opt) {
+    if (!opt) return NULL;
+    nc_state_dict* sd = nc_state_dict_create();
+    if (!sd) return NULL;
+    const int64_t t = (int64_t)opt->t;
+    const size_t one = 1;
+    nc_device_type dev = nc_get_default_device();
+    nc_set_default_device(NC_DEVICE_CPU);  /* the counter is host bookkeeping */
+    nc_tensor* step = nc_tensor_from_data(&t, &one, 1, NC_I64);
+    nc_set_default_device(dev);
+    if (step) nc_state_dict_add(sd, "step", step);
+    if (opt->step == sgd_step) {
+        sgd_state* st = opt->state;
+        for (size_t i = 0; i < opt->n_params; i++) sd_add_clone(sd, "velocity", i, st->velocity[i]);
+    } else if (opt->step == adam_step) {
+        adam_state* st = opt->state;
+        for (size_t i = 0; i < opt->n_params; i++) {
+            sd_add_clone(sd, "m", i, st->m[i]);
+            sd_add_clone(sd, "v", i, st->v[i]);
+            sd_add_clone(sd, "vmax", i, st->vmax[i]);
+        }
+    }
+    return sd;
+}
+static nc_error restore_slot(nc_state_dict* sd, const char* prefix, size_t i, const nc_tensor* param, nc_tensor** slot) {
+    char name[NC_MAX_NAME_LEN];
+    snprintf(name, sizeof(name), "%s.%zu", prefix, i);
+    nc_tensor* src = nc_state_dict_get(sd, name);
+    if (!src) return NC_OK;
+    if (!nc_tensor_shape_eq(param, src)) { NC_SET_ERROR(NC_ERR_SHAPE_MISMATCH, "optimizer state %s does not fit parameter %zu", name, i); return NC_ERR_SHAPE_MISMATCH; }
+    if (!*slot) *slot = state_like(param);
+    if (!*slot) return NC_ERR_ALLOC;
+    return nc_tensor_copy_(*slot, src);
+}
+nc_error nc_optimizer_load_state_dict(nc_optimizer* opt, nc_state_dict* sd) {
+    if (!opt || !sd) return NC_ERR_NULL_PTR;
+    nc_tensor* step = nc_state_dict_get(sd, "step");
+    if (step && step->numel == 1) opt->t = (size_t)nc_tensor_get_flat(step, 0);
+    nc_error err = NC_OK;
+    for (size_t i = 0; i < opt->n_params && err == NC_OK; i++) {
+        if (opt->step == sgd_step) {
+            err = restore_slot(sd, "velocity", i, opt->params[i], &((sgd_state*)opt->state)->velocity[i]);
+        } else if (opt->step == adam_step) {
+            adam_state* st = opt->state;
+            err = restore_slot(sd, "m", i, opt->params[i], &st->m[i]);
+            if (err == NC_OK) err = restore_slot(sd, "v", i, opt->params[i], &st->v[i]);
+            if (err == NC_OK) err = restore_slot(sd, "vmax", i, opt->params[i], &st->vmax[i]);
+        }
+    }
+    return err;
+}
