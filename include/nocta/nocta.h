@@ -343,6 +343,10 @@ nc_tensor* nc_batchnorm2d_forward_fn(nc_tensor* input, nc_tensor* running_mean, 
 nc_tensor* nc_batchnorm2d_relu_forward_fn(nc_tensor* input, nc_tensor* running_mean, nc_tensor* running_var,
                                           nc_tensor* weight, nc_tensor* bias, bool training, double momentum, double eps);
 nc_tensor* nc_batchnorm2d_relu(nc_module* bn, nc_tensor* x);
+/* new: the same followed by a 2x2 / stride-2 max-pool, as one pass each way that never stores the
+ * full-resolution activation (channels-last CUDA input with C % 4 == 0 and even H, W; any other input is
+ * served by the two separate ops with the same result). */
+nc_tensor* nc_batchnorm2d_relu_maxpool2(nc_module* bn, nc_tensor* x);
 typedef struct {
     size_t* normalized_shape;
     size_t normalized_ndim;

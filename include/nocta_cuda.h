@@ -249,6 +249,21 @@ int nc_cuda_batchnorm_backward_f32_ex(float* grad_input, float* grad_gamma, floa
                                       const float* relu_beta, int relu_recompute,
                                       int N, int C, int spatial, double eps, int layout, void* stream);
 
+/* new: BatchNorm + ReLU + 2x2 stride-2 max-pool as one pass each way, channels-last only (x is (N, H, W, C) in
+ * memory, C % 4 == 0, H and W even).  Forward writes the pooled tensor (N, H/2, W/2, C) and one window offset
+ * (kh * 2 + kw, first maximum wins) per pooled element; the full-resolution activation is never stored.
+ * Backward takes the pooled gradient and those offsets and returns dx (N, H, W, C), dgamma, dbeta.
+ * Results equal nc_cuda_batchnorm_forward_f32_ex(relu = 1) followed by nc_cuda_maxpool2d_forward_idx_f32_ex. */
+int nc_cuda_batchnorm_relu_maxpool2_forward_f32_ex(float* pooled, uint8_t* argmax, const float* x, const float* gamma,
+                                                   const float* beta, float* running_mean, float* running_var,
+                                                   float* save_mean, float* save_var, int N, int C, int H, int W,
+                                                   double momentum, double eps, int training, void* stream);
+int nc_cuda_batchnorm_relu_maxpool2_backward_f32_ex(float* grad_input, float* grad_gamma, float* grad_beta,
+                                                    const float* grad_pooled, const uint8_t* argmax, const float* x,
+                                                    const float* gamma, const float* beta, const float* save_mean,
+                                                    const float* save_var, int N, int C, int H, int W, double eps,
+                                                    void* stream);
+
 /* ---------------- layer norm (new; CPU semantics src/nn/batchnorm.c:600-702,946-1026) ---------- */
 int nc_cuda_layernorm_forward_f32_ex(float* output, const float* input, const float* gamma, const float* beta,
                                      size_t rows, size_t cols, double eps, void* stream);

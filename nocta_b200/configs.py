@@ -63,6 +63,9 @@ class Runner:
             lib.nc_batchnorm2d_relu.restype = capi.TensorP
             lib.nc_batchnorm2d_relu.argtypes = [capi.ModuleP, capi.TensorP]
             self._bn_relu = lib.nc_batchnorm2d_relu
+            lib.nc_batchnorm2d_relu_maxpool2.restype = capi.TensorP
+            lib.nc_batchnorm2d_relu_maxpool2.argtypes = [capi.ModuleP, capi.TensorP]
+            self._bn_relu_pool = lib.nc_batchnorm2d_relu_maxpool2
         else:  # reference build: differentiable shims compiled next to it
             self.flatten = api.shim_flatten
             self.gelu = api.shim_gelu
@@ -86,6 +89,13 @@ class Runner:
             return _k(keep, self._bn_relu(module, x))
         h = _k(keep, self.api.nc_module_forward(module, x))
         return _k(keep, self.api.nc_relu(h))
+
+    def bn_relu_pool(self, keep, module, x):
+        """BatchNorm2d + ReLU + MaxPool(2, 2): one fused call where the library has it, else the reference calls."""
+        fused = getattr(self, "_bn_relu_pool", None)
+        if fused is not None:
+            return _k(keep, fused(module, x))
+        return _k(keep, self.api.nc_maxpool2d_forward(self.bn_relu(keep, module, x), 2, 2))
 
     def tensor(self, a: np.ndarray, requires_grad=False):
         # after nc_init the default device is CUDA, so from_data uploads
@@ -235,10 +245,9 @@ def build_vgg(r: Runner, seed=1239, batch=256, classes=100, rank=0, size=64, wid
         a, k, m = net.api, net.keep, net.modules
         h = xt
         for names in stages:
-            for c, b in names:
+            for i, (c, b) in enumerate(names):
                 h = _k(k, a.nc_module_forward(m[c], h))
-                h = r.bn_relu(k, m[b], h)
-            h = _k(k, a.nc_maxpool2d_forward(h, 2, 2))
+                h = r.bn_relu_pool(k, m[b], h) if i == len(names) - 1 else r.bn_relu(k, m[b], h)
         h = _k(k, r.flatten(h))
         return _k(k, a.nc_module_forward(m["fc"], h))
 

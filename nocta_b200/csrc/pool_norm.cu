@@ -576,6 +576,138 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_apply_nhwc4_kernel(float4* __
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// BatchNorm + ReLU + 2x2 / stride-2 max-pool in one pass each way (channels-last, C % 4 == 0, H and W even).
+// Forward reads x once and writes only the pooled tensor and the window offsets: the full-resolution
+// activation is never materialised (its backward needs x, the statistics and the offsets only).
+// Same arithmetic, same order, same tie rule (first maximum in (kh, kw) order wins) as bn_apply followed
+// by maxpool_fwd_kernel.  A thread keeps its four channels for the whole grid-stride walk.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) bn_relu_pool2_fwd_kernel(float4* __restrict__ pooled, uchar4* __restrict__ idx,
+                                                                     const float4* __restrict__ x, const float* __restrict__ gamma,
+                                                                     const float* __restrict__ beta, const float* __restrict__ mean,
+                                                                     const float* __restrict__ var, float eps, int C, int H, int W,
+                                                                     size_t nvec_out, int rnd) {
+    const unsigned tid = blockIdx.x * kThreads + threadIdx.x, total = gridDim.x * kThreads;
+    const int C4 = C >> 2, Ho = H >> 1, Wo = W >> 1;
+    const int c = (int)((tid * 4ull) % (unsigned)C);
+    float mu[4], is[4], g[4], b[4];
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+        mu[v] = mean[c + v];
+        is[v] = rsqrtf(var[c + v] + eps);
+        g[v] = gamma ? gamma[c + v] : 1.f;
+        b[v] = beta ? beta[c + v] : 0.f;
+    }
+    for (size_t i = tid; i < nvec_out; i += total) {
+        const unsigned pix = (unsigned)(i / (unsigned)C4);  // pooled pixel (n, ho, wo)
+        const unsigned wo = pix % (unsigned)Wo, t = pix / (unsigned)Wo, ho = t % (unsigned)Ho, n = t / (unsigned)Ho;
+        const size_t base = (((size_t)n * H + 2 * ho) * W + 2 * wo) * C4 + (c >> 2);
+        float best[4] = {-1e30f, -1e30f, -1e30f, -1e30f};
+        int bi[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int pos = 0; pos < 4; pos++) {
+            const float4 q = x[base + ((size_t)(pos >> 1) * W + (pos & 1)) * C4];
+            const float xv[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int v = 0; v < 4; v++) {
+                float o = g[v] * ((xv[v] - mu[v]) * is[v]) + b[v];
+                if (!(o > 0.f)) o = 0.f;
+                if (rnd) o = round_tf32(o);
+                if (o > best[v]) { best[v] = o; bi[v] = pos; }
+            }
+        }
+        pooled[i] = make_float4(best[0], best[1], best[2], best[3]);
+        if (idx) idx[i] = make_uchar4((uint8_t)bi[0], (uint8_t)bi[1], (uint8_t)bi[2], (uint8_t)bi[3]);
+    }
+}
+
+// Stage-1 functor of the fused backward: rows are POOLED pixels; the gradient lives only at each window's saved offset.
+struct BnPoolBwdSum {
+    const float* dp; const uint8_t* idx; const float* x; const float* gamma; const float* beta; const float* mean; const float* var;
+    float eps; int cols, H, W;
+    struct Ctx { float mu[4], is[4], g[4], b[4]; };
+    __device__ Ctx prepare(int c) const {
+        Ctx k;
+#pragma unroll
+        for (int v = 0; v < 4; v++) {
+            k.mu[v] = mean[c + v];
+            k.is[v] = rsqrtf(var[c + v] + eps);
+            k.g[v] = gamma ? gamma[c + v] : 1.f;
+            k.b[v] = beta ? beta[c + v] : 0.f;
+        }
+        return k;
+    }
+    __device__ void vec(const Ctx& k, size_t r, int c, float4& v1, float4& v2) const {
+        const unsigned Wo = (unsigned)(W >> 1), Ho = (unsigned)(H >> 1);
+        const unsigned pix = (unsigned)r, wo = pix % Wo, t = pix / Wo, ho = t % Ho, n = t / Ho;
+        const float4 gq = *reinterpret_cast<const float4*>(dp + r * cols + c);
+        const uchar4 iq = *reinterpret_cast<const uchar4*>(idx + r * cols + c);
+        const size_t base = (((size_t)n * H + 2 * ho) * W + 2 * wo) * cols + c;
+        const int pos[4] = {iq.x, iq.y, iq.z, iq.w};
+        float g[4] = {gq.x, gq.y, gq.z, gq.w}, gx[4];
+#pragma unroll
+        for (int v = 0; v < 4; v++) {
+            const float xv = x[base + ((size_t)(pos[v] >> 1) * W + (pos[v] & 1)) * cols + v];
+            const float xh = (xv - k.mu[v]) * k.is[v];
+            if (!((k.g[v] * xh + k.b[v]) > 0.f)) g[v] = 0.f;
+            gx[v] = g[v] * xh;
+        }
+        v1 = make_float4(g[0], g[1], g[2], g[3]);
+        v2 = make_float4(gx[0], gx[1], gx[2], gx[3]);
+    }
+    __device__ void operator()(size_t, int, float& v1, float& v2) const { v1 = 0.f; v2 = 0.f; }  // scalar path unused (C % 4 == 0 required)
+};
+
+// dx for all four positions of each window: the pooled gradient at the saved offset, zero elsewhere, both under
+// the recomputed ReLU mask, through dx = gamma * inv_std / M * (M * g - sum_g - xhat * sum_gx).
+__global__ void __launch_bounds__(kThreads) bn_relu_pool2_bwd_apply_kernel(float4* __restrict__ dx, const float4* __restrict__ dp,
+                                                                           const uchar4* __restrict__ idx, const float4* __restrict__ x,
+                                                                           const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                                           const float* __restrict__ mean, const float* __restrict__ var,
+                                                                           const float* __restrict__ sums, float eps, float Mf, int C, int H,
+                                                                           int W, size_t nvec_out, int rnd) {
+    const unsigned tid = blockIdx.x * kThreads + threadIdx.x, total = gridDim.x * kThreads;
+    const int C4 = C >> 2, Ho = H >> 1, Wo = W >> 1;
+    const int c = (int)((tid * 4ull) % (unsigned)C);
+    float mu[4], is[4], g[4], b[4], coeff[4], s1[4], s2[4];
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+        mu[v] = mean[c + v];
+        is[v] = rsqrtf(var[c + v] + eps);
+        g[v] = gamma ? gamma[c + v] : 1.f;
+        b[v] = beta ? beta[c + v] : 0.f;
+        coeff[v] = g[v] * is[v] / Mf;
+        s1[v] = sums[2 * (c + v)];
+        s2[v] = sums[2 * (c + v) + 1];
+    }
+    for (size_t i = tid; i < nvec_out; i += total) {
+        const unsigned pix = (unsigned)(i / (unsigned)C4);
+        const unsigned wo = pix % (unsigned)Wo, t = pix / (unsigned)Wo, ho = t % (unsigned)Ho, n = t / (unsigned)Ho;
+        const size_t base = (((size_t)n * H + 2 * ho) * W + 2 * wo) * C4 + (c >> 2);
+        const float4 gq = dp[i];
+        const uchar4 iq = idx[i];
+        const float gp[4] = {gq.x, gq.y, gq.z, gq.w};
+        const int sel[4] = {iq.x, iq.y, iq.z, iq.w};
+#pragma unroll
+        for (int pos = 0; pos < 4; pos++) {
+            const size_t at = base + ((size_t)(pos >> 1) * W + (pos & 1)) * C4;
+            const float4 q = x[at];
+            const float xv[4] = {q.x, q.y, q.z, q.w};
+            float o[4];
+#pragma unroll
+            for (int v = 0; v < 4; v++) {
+                const float xh = (xv[v] - mu[v]) * is[v];
+                float gv = sel[v] == pos ? gp[v] : 0.f;
+                if (!((g[v] * xh + b[v]) > 0.f)) gv = 0.f;
+                o[v] = coeff[v] * (Mf * gv - s1[v] - xh * s2[v]);
+                if (rnd) o[v] = round_tf32(o[v]);
+            }
+            dx[at] = make_float4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
 // Grid for the channels-last fast path: blocks * kThreads * 4 must be a multiple of C.
 inline int nhwc4_grid(size_t nvec, int C) {
     int a = C, b = kThreads * 4;
@@ -881,6 +1013,63 @@ int nc_cuda_batchnorm_backward_f32_ex(float* dx, float* dgamma, float* dbeta, co
     }
     NCC_COUNT_LAUNCH();
     return launch_status("batchnorm_backward");
+}
+
+int nc_cuda_batchnorm_relu_maxpool2_forward_f32_ex(float* pooled, uint8_t* argmax, const float* x, const float* gamma,
+                                                   const float* beta, float* run_mean, float* run_var, float* save_mean,
+                                                   float* save_var, int N, int C, int H, int W, double momentum, double eps,
+                                                   int training, void* stream) {
+    NCC_REQUIRE(pooled && x && save_mean && save_var && N > 0 && C > 0 && H > 0 && W > 0, "batchnorm_relu_maxpool2_forward: bad argument");
+    NCC_REQUIRE((C % 4 == 0) && (H % 2 == 0) && (W % 2 == 0), "batchnorm_relu_maxpool2_forward: needs C %% 4 == 0 and even H, W");
+    NCC_REQUIRE(al16(pooled) && al16(x) && ((uintptr_t)argmax % 4 == 0), "batchnorm_relu_maxpool2_forward: misaligned operand");
+    NCC_REQUIRE((size_t)N * (H / 2) * (W / 2) < 0xffffffffull, "batchnorm_relu_maxpool2_forward: too many pixels");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (training) {
+        double* partial = nullptr;
+        int slabs = 0;
+        int rc = channel_reduce(&partial, &slabs, N, C, H * W, 1, BnFwdSum{x, C}, BnFwdSumFlat{x}, true, st);
+        if (rc) return rc;
+        bn_fwd_finalize_kernel<<<ceil_div(C * 32, 128), 128, 0, st>>>(partial, slabs, C, (double)N * H * W, save_mean, save_var, run_mean,
+                                                                run_var, momentum);
+    } else {
+        bn_eval_stats_kernel<<<ceil_div(C, 128), 128, 0, st>>>(C, save_mean, save_var, run_mean, run_var);
+    }
+    NCC_COUNT_LAUNCH();
+    const size_t nvec = (size_t)N * (H / 2) * (W / 2) * (C / 4);
+    bn_relu_pool2_fwd_kernel<<<nhwc4_grid(nvec, C), kThreads, 0, st>>>((float4*)pooled, (uchar4*)argmax, (const float4*)x, gamma, beta,
+                                                                     save_mean, save_var, (float)eps, C, H, W, nvec,
+                                                                     round_outputs() ? 1 : 0);
+    NCC_COUNT_LAUNCH();
+    return launch_status("batchnorm_relu_maxpool2_forward");
+}
+
+int nc_cuda_batchnorm_relu_maxpool2_backward_f32_ex(float* dx, float* dgamma, float* dbeta, const float* dpooled,
+                                                    const uint8_t* argmax, const float* x, const float* gamma, const float* beta,
+                                                    const float* save_mean, const float* save_var, int N, int C, int H, int W,
+                                                    double eps, void* stream) {
+    NCC_REQUIRE(dx && dpooled && argmax && x && save_mean && save_var && N > 0 && C > 0 && H > 0 && W > 0,
+                "batchnorm_relu_maxpool2_backward: bad argument");
+    NCC_REQUIRE((C % 4 == 0) && (H % 2 == 0) && (W % 2 == 0), "batchnorm_relu_maxpool2_backward: needs C %% 4 == 0 and even H, W");
+    NCC_REQUIRE(al16(dx) && al16(dpooled) && al16(x) && ((uintptr_t)argmax % 4 == 0), "batchnorm_relu_maxpool2_backward: misaligned operand");
+    NCC_REQUIRE((size_t)N * (H / 2) * (W / 2) < 0xffffffffull, "batchnorm_relu_maxpool2_backward: too many pixels");
+    cudaStream_t st = (cudaStream_t)stream;
+    const float fe = (float)eps;
+    double* partial = nullptr;
+    int slabs = 0;
+    const size_t prow = (size_t)N * (H / 2) * (W / 2);
+    int rc = launch_colreduce(&partial, &slabs, prow, C, true, BnPoolBwdSum{dpooled, argmax, x, gamma, beta, save_mean, save_var, fe, C, H, W}, st);
+    if (rc) return rc;
+    float* sums = (float*)scratch(6, sizeof(float) * 2 * (size_t)C, st);
+    if (!sums) return NC_CUDA_ERR_RUNTIME;
+    bn_bwd_finalize_kernel<<<ceil_div(C * 32, 128), 128, 0, st>>>(partial, slabs, C, dgamma, dbeta, sums);
+    NCC_COUNT_LAUNCH();
+    const size_t nvec = prow * (C / 4);
+    bn_relu_pool2_bwd_apply_kernel<<<nhwc4_grid(nvec, C), kThreads, 0, st>>>((float4*)dx, (const float4*)dpooled, (const uchar4*)argmax,
+                                                                           (const float4*)x, gamma, beta, save_mean, save_var, sums, fe,
+                                                                           (float)((double)N * H * W), C, H, W, nvec,
+                                                                           round_outputs() ? 1 : 0);
+    NCC_COUNT_LAUNCH();
+    return launch_status("batchnorm_relu_maxpool2_backward");
 }
 
 void nc_cuda_batchnorm_forward_f32(float* y, const float* x, const float* gamma, const float* beta, float* rm, float* rv,

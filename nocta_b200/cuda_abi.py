@@ -120,6 +120,8 @@ SIGNATURES = {
     "nc_cuda_batchnorm_backward_f32": (None, [_p] * 8 + [_i, _i, _i, _f]),
     "nc_cuda_batchnorm_forward_f32_ex": (_i, [_p] * 8 + [_i, _i, _i, _d, _d, _i, _i, _i, _p]),
     "nc_cuda_batchnorm_backward_f32_ex": (_i, [_p] * 10 + [_i, _i, _i, _i, _d, _i, _p]),
+    "nc_cuda_batchnorm_relu_maxpool2_forward_f32_ex": (_i, [_p] * 9 + [_i] * 4 + [_d, _d, _i, _p]),
+    "nc_cuda_batchnorm_relu_maxpool2_backward_f32_ex": (_i, [_p] * 10 + [_i] * 4 + [_d, _p]),
     "nc_cuda_layernorm_forward_f32_ex": (_i, [_p, _p, _p, _p, _z, _z, _d, _p]),
     "nc_cuda_layernorm_backward_f32_ex": (_i, [_p, _p, _p, _p, _p, _p, _z, _z, _d, _p]),
     # losses

@@ -519,6 +519,100 @@ nc_tensor* nc_batchnorm2d_relu(nc_module* bn, nc_tensor* x) {
     return bn_forward(x, nc_module_get_param(bn, "running_mean"), nc_module_get_param(bn, "running_var"), nc_module_get_param(bn, "weight"),
                       nc_module_get_param(bn, "bias"), bn->training, c->momentum, c->eps, 1);
 }
+/* ---- BatchNorm2d + ReLU + MaxPool(2, 2) as one forward pass and one backward pass ----
+ * saved: [x, gamma, batch_mean, batch_var, host scalar (eps), beta, window offsets] */
+static nc_tensor** bwd_bn_relu_pool(nc_tensor* g, nc_tensor** saved, size_t n) {
+    (void)n;
+    nc_tensor** out = grad_array(3);
+    if (!out) return NULL;
+    nc_tensor* x = saved[0];
+    nc_tensor* gamma = saved[1];
+    nc_tensor* mean = saved[2];
+    nc_tensor* var = saved[3];
+    const double eps = nc_tensor_get_flat(saved[4], 0);
+    nc_tensor* beta = saved[5];
+    nc_tensor* idx = saved[6];
+    /* gradient in the layout of the pooled output (= layout of idx) */
+    nc_tensor* like = nci_alias(idx);
+    if (!like) return out;
+    like->dtype = NC_F32;
+    nc_tensor* gd = nci_match_layout(g, like);
+    nc_tensor_free(like);
+    if (!gd) return out;
+    const int N = (int)x->shape[0], C = (int)x->shape[1], H = (int)x->shape[2], W = (int)x->shape[3];
+    size_t cs = (size_t)C;
+    nci_round_outputs(true);
+    out[0] = nci_empty_like(x);
+    if (gamma) { out[1] = nci_empty_on(&cs, 1, NC_F32, NC_DEVICE_CUDA); out[2] = nci_empty_on(&cs, 1, NC_F32, NC_DEVICE_CUDA); }
+    if (out[0] && (!gamma || (out[1] && out[2])))
+        nci_ok(nc_cuda_batchnorm_relu_maxpool2_backward_f32_ex(nci_fptr(out[0]), gamma ? nci_fptr(out[1]) : NULL, gamma ? nci_fptr(out[2]) : NULL,
+                                                               nci_fptr(gd), (const uint8_t*)nci_dptr(idx), nci_fptr(x), gamma ? nci_fptr(gamma) : NULL,
+                                                               beta ? nci_fptr(beta) : NULL, nci_fptr(mean), nci_fptr(var), N, C, H, W, eps,
+                                                               nci_stream()), "batchnorm+relu+maxpool backward");
+    if (gd != g) nc_tensor_free(gd);
+    return out;
+}
+nc_tensor* nc_batchnorm2d_relu_maxpool2(nc_module* bn, nc_tensor* input) {
+    if (!bn || !bn->extra) { NC_SET_ERROR(NC_ERR_NULL_PTR, "batchnorm2d_relu_maxpool2: not a BatchNorm2D module"); return NULL; }
+    if (!input || input->ndim != 4) { NC_SET_ERROR(NC_ERR_SHAPE_MISMATCH, "BatchNorm2D requires 4D input (N,C,H,W)"); return NULL; }
+    const size_t N = input->shape[0], C = input->shape[1], H = input->shape[2], W = input->shape[3];
+    const bool fusable = nci_on_cuda(input) && input->dtype == NC_F32 && nci_is_channels_last(input) && nci_is_dense(input) &&
+                         (C % 4 == 0) && (H % 2 == 0) && (W % 2 == 0) && H >= 2 && W >= 2;
+    if (!fusable) { /* same result from the two separate ops */
+        nc_tensor* y = nc_batchnorm2d_relu(bn, input);
+        nc_tensor* p = y ? nc_maxpool2d_forward(y, 2, 2) : NULL;
+        /* y is invisible to the caller: the pool node takes ownership when there is a graph, else it goes now */
+        if (y && p && p->grad_fn) nc_node_save_owned_tensor(p->grad_fn, y);
+        else if (y) nc_tensor_free(y);
+        return p;
+    }
+    bn_cfg* c = bn->extra;
+    if (bn->training) c->batches++;
+    nc_tensor* weight = nc_module_get_param(bn, "weight");
+    nc_tensor* bias = nc_module_get_param(bn, "bias");
+    nc_tensor* rm = nc_module_get_param(bn, "running_mean");
+    nc_tensor* rv = nc_module_get_param(bn, "running_var");
+    size_t cs = C, oshape[4] = {N, C, H / 2, W / 2};
+    nci_round_outputs(true);
+    nc_tensor* y = nci_empty_cl(N, C, H / 2, W / 2);
+    nc_tensor* mean = nci_empty_on(&cs, 1, NC_F32, NC_DEVICE_CUDA);
+    nc_tensor* var = nci_empty_on(&cs, 1, NC_F32, NC_DEVICE_CUDA);
+    const bool need = nc_grad_enabled() && any_grad(input, weight, bias);
+    nc_tensor* idx = NULL;
+    if (y && need) {
+        idx = nci_empty_on(oshape, 4, NC_U8, NC_DEVICE_CUDA);
+        if (idx) { memcpy(idx->strides, y->strides, sizeof(idx->strides)); idx->is_contiguous = y->is_contiguous; }
+    }
+    bool ok = y && mean && var && (!need || idx) &&
+              nci_ok(nc_cuda_batchnorm_relu_maxpool2_forward_f32_ex(nci_fptr(y), idx ? (uint8_t*)nci_dptr(idx) : NULL, nci_fptr(input),
+                                                                    weight ? nci_fptr(weight) : NULL, bias ? nci_fptr(bias) : NULL,
+                                                                    rm ? nci_fptr(rm) : NULL, rv ? nci_fptr(rv) : NULL, nci_fptr(mean), nci_fptr(var),
+                                                                    (int)N, (int)C, (int)H, (int)W, c->momentum, c->eps, bn->training ? 1 : 0,
+                                                                    nci_stream()), "batchnorm+relu+maxpool");
+    bool wired = false;
+    if (ok && need) {
+        nc_node* nd = nci_attach(y, "batchnorm2d_relu_maxpool2", bwd_bn_relu_pool);
+        if (nd) {
+            nc_node_add_input(nd, input);
+            if (weight) nc_node_add_input(nd, weight);
+            if (bias) nc_node_add_input(nd, bias);
+            nc_node_save_tensor(nd, input);
+            nc_node_save_tensor(nd, weight);
+            nc_node_save_owned_tensor(nd, mean);
+            nc_node_save_owned_tensor(nd, var);
+            size_t one = 1;
+            nc_tensor* hp = nci_empty_on(&one, 1, NC_F64, NC_DEVICE_CPU);
+            if (hp) nc_tensor_set_flat(hp, 0, c->eps);
+            nc_node_save_owned_tensor(nd, hp);
+            nc_node_save_tensor(nd, bias);
+            nc_node_save_owned_tensor(nd, idx);
+            wired = true;
+        }
+    }
+    if (!wired) { nc_tensor_free(mean); nc_tensor_free(var); nc_tensor_free(idx); }
+    if (!ok) { nc_tensor_free(y); return NULL; }
+    return y;
+}
 static nc_tensor* bn_module_forward(nc_module* self, nc_tensor* x) {
     bn_cfg* c = self->extra;
     if (self->training) c->batches++;

@@ -449,3 +449,43 @@ def test_bad_arguments_are_errors(abi):
     assert abi.nc_cuda_set_math_mode(99) in (0, 1, 2, 3)
     assert abi.nc_cuda_last_status() != 0
     abi.nc_cuda_clear_status()
+
+
+@pytest.mark.parametrize("shape", [(3, 8, 6, 10), (2, 64, 16, 16), (5, 36, 2, 2)])
+@pytest.mark.parametrize("rounding", [0, 1])
+def test_fused_batchnorm_relu_maxpool_equals_the_separate_kernels(abi, shape, rounding):
+    """nc_cuda_batchnorm_relu_maxpool2_*: pooled values and window offsets bit-equal to BatchNorm(+ReLU)
+    followed by max-pool; gradients equal up to summation order (2e-6)."""
+    N, Cc, H, W = shape
+    rng = np.random.default_rng(N * 100 + Cc)
+    x = dev((rng.standard_normal((N, H, W, Cc)) * 2 + 0.5).astype(np.float32))   # channels-last memory
+    gamma, beta = dev(rng.standard_normal(Cc).astype(np.float32)), dev(rng.standard_normal(Cc).astype(np.float32))
+    dp = dev(rng.standard_normal((N, H // 2, W // 2, Cc)).astype(np.float32))
+    f32 = lambda *s: torch.empty(*s, device="cuda")
+    u8 = lambda *s: torch.empty(*s, dtype=torch.uint8, device="cuda")
+    prev = abi.nc_cuda_set_round_outputs(rounding)
+    try:
+        # separate kernels
+        y, m0, v0 = f32(N, H, W, Cc), f32(Cc), f32(Cc)
+        ok(abi, abi.nc_cuda_batchnorm_forward_f32_ex(P(y), P(x), P(gamma), P(beta), None, None, P(m0), P(v0), N, Cc, H * W, 0.1, 1e-5, 1, 1, 1, None))
+        p0, i0 = f32(N, H // 2, W // 2, Cc), u8(N, H // 2, W // 2, Cc)
+        ok(abi, abi.nc_cuda_maxpool2d_forward_idx_f32_ex(P(p0), P(i0), P(y), N, Cc, H, W, 2, 2, 1, None))
+        dy, dx0, dg0, db0 = f32(N, H, W, Cc), f32(N, H, W, Cc), f32(Cc), f32(Cc)
+        ok(abi, abi.nc_cuda_maxpool2d_backward_idx_f32_ex(P(dy), P(dp), P(i0), N, Cc, H, W, 2, 2, 1, None))
+        ok(abi, abi.nc_cuda_batchnorm_backward_f32_ex(P(dx0), P(dg0), P(db0), P(dy), P(x), P(gamma), P(m0), P(v0), None, P(beta), 1, N, Cc, H * W, 1e-5, 1, None))
+        # fused
+        p1, i1, m1, v1 = f32(N, H // 2, W // 2, Cc), u8(N, H // 2, W // 2, Cc), f32(Cc), f32(Cc)
+        ok(abi, abi.nc_cuda_batchnorm_relu_maxpool2_forward_f32_ex(P(p1), P(i1), P(x), P(gamma), P(beta), None, None, P(m1), P(v1), N, Cc, H, W, 0.1, 1e-5, 1, None))
+        dx1, dg1, db1 = f32(N, H, W, Cc), f32(Cc), f32(Cc)
+        ok(abi, abi.nc_cuda_batchnorm_relu_maxpool2_backward_f32_ex(P(dx1), P(dg1), P(db1), P(dp), P(i1), P(x), P(gamma), P(beta), P(m1), P(v1), N, Cc, H, W, 1e-5, None))
+    finally:
+        abi.nc_cuda_set_round_outputs(prev)
+    assert torch.equal(m0, m1) and torch.equal(v0, v1)
+    assert torch.equal(p0, p1)
+    assert torch.equal(i0, i1)
+    close(host(dx1), host(dx0), 2e-6)
+    close(host(dg1), host(dg0), 2e-6)
+    close(host(db1), host(db0), 2e-6)
+    # rejected shapes
+    assert abi.nc_cuda_batchnorm_relu_maxpool2_forward_f32_ex(P(p1), P(i1), P(x), P(gamma), P(beta), None, None, P(m1), P(v1), N, Cc, H + 1, W, 0.1, 1e-5, 1, None) != 0
+    abi.nc_cuda_clear_status()
