@@ -88,6 +88,12 @@ int   nc_cuda_get_math_mode(void);
  * they store to the nearest TF32 number, which removes the truncation bias of a tensor-core contraction
  * that reads it next.  Off by default (plain f32 results).  Returns the previous setting. */
 int   nc_cuda_set_round_outputs(int on);
+/* new: while on, nc_cuda_conv2d_forward_f32_ex (channels-last output, tensor-core or first-layer kernels)
+ * also sums its output per channel, and a training-mode BatchNorm forward that is the library's very next
+ * kernel-launching call on exactly that output takes those sums instead of reading the tensor again.  Any other
+ * launch of the library in between cancels the offer; switching off afterwards does not.  Off by default.
+ * Returns the previous setting. */
+int   nc_cuda_set_conv_stats(int on);
 /* new: reads and clears the device-side error word set when a bounded in-kernel wait expires */
 unsigned int nc_cuda_device_error_word(void);
 /* new: number of kernels this library has launched since the last reset (bookkeeping for benches) */

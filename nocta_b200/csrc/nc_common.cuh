@@ -30,6 +30,14 @@ cudaStream_t current_stream();
 // `slot` separates users whose lifetimes overlap inside one entry point.
 void* scratch(int slot, size_t bytes, cudaStream_t st);
 
+// Per-channel output statistics offered by a forward convolution to the BatchNorm that follows (runtime.cu).
+// partial[slab][C][2] doubles: (sum, sum of squares) of the slab's pixels.
+int set_conv_stats(int on);
+bool conv_stats_wanted();
+double* conv_stats_buffer(size_t slabs, int C, cudaStream_t st);
+void conv_stats_publish(const float* y, int C, long long rows, int slabs, double* partial);
+bool conv_stats_take(const float* x, int C, long long rows, double** partial, int* slabs);
+
 // Device-resident error word the tensor-core kernels set when a bounded wait expires.
 unsigned int* device_error_word();
 

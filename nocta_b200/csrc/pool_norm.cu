@@ -946,8 +946,11 @@ int nc_cuda_batchnorm_forward_f32_ex(float* y, const float* x, const float* gamm
     if (training) {
         double* partial = nullptr;
         int slabs = 0;
-        int rc = channel_reduce(&partial, &slabs, N, C, spatial, layout, BnFwdSum{x, C}, BnFwdSumFlat{x}, al16(x), st);
-        if (rc) return rc;
+        // the convolution that produced x may have left its per-channel sums behind (see nc_cuda_set_conv_stats)
+        if (!(layout == 1 && conv_stats_take(x, C, (long long)N * spatial, &partial, &slabs))) {
+            int rc = channel_reduce(&partial, &slabs, N, C, spatial, layout, BnFwdSum{x, C}, BnFwdSumFlat{x}, al16(x), st);
+            if (rc) return rc;
+        }
         bn_fwd_finalize_kernel<<<ceil_div(C * 32, 128), 128, 0, st>>>(partial, slabs, C, (double)N * spatial, save_mean,
                                                                 save_var, run_mean, run_var, momentum);
     } else {
@@ -1027,8 +1030,10 @@ int nc_cuda_batchnorm_relu_maxpool2_forward_f32_ex(float* pooled, uint8_t* argma
     if (training) {
         double* partial = nullptr;
         int slabs = 0;
-        int rc = channel_reduce(&partial, &slabs, N, C, H * W, 1, BnFwdSum{x, C}, BnFwdSumFlat{x}, true, st);
-        if (rc) return rc;
+        if (!conv_stats_take(x, C, (long long)N * H * W, &partial, &slabs)) {
+            int rc = channel_reduce(&partial, &slabs, N, C, H * W, 1, BnFwdSum{x, C}, BnFwdSumFlat{x}, true, st);
+            if (rc) return rc;
+        }
         bn_fwd_finalize_kernel<<<ceil_div(C * 32, 128), 128, 0, st>>>(partial, slabs, C, (double)N * H * W, save_mean, save_var, run_mean,
                                                                 run_var, momentum);
     } else {

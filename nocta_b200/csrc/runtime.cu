@@ -14,7 +14,7 @@ static int g_sm_count = 0;
 static int g_math_mode = NC_CUDA_MATH_TF32;
 unsigned long long g_launches = 0;
 
-static const int kScratchSlots = 8;
+static const int kScratchSlots = 9;
 static void* g_scratch[kScratchSlots] = {nullptr};
 static size_t g_scratch_bytes[kScratchSlots] = {0};
 static unsigned int* g_err_word = nullptr;
@@ -65,6 +65,30 @@ void* scratch(int slot, size_t bytes, cudaStream_t st) {
     g_scratch[slot] = p;
     g_scratch_bytes[slot] = want;
     return p;
+}
+
+// ---- per-channel statistics captured by a forward convolution for the BatchNorm that follows ----
+// A convolution kernel whose epilogue threads own whole output channels can sum its output (and its
+// square) per channel on the way out.  While the switch is on, the forward convolution entry point
+// publishes such partial sums together with the output pointer; a training-mode BatchNorm forward that
+// is the very next kernel-launching call of the library, on exactly that tensor, takes them instead of
+// reading the tensor again.  Any other library launch in between (which could have changed the tensor)
+// invalidates the offer.
+static int g_conv_stats_on = 0;
+static struct { const float* y; int C; long long rows; int slabs; double* partial; unsigned long long stamp; bool valid; } g_offer = {};
+int set_conv_stats(int on) { int p = g_conv_stats_on; g_conv_stats_on = on ? 1 : 0; return p; }  // an offer already made stays
+bool conv_stats_wanted() { return g_conv_stats_on != 0; }
+double* conv_stats_buffer(size_t slabs, int C, cudaStream_t st) { return (double*)scratch(8, sizeof(double) * 2 * slabs * (size_t)C, st); }
+void conv_stats_publish(const float* y, int C, long long rows, int slabs, double* partial) {
+    g_offer.y = y; g_offer.C = C; g_offer.rows = rows; g_offer.slabs = slabs; g_offer.partial = partial;
+    g_offer.stamp = g_launches;
+    g_offer.valid = true;
+}
+bool conv_stats_take(const float* x, int C, long long rows, double** partial, int* slabs) {
+    const bool hit = g_offer.valid && g_offer.y == x && g_offer.C == C && g_offer.rows == rows && g_offer.stamp == g_launches;
+    g_offer.valid = false;
+    if (hit) { *partial = g_offer.partial; *slabs = g_offer.slabs; }
+    return hit;
 }
 
 unsigned int* device_error_word() {
@@ -250,6 +274,7 @@ int nc_cuda_set_math_mode(int mode) {
 }
 int nc_cuda_get_math_mode(void) { return g_math_mode; }
 int nc_cuda_set_round_outputs(int on) { return ncc::set_round_outputs(on); }
+int nc_cuda_set_conv_stats(int on) { return set_conv_stats(on); }
 unsigned int nc_cuda_device_error_word(void) {
     unsigned int* w = device_error_word();
     unsigned int h = 0;

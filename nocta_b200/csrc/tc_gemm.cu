@@ -51,6 +51,7 @@ struct TcParams {
     int lbw, lbh;                  // CONVT: log2 of the pixel box width / height
     int tiles_m, tiles_n, splits;  // persistent tile walk
     int stages;                    // operand ring depth
+    double* stat;                  // CONVT, non-null: per pixel tile and channel (sum, sum of squares) of the output
     unsigned int* err;
 };
 
@@ -539,8 +540,10 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                 const float bv = (co_ok && p.bias) ? p.bias[co] : 0.f;
                 const int tw = n_tile % p.tiles_w, tt = n_tile / p.tiles_w;
                 const int pw0 = tw * p.bw, ph0 = (tt % p.tiles_h) * p.bh, pn0 = (tt / p.tiles_h) * p.bn;
+                double ssum = 0.0, ssq = 0.0;  // this channel's output statistics over the pixels of the tile that exist
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 32) {
+                    float fs = 0.f, fq = 0.f;
                     uint32_t v[32];
                     tmem_ld32(acc_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
                     tmem_ld_wait();
@@ -570,7 +573,11 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                             const int lim = p.Wo - w;  // columns j < lim are inside the image
 #pragma unroll
                             for (int j = 0; j < 32; j++)
-                                if (j < lim) dst[j * ldd] = __uint_as_float(v[j]) + bv;
+                                if (j < lim) {
+                                    const float o = __uint_as_float(v[j]) + bv;
+                                    dst[j * ldd] = o;
+                                    if (p.stat) { fs += o; fq = fmaf(o, o, fq); }
+                                }
                         }
                     } else {
 #pragma unroll
@@ -584,10 +591,21 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                                 const int lim = p.Wo - w;
 #pragma unroll
                                 for (int j = 0; j < 8; j++)
-                                    if (j < lim) dst[j * ldd] = __uint_as_float(v[j0 + j]) + bv;
+                                    if (j < lim) {
+                                        const float o = __uint_as_float(v[j0 + j]) + bv;
+                                        dst[j * ldd] = o;
+                                        if (p.stat) { fs += o; fq = fmaf(o, o, fq); }
+                                    }
                             }
                         }
                     }
+                    ssum += (double)fs;
+                    ssq += (double)fq;
+                }
+                if (p.stat && co_ok) {
+                    double* sd = p.stat + ((size_t)n_tile * p.M + co) * 2;
+                    sd[0] = ssum;
+                    sd[1] = ssq;
                 }
                 continue;
             }
@@ -714,6 +732,7 @@ struct ConvhParams {
     int wrows;             // rows per tap in the packed weights
     int pitch;             // halo line pitch in pixels
     int halo_bytes, halo_stride;
+    double* stat;          // non-null: per pixel tile and channel (sum, sum of squares) of the output, [tile][M][2]
     int skip_loads;        // experiment: 1 = no weight copies, 2 = no halo copies, 3 = neither (timing only)
     unsigned int* err;
 };
@@ -875,6 +894,7 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
             // first pixel of the tile; a column chunk of 32 = 4 lines x 8 pixels of one 8-column sub-tile
             float* tile_dst = p.D + (((long long)n * p.Ho + th * TH) * p.Wo + tw * TW) * p.ldd + co;
             const int line = p.Wo * p.ldd;  // elements between image rows (< 2^31 checked by the host)
+            double ssum = 0.0, ssq = 0.0;   // this channel's output statistics over the tile (32 values in f32, then double)
 #pragma unroll 1
             for (int c0 = 0; c0 < 256; c0 += 32) {
                 uint32_t v[32];
@@ -893,6 +913,22 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                     for (int j = 0; j < 8; j++) dst[j * p.ldd] = __uint_as_float(v[hh * 8 + j]) + bv;
                     dst += line;
                 }
+                if (p.stat) {  // uniform over the CTA
+                    float fs = 0.f, fq = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const float o = __uint_as_float(v[j]) + bv;
+                        fs += o;
+                        fq = fmaf(o, o, fq);
+                    }
+                    ssum += (double)fs;
+                    ssq += (double)fq;
+                }
+            }
+            if (p.stat && co_ok) {
+                double* sd = p.stat + ((size_t)pt * p.M + co) * 2;
+                sd[0] = ssum;
+                sd[1] = ssq;
             }
         }
     }
@@ -1192,6 +1228,7 @@ static int conv_halo_launch(float* y, const float* x, const float* wpacked, cons
     p.halo_stride = (p.halo_bytes + 1023) & ~1023;
     p.skip_loads = (g_desc_variant >= 11 && g_desc_variant <= 13) ? g_desc_variant - 10 : 0;
     p.err = ncc::device_error_word();
+    if (ncc::conv_stats_wanted()) p.stat = ncc::conv_stats_buffer((size_t)p.tiles_px, Cout, st);
     const int smem = 2 * p.halo_stride + kConvhWStages * A_BYTES + 1024;
     static bool attr_set = false;
     if (!attr_set) {
@@ -1211,6 +1248,7 @@ static int conv_halo_launch(float* y, const float* x, const float* wpacked, cons
         g_prof.flops += g_prof.next_flops;
     }
     NCC_COUNT_LAUNCH();
+    if (p.stat) ncc::conv_stats_publish(y, Cout, (long long)N * Ho * Wo, p.tiles_px, p.stat);
     return ncc::launch_status("convh_kernel");
 }
 
@@ -1263,7 +1301,10 @@ int conv_nhwc(float* y, const float* x, const float* wpacked, const float* bias,
         p.N = (int)(tiles_px * 256 < 0x7fffffffLL ? tiles_px * 256 : 0x7fffffff);
         dim3 tiles((unsigned)tiles_px, (unsigned)((Cout + BM - 1) / BM), 1);
         g_prof.next_flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
-        return launch_mode<256, false, false>(mode, ta, tb, p, tiles, st);
+        if (ncc::conv_stats_wanted() && tiles_px < 0x7fffffffLL) p.stat = ncc::conv_stats_buffer((size_t)tiles_px, Cout, st);
+        const int rc = launch_mode<256, false, false>(mode, ta, tb, p, tiles, st);
+        if (rc == NC_CUDA_OK && p.stat) ncc::conv_stats_publish(y, Cout, (long long)N * Ho * Wo, (int)tiles_px, p.stat);
+        return rc;
     }
     const int bn_cols = pick_bn(Cout, mode);
     int bw = 1, bh = 1, bnn = 1;

@@ -57,6 +57,7 @@ SIGNATURES = {
     "nc_cuda_set_math_mode": (_i, [_i]),
     "nc_cuda_get_math_mode": (_i, []),
     "nc_cuda_set_round_outputs": (_i, [_i]),
+    "nc_cuda_set_conv_stats": (_i, [_i]),
     "nc_cuda_device_error_word": (C.c_uint, []),
     "nc_cuda_launch_count": (C.c_ulonglong, []),
     "nc_cuda_reset_launch_count": (None, []),

@@ -267,9 +267,13 @@ nc_tensor* nc_conv2d_forward(nc_tensor* input, nc_tensor* weight, nc_tensor* bia
     nc_tensor* y = nci_empty_cl(N, Cout, Ho, Wo);
     size_t xs[4], ys[4];
     if (y) { nci_strides4(x, xs); nci_strides4(y, ys); }
-    if (y && !nci_ok(nc_cuda_conv2d_forward_f32_ex(nci_fptr(y), ys, nci_fptr(x), xs, nci_fptr(weight), bias ? nci_fptr(bias) : NULL, (int)N,
-                                                   (int)Cin, (int)H, (int)Wd, (int)Cout, (int)kH, (int)kW, (int)stride, (int)padding,
-                                                   nci_stream()), "conv2d")) {
+    /* in a training graph the kernel also leaves per-channel sums of y for a BatchNorm called right after it */
+    const int prev_stats = nc_cuda_set_conv_stats(nc_grad_enabled() ? 1 : 0);
+    const bool conv_ok = y && nci_ok(nc_cuda_conv2d_forward_f32_ex(nci_fptr(y), ys, nci_fptr(x), xs, nci_fptr(weight), bias ? nci_fptr(bias) : NULL, (int)N,
+                                                                   (int)Cin, (int)H, (int)Wd, (int)Cout, (int)kH, (int)kW, (int)stride, (int)padding,
+                                                                   nci_stream()), "conv2d");
+    nc_cuda_set_conv_stats(prev_stats); /* an offer already made stays valid until the next launch */
+    if (y && !conv_ok) {
         nc_tensor_free(y);
         y = NULL;
     }

@@ -489,3 +489,57 @@ def test_fused_batchnorm_relu_maxpool_equals_the_separate_kernels(abi, shape, ro
     # rejected shapes
     assert abi.nc_cuda_batchnorm_relu_maxpool2_forward_f32_ex(P(p1), P(i1), P(x), P(gamma), P(beta), None, None, P(m1), P(v1), N, Cc, H + 1, W, 0.1, 1e-5, 1, None) != 0
     abi.nc_cuda_clear_status()
+
+
+@pytest.mark.parametrize("shape", [(8, 64, 32, 64), (4, 128, 16, 256), (6, 32, 32, 48)])
+def test_batchnorm_takes_statistics_offered_by_the_convolution(abi, shape):
+    """With nc_cuda_set_conv_stats(1) the forward convolution leaves per-channel sums behind and the BatchNorm
+    called right after it uses them: same result (2e-6) as BatchNorm reading the tensor; the offer is void after
+    any other launch or for any other tensor."""
+    from nocta_b200 import cuda_abi
+    N, Cin, H, Cout = shape
+    rng = np.random.default_rng(Cin + Cout)
+    x = dev(rng.standard_normal((N, H, H, Cin)).astype(np.float32))
+    w = dev((rng.standard_normal((Cout, Cin, 3, 3)) / (3 * Cin ** 0.5)).astype(np.float32))
+    b = dev(rng.standard_normal(Cout).astype(np.float32))
+    gamma, beta = dev(rng.standard_normal(Cout).astype(np.float32)), dev(rng.standard_normal(Cout).astype(np.float32))
+    xs = cuda_abi.size4([H * H * Cin, 1, H * Cin, Cin])
+    ys = cuda_abi.size4([H * H * Cout, 1, H * Cout, Cout])
+    y = torch.empty(N, H, H, Cout, device="cuda")
+
+    def bn(inp):
+        out, m, v = torch.empty_like(inp), torch.empty(Cout, device="cuda"), torch.empty(Cout, device="cuda")
+        ok(abi, abi.nc_cuda_batchnorm_forward_f32_ex(P(out), P(inp), P(gamma), P(beta), None, None, P(m), P(v), N, Cout, H * H, 0.1, 1e-5, 1, 1, 1, None))
+        return out, m, v
+
+    conv = lambda: ok(abi, abi.nc_cuda_conv2d_forward_f32_ex(P(y), ys, P(x), xs, P(w), P(b), N, Cin, H, H, Cout, 3, 3, 1, 1, None))
+    conv()
+    ref_out, ref_m, ref_v = bn(y)                       # switch off: BatchNorm reads y
+    launches_plain = abi.nc_cuda_launch_count()
+    prev = abi.nc_cuda_set_conv_stats(1)
+    try:
+        abi.nc_cuda_reset_launch_count()
+        conv()
+        base = abi.nc_cuda_launch_count()
+        out, m, v = bn(y)                               # takes the offer: finalize + apply only
+        assert abi.nc_cuda_launch_count() - base == 2
+        close(host(m), host(ref_m), 2e-6)
+        close(host(v), host(ref_v), 2e-6)
+        close(host(out), host(ref_out), 2e-6)
+        # the offer is used once
+        base = abi.nc_cuda_launch_count()
+        bn(y)
+        assert abi.nc_cuda_launch_count() - base == 3
+        # another launch in between voids it (the tensor could have changed: here it does)
+        conv()
+        ok(abi, abi.nc_cuda_scalar_f32_ex(2, P(y), P(y), 2.0, y.numel(), None))   # y *= 2 in place (op 2 = mul)
+        out2, m2, v2 = bn(y)
+        close(host(m2), 2 * host(ref_m), 2e-6)
+        # and it is tied to the tensor
+        conv()
+        other = y.clone()
+        base = abi.nc_cuda_launch_count()
+        bn(other)
+        assert abi.nc_cuda_launch_count() - base == 3
+    finally:
+        abi.nc_cuda_set_conv_stats(prev)
