@@ -434,22 +434,43 @@ int launch_colreduce(double** partial_out, int* slabs_out, size_t rows, int cols
 }
 inline bool al16(const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Stage 2 for BatchNorm forward: combine slabs in order, derive mean / biased variance, update the
-// running statistics (unbiased variance, src/nn/batchnorm.c:307-314).
-__global__ void bn_fwd_finalize_kernel(const double* __restrict__ partial, int slabs, int C, double M,
+// Stage 2: a block of 256 threads combines the slabs of 8 neighbouring columns; thread (tx, ty) adds slabs
+// ty, ty + 32, ... of column c0 + tx (a slab row of 8 columns is one 128-byte request), then thread (tx, 0)
+// adds the 32 lane sums in index order: the result does not depend on the launch geometry of stage 1.
+constexpr int kFinCols = 8, kFinLanes = 32;
+__device__ __forceinline__ bool combine_slabs(const double* __restrict__ partial, int slabs, int C, int* c_out, double* s1, double* s2) {
+    __shared__ double sh1[kFinLanes][kFinCols], sh2[kFinLanes][kFinCols];
+    const int tx = threadIdx.x & (kFinCols - 1), ty = threadIdx.x / kFinCols;
+    const int c = blockIdx.x * kFinCols + tx;
+    double a = 0.0, b = 0.0;
+    if (c < C) {
+#pragma unroll 4
+        for (int s = ty; s < slabs; s += kFinLanes) {
+            const double2 v = *reinterpret_cast<const double2*>(partial + ((size_t)s * C + c) * 2);
+            a += v.x;
+            b += v.y;
+        }
+    }
+    sh1[ty][tx] = a;
+    sh2[ty][tx] = b;
+    __syncthreads();
+    if (ty != 0 || c >= C) return false;
+    a = 0.0; b = 0.0;
+#pragma unroll
+    for (int k = 0; k < kFinLanes; k++) { a += sh1[k][tx]; b += sh2[k][tx]; }
+    *c_out = c; *s1 = a; *s2 = b;
+    return true;
+}
+inline int fin_grid(int C) { return (C + kFinCols - 1) / kFinCols; }
+
+// Stage 2 for BatchNorm forward: mean / biased variance, running statistics (unbiased variance,
+// src/nn/batchnorm.c:307-314).
+__global__ void __launch_bounds__(kFinCols * kFinLanes) bn_fwd_finalize_kernel(const double* __restrict__ partial, int slabs, int C, double M,
                                        float* __restrict__ save_mean, float* __restrict__ save_var,
                                        float* __restrict__ run_mean, float* __restrict__ run_var, double momentum) {
-    // one warp per channel: lanes stride over the slabs, then a fixed-order shuffle tree
-    const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (c >= C) return;
-    double s1 = 0.0, s2 = 0.0;
-    for (int s = lane; s < slabs; s += 32) {
-        s1 += partial[((size_t)s * C + c) * 2];
-        s2 += partial[((size_t)s * C + c) * 2 + 1];
-    }
-    s1 = warp_sum(s1);
-    s2 = warp_sum(s2);
-    if (lane != 0) return;
+    int c;
+    double s1, s2;
+    if (!combine_slabs(partial, slabs, C, &c, &s1, &s2)) return;
     double mean = s1 / M;
     double var_sum = s2 - s1 * mean;  // sum (x - mean)^2
     if (var_sum < 0.0) var_sum = 0.0;
@@ -719,18 +740,11 @@ inline int nhwc4_grid(size_t nvec, int C) {
     return (int)g;
 }
 
-__global__ void bn_bwd_finalize_kernel(const double* __restrict__ partial, int slabs, int C,
+__global__ void __launch_bounds__(kFinCols * kFinLanes) bn_bwd_finalize_kernel(const double* __restrict__ partial, int slabs, int C,
                                        float* __restrict__ dgamma, float* __restrict__ dbeta, float* __restrict__ sums) {
-    const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (c >= C) return;
-    double s1 = 0.0, s2 = 0.0;
-    for (int s = lane; s < slabs; s += 32) {
-        s1 += partial[((size_t)s * C + c) * 2];
-        s2 += partial[((size_t)s * C + c) * 2 + 1];
-    }
-    s1 = warp_sum(s1);
-    s2 = warp_sum(s2);
-    if (lane != 0) return;
+    int c;
+    double s1, s2;
+    if (!combine_slabs(partial, slabs, C, &c, &s1, &s2)) return;
     if (dbeta) dbeta[c] = (float)s1;
     if (dgamma) dgamma[c] = (float)s2;
     sums[2 * c] = (float)s1;
@@ -859,18 +873,11 @@ __global__ void __launch_bounds__(kThreads) ln_bwd_rows_kernel(float* __restrict
     }
 }
 
-__global__ void ln_param_finalize_kernel(const double* __restrict__ partial, int slabs, int cols,
+__global__ void __launch_bounds__(kFinCols * kFinLanes) ln_param_finalize_kernel(const double* __restrict__ partial, int slabs, int cols,
                                          float* __restrict__ dgamma, float* __restrict__ dbeta) {
-    const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (c >= cols) return;
-    double s1 = 0.0, s2 = 0.0;
-    for (int s = lane; s < slabs; s += 32) {
-        s1 += partial[((size_t)s * cols + c) * 2];
-        s2 += partial[((size_t)s * cols + c) * 2 + 1];
-    }
-    s1 = warp_sum(s1);
-    s2 = warp_sum(s2);
-    if (lane != 0) return;
+    int c;
+    double s1, s2;
+    if (!combine_slabs(partial, slabs, cols, &c, &s1, &s2)) return;
     if (dgamma) dgamma[c] = (float)s1;
     if (dbeta) dbeta[c] = (float)s2;
 }
@@ -896,7 +903,7 @@ int ncc::column_sums(float* out, const float* in, size_t rows, int cols, cudaStr
     int slabs = 0;
     int rc = launch_colreduce(&partial, &slabs, rows, cols, al16(in), ColSum{in, cols}, st);
     if (rc) return rc;
-    ln_param_finalize_kernel<<<ceil_div(cols * 32, 128), 128, 0, st>>>(partial, slabs, cols, out, nullptr);
+    ln_param_finalize_kernel<<<fin_grid(cols), kFinCols * kFinLanes, 0, st>>>(partial, slabs, cols, out, nullptr);
     NCC_COUNT_LAUNCH();
     return launch_status("column_sums");
 }
@@ -951,7 +958,7 @@ int nc_cuda_batchnorm_forward_f32_ex(float* y, const float* x, const float* gamm
             int rc = channel_reduce(&partial, &slabs, N, C, spatial, layout, BnFwdSum{x, C}, BnFwdSumFlat{x}, al16(x), st);
             if (rc) return rc;
         }
-        bn_fwd_finalize_kernel<<<ceil_div(C * 32, 128), 128, 0, st>>>(partial, slabs, C, (double)N * spatial, save_mean,
+        bn_fwd_finalize_kernel<<<fin_grid(C), kFinCols * kFinLanes, 0, st>>>(partial, slabs, C, (double)N * spatial, save_mean,
                                                                 save_var, run_mean, run_var, momentum);
     } else {
         bn_eval_stats_kernel<<<ceil_div(C, 128), 128, 0, st>>>(C, save_mean, save_var, run_mean, run_var);
@@ -994,7 +1001,7 @@ int nc_cuda_batchnorm_backward_f32_ex(float* dx, float* dgamma, float* dbeta, co
     if (rc) return rc;
     float* sums = (float*)scratch(6, sizeof(float) * 2 * (size_t)C, st);
     if (!sums) return NC_CUDA_ERR_RUNTIME;
-    bn_bwd_finalize_kernel<<<ceil_div(C * 32, 128), 128, 0, st>>>(partial, slabs, C, dgamma, dbeta, sums);
+    bn_bwd_finalize_kernel<<<fin_grid(C), kFinCols * kFinLanes, 0, st>>>(partial, slabs, C, dgamma, dbeta, sums);
     NCC_COUNT_LAUNCH();
     const bool al = ((uintptr_t)dx % 16 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)dy % 16 == 0) &&
                     (!relu_out || (uintptr_t)relu_out % 16 == 0);
@@ -1034,7 +1041,7 @@ int nc_cuda_batchnorm_relu_maxpool2_forward_f32_ex(float* pooled, uint8_t* argma
             int rc = channel_reduce(&partial, &slabs, N, C, H * W, 1, BnFwdSum{x, C}, BnFwdSumFlat{x}, true, st);
             if (rc) return rc;
         }
-        bn_fwd_finalize_kernel<<<ceil_div(C * 32, 128), 128, 0, st>>>(partial, slabs, C, (double)N * H * W, save_mean, save_var, run_mean,
+        bn_fwd_finalize_kernel<<<fin_grid(C), kFinCols * kFinLanes, 0, st>>>(partial, slabs, C, (double)N * H * W, save_mean, save_var, run_mean,
                                                                 run_var, momentum);
     } else {
         bn_eval_stats_kernel<<<ceil_div(C, 128), 128, 0, st>>>(C, save_mean, save_var, run_mean, run_var);
@@ -1066,7 +1073,7 @@ int nc_cuda_batchnorm_relu_maxpool2_backward_f32_ex(float* dx, float* dgamma, fl
     if (rc) return rc;
     float* sums = (float*)scratch(6, sizeof(float) * 2 * (size_t)C, st);
     if (!sums) return NC_CUDA_ERR_RUNTIME;
-    bn_bwd_finalize_kernel<<<ceil_div(C * 32, 128), 128, 0, st>>>(partial, slabs, C, dgamma, dbeta, sums);
+    bn_bwd_finalize_kernel<<<fin_grid(C), kFinCols * kFinLanes, 0, st>>>(partial, slabs, C, dgamma, dbeta, sums);
     NCC_COUNT_LAUNCH();
     const size_t nvec = prow * (C / 4);
     bn_relu_pool2_bwd_apply_kernel<<<nhwc4_grid(nvec, C), kThreads, 0, st>>>((float4*)dx, (const float4*)dpooled, (const uchar4*)argmax,
@@ -1118,7 +1125,7 @@ int nc_cuda_layernorm_backward_f32_ex(float* dx, float* dgamma, float* dbeta, co
         int slabs = 0;
         int rc = launch_colreduce(&partial, &slabs, rows, C, al16(dy) && al16(x), LnParamSum{dy, x, stats, C}, st);
         if (rc) return rc;
-        ln_param_finalize_kernel<<<ceil_div(C * 32, 128), 128, 0, st>>>(partial, slabs, C, dgamma, dbeta);
+        ln_param_finalize_kernel<<<fin_grid(C), kFinCols * kFinLanes, 0, st>>>(partial, slabs, C, dgamma, dbeta);
         NCC_COUNT_LAUNCH();
     }
     return launch_status("layernorm_backward");

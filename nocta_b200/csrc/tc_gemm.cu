@@ -51,7 +51,7 @@ struct TcParams {
     int lbw, lbh;                  // CONVT: log2 of the pixel box width / height
     int tiles_m, tiles_n, splits;  // persistent tile walk
     int stages;                    // operand ring depth
-    double* stat;                  // CONVT, non-null: per pixel tile and channel (sum, sum of squares) of the output
+    double* stat;                  // CONVT, non-null: per CTA and channel (sum, sum of squares) of the output it wrote, [gridDim.x][M][2]
     unsigned int* err;
 };
 
@@ -499,6 +499,15 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         int s = 0;
         uint32_t ph = 0, tile_iter = 0;
         bool ok = true;
+        // CONVT output statistics: one running pair per channel tile, written once per CTA (see convh_kernel)
+        double ssum = 0.0, ssq = 0.0;
+        int stat_m0 = -1;
+        if (p.kind == KIND_CONVT && p.stat)
+            for (int mt = 0; mt < p.tiles_m; mt++)
+                if (mt * BM + r < p.M) {
+                    double* sd = p.stat + ((size_t)blockIdx.x * p.M + mt * BM + r) * 2;
+                    sd[0] = 0.0; sd[1] = 0.0;
+                }
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, tile_iter++) {
             const int n_tile = t % p.tiles_n, r_ = t / p.tiles_n, m_tile = r_ % p.tiles_m, z = r_ / p.tiles_m;
             const int kt_begin = z * p.k_tiles_per_split;
@@ -506,6 +515,13 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
             if (kt_end > p.num_k_tiles) kt_end = p.num_k_tiles;
             const int nk = kt_end - kt_begin;
             const int m0 = m_tile * BM, n0 = n_tile * BN;
+            if (p.kind == KIND_CONVT && p.stat && m0 != stat_m0) {
+                if (stat_m0 >= 0 && stat_m0 + r < p.M) {
+                    double* sd = p.stat + ((size_t)blockIdx.x * p.M + stat_m0 + r) * 2;
+                    sd[0] = ssum; sd[1] = ssq;
+                }
+                ssum = 0.0; ssq = 0.0; stat_m0 = m0;
+            }
             if (MODE != 0) {
                 constexpr int NV = Cfg::OPER_BYTES / 16;
                 for (int i = 0; i < nk && ok; i++) {
@@ -540,10 +556,9 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                 const float bv = (co_ok && p.bias) ? p.bias[co] : 0.f;
                 const int tw = n_tile % p.tiles_w, tt = n_tile / p.tiles_w;
                 const int pw0 = tw * p.bw, ph0 = (tt % p.tiles_h) * p.bh, pn0 = (tt / p.tiles_h) * p.bn;
-                double ssum = 0.0, ssq = 0.0;  // this channel's output statistics over the pixels of the tile that exist
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 32) {
-                    float fs = 0.f, fq = 0.f;
+                    float fs = 0.f, fq = 0.f;  // output statistics over the pixels of this chunk that exist
                     uint32_t v[32];
                     tmem_ld32(acc_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
                     tmem_ld_wait();
@@ -601,11 +616,6 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                     }
                     ssum += (double)fs;
                     ssq += (double)fq;
-                }
-                if (p.stat && co_ok) {
-                    double* sd = p.stat + ((size_t)n_tile * p.M + co) * 2;
-                    sd[0] = ssum;
-                    sd[1] = ssq;
                 }
                 continue;
             }
@@ -687,6 +697,10 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                 }
             }
         }
+        if (p.kind == KIND_CONVT && p.stat && stat_m0 >= 0 && stat_m0 + r < p.M) {
+            double* sd = p.stat + ((size_t)blockIdx.x * p.M + stat_m0 + r) * 2;
+            sd[0] = ssum; sd[1] = ssq;
+        }
     }
 
     // ------------------------------ teardown ------------------------------
@@ -732,7 +746,7 @@ struct ConvhParams {
     int wrows;             // rows per tap in the packed weights
     int pitch;             // halo line pitch in pixels
     int halo_bytes, halo_stride;
-    double* stat;          // non-null: per pixel tile and channel (sum, sum of squares) of the output, [tile][M][2]
+    double* stat;          // non-null: per CTA and channel (sum, sum of squares) of the output it wrote, [gridDim.x][M][2]
     int skip_loads;        // experiment: 1 = no weight copies, 2 = no halo copies, 3 = neither (timing only)
     unsigned int* err;
 };
@@ -878,8 +892,26 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
         const int r = q * 32 + lane;
         uint32_t tile_iter = 0;
         bool ok = true;
+        // Output statistics: a thread owns channel m0 + r of every tile it sees, so it keeps one running pair per
+        // channel tile and writes it once (slab = this CTA): stat[blockIdx.x][M][2].  Slots of channel tiles this
+        // CTA never visits must read zero, so the thread clears all of its slots first.
+        double ssum = 0.0, ssq = 0.0;
+        int stat_m0 = -1;
+        if (p.stat)
+            for (int mt = 0; mt < p.tiles_m; mt++)
+                if (mt * BM + r < p.M) {
+                    double* sd = p.stat + ((size_t)blockIdx.x * p.M + mt * BM + r) * 2;
+                    sd[0] = 0.0; sd[1] = 0.0;
+                }
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, tile_iter++) {
             const int pt = t % p.tiles_px, m0 = (t / p.tiles_px) * BM;
+            if (p.stat && m0 != stat_m0) {
+                if (stat_m0 >= 0 && stat_m0 + r < p.M) {
+                    double* sd = p.stat + ((size_t)blockIdx.x * p.M + stat_m0 + r) * 2;
+                    sd[0] = ssum; sd[1] = ssq;
+                }
+                ssum = 0.0; ssq = 0.0; stat_m0 = m0;
+            }
             const int tw = pt % p.tiles_w, tt = pt / p.tiles_w;
             const int th = tt % p.tiles_h, n = tt / p.tiles_h;
             const uint32_t ab = tile_iter & 1u;
@@ -894,7 +926,6 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
             // first pixel of the tile; a column chunk of 32 = 4 lines x 8 pixels of one 8-column sub-tile
             float* tile_dst = p.D + (((long long)n * p.Ho + th * TH) * p.Wo + tw * TW) * p.ldd + co;
             const int line = p.Wo * p.ldd;  // elements between image rows (< 2^31 checked by the host)
-            double ssum = 0.0, ssq = 0.0;   // this channel's output statistics over the tile (32 values in f32, then double)
 #pragma unroll 1
             for (int c0 = 0; c0 < 256; c0 += 32) {
                 uint32_t v[32];
@@ -925,11 +956,10 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                     ssq += (double)fq;
                 }
             }
-            if (p.stat && co_ok) {
-                double* sd = p.stat + ((size_t)pt * p.M + co) * 2;
-                sd[0] = ssum;
-                sd[1] = ssq;
-            }
+        }
+        if (p.stat && stat_m0 >= 0 && stat_m0 + r < p.M) {
+            double* sd = p.stat + ((size_t)blockIdx.x * p.M + stat_m0 + r) * 2;
+            sd[0] = ssum; sd[1] = ssq;
         }
     }
 
@@ -1228,7 +1258,10 @@ static int conv_halo_launch(float* y, const float* x, const float* wpacked, cons
     p.halo_stride = (p.halo_bytes + 1023) & ~1023;
     p.skip_loads = (g_desc_variant >= 11 && g_desc_variant <= 13) ? g_desc_variant - 10 : 0;
     p.err = ncc::device_error_word();
-    if (ncc::conv_stats_wanted()) p.stat = ncc::conv_stats_buffer((size_t)p.tiles_px, Cout, st);
+    const long long total = (long long)p.tiles_px * p.tiles_m;
+    const int sms = ncc::sm_count();
+    const unsigned grid = (unsigned)(total < sms ? total : sms);
+    if (ncc::conv_stats_wanted()) p.stat = ncc::conv_stats_buffer(grid, Cout, st);
     const int smem = 2 * p.halo_stride + kConvhWStages * A_BYTES + 1024;
     static bool attr_set = false;
     if (!attr_set) {
@@ -1236,19 +1269,17 @@ static int conv_halo_launch(float* y, const float* x, const float* wpacked, cons
                                      2 * 44 * 1024 + kConvhWStages * A_BYTES + 1024));
         attr_set = true;
     }
-    const long long total = (long long)p.tiles_px * p.tiles_m;
-    const int sms = ncc::sm_count();
     g_prof.next_flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
     const bool prof = g_prof.on && g_prof.n < g_prof.cap;
     if (prof) cudaEventRecord(g_prof.start[g_prof.n], st);
-    convh_kernel<TW, TH><<<(unsigned)(total < sms ? total : sms), 192, smem, st>>>(tw, tx, p);
+    convh_kernel<TW, TH><<<grid, 192, smem, st>>>(tw, tx, p);
     if (prof) {
         cudaEventRecord(g_prof.stop[g_prof.n], st);
         g_prof.n++;
         g_prof.flops += g_prof.next_flops;
     }
     NCC_COUNT_LAUNCH();
-    if (p.stat) ncc::conv_stats_publish(y, Cout, (long long)N * Ho * Wo, p.tiles_px, p.stat);
+    if (p.stat) ncc::conv_stats_publish(y, Cout, (long long)N * Ho * Wo, (int)grid, p.stat);
     return ncc::launch_status("convh_kernel");
 }
 
@@ -1301,9 +1332,12 @@ int conv_nhwc(float* y, const float* x, const float* wpacked, const float* bias,
         p.N = (int)(tiles_px * 256 < 0x7fffffffLL ? tiles_px * 256 : 0x7fffffff);
         dim3 tiles((unsigned)tiles_px, (unsigned)((Cout + BM - 1) / BM), 1);
         g_prof.next_flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
-        if (ncc::conv_stats_wanted() && tiles_px < 0x7fffffffLL) p.stat = ncc::conv_stats_buffer((size_t)tiles_px, Cout, st);
+        // launch_one uses min(tiles, SMs) persistent CTAs: one statistics slab per CTA
+        const long long total_tiles = (long long)tiles.x * tiles.y;
+        const int n_ctas = (int)(total_tiles < ncc::sm_count() ? total_tiles : ncc::sm_count());
+        if (ncc::conv_stats_wanted()) p.stat = ncc::conv_stats_buffer((size_t)n_ctas, Cout, st);
         const int rc = launch_mode<256, false, false>(mode, ta, tb, p, tiles, st);
-        if (rc == NC_CUDA_OK && p.stat) ncc::conv_stats_publish(y, Cout, (long long)N * Ho * Wo, (int)tiles_px, p.stat);
+        if (rc == NC_CUDA_OK && p.stat) ncc::conv_stats_publish(y, Cout, (long long)N * Ho * Wo, n_ctas, p.stat);
         return rc;
     }
     const int bn_cols = pick_bn(Cout, mode);
