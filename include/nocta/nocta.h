@@ -17,6 +17,10 @@
  *     channels-last; their shape is still (N,C,H,W) and their strides say so.
  *   - nc_flatten, nc_tensor_reshape-of-an-activation (through nc_flatten) and nc_gelu take part
  *     in autograd (the reference registers no node for them).
+ *   - nc_tensor_zero_grad_ / nc_optimizer_zero_grad DROP a gradient that a backward pass wrote (t->grad
+ *     becomes NULL until the next backward, which takes over its first contribution instead of adding it
+ *     to zeros); optimizers skip a parameter without a gradient.  Gradients no backward pass ever wrote
+ *     (BatchNorm running statistics) are zeroed in place and updated as in the reference.
  *   - nc_node carries extra trailing fields; code that only touches the reference's fields is
  *     unaffected because nodes are always allocated by nc_node_create.
  */

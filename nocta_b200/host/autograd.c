@@ -121,11 +121,32 @@ void nc_set_grad_ready_hook(nc_grad_ready_fn fn, void* ctx) { g_ready_fn = fn; g
 static void accumulate_leaf(nc_tensor* leaf, nc_tensor* g) {
     if (!leaf->requires_grad || leaf->numel != g->numel) return;
     if (!leaf->grad) {
+        /* first contribution since the gradient was cleared: take it over instead of adding it to zeros.  The
+         * new header shares g's storage; a later in-place add goes through add_into, which copies first while
+         * the storage is still shared. */
+        if (g->dtype == leaf->dtype && g->storage->device == leaf->storage->device && g->is_contiguous && nci_is_dense(g) &&
+            nc_tensor_shape_eq(g, leaf)) {
+            leaf->grad = nci_alias(g);
+            if (leaf->grad) {
+                leaf->grad->is_leaf = true;
+                leaf->grad->is_reachable = true; /* written by backward: see nc_tensor_zero_grad_ */
+                if (g_ready_fn) g_ready_fn(leaf, g_ready_ctx);
+                return;
+            }
+        }
         leaf->grad = nci_empty_on(leaf->shape, leaf->ndim, leaf->dtype, leaf->storage->device);
         if (!leaf->grad) return;
         nc_tensor_fill_(leaf->grad, 0.0);
     }
+    if (leaf->grad->storage->refcount > 1 && !nci_is_grad_arena(leaf->grad->storage)) {
+        /* taken over earlier in this sweep and still shared with the tensor it came from */
+        nc_tensor* own = add_into(leaf->grad, g);
+        if (own) { leaf->grad = own; own->is_leaf = true; own->is_reachable = true; }
+        if (g_ready_fn) g_ready_fn(leaf, g_ready_ctx);
+        return;
+    }
     nc_add_(leaf->grad, g);
+    leaf->grad->is_reachable = true;
     /* the accumulate kernel is queued: a data-parallel caller may now queue this gradient's all-reduce
      * behind it while the rest of the backward sweep keeps the device busy */
     if (g_ready_fn) g_ready_fn(leaf, g_ready_ctx);

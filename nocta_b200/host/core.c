@@ -640,7 +640,21 @@ void nc_tensor_requires_grad_(nc_tensor* t, bool rg) {
     }
 }
 nc_tensor* nc_tensor_detach(const nc_tensor* t) { return t ? nci_alias(t) : NULL; }
-void nc_tensor_zero_grad_(nc_tensor* t) { if (t && t->grad) nc_tensor_fill_(t->grad, 0.0); }
+/* A gradient that backward wrote since it was last cleared (marked in its is_reachable field, which is
+ * otherwise unused on gradient tensors) is dropped instead of being zeroed: the next backward takes over its
+ * first contribution instead of adding it to zeros.  Gradients backward never wrote (e.g. BatchNorm running
+ * statistics, which the reference registers as parameters with a zero .grad) and views into the flattened
+ * arena of nc_optimizer_flatten_grads are zeroed in place, as in the reference. */
+void nc_tensor_zero_grad_(nc_tensor* t) {
+    if (!t || !t->grad) return;
+    nc_tensor* g = t->grad;
+    if (g->is_reachable && g->storage && !nci_is_grad_arena(g->storage) && !g->grad_fn) {
+        nc_tensor_free(g);
+        t->grad = NULL;
+        return;
+    }
+    nc_tensor_fill_(g, 0.0);
+}
 bool nc_tensor_shape_eq(const nc_tensor* a, const nc_tensor* b) {
     if (!a || !b || a->ndim != b->ndim) return false;
     for (size_t i = 0; i < a->ndim; i++) if (a->shape[i] != b->shape[i]) return false;

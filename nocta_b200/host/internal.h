@@ -23,6 +23,8 @@ nc_tensor* nci_empty_like(const nc_tensor* like);
 nc_tensor* nci_alias(const nc_tensor* t);
 
 bool nci_on_cuda(const nc_tensor* t);
+/* the storage is a flattened-gradient arena of some optimizer (optim.c) */
+bool nci_is_grad_arena(const nc_storage* st);
 /* device pointer to element 0 (honours offset) */
 void* nci_dptr(const nc_tensor* t);
 #define nci_fptr(t) ((float*)nci_dptr(t))

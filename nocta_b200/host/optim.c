@@ -9,7 +9,7 @@
 #include "internal.h"
 #include <math.h>
 
-typedef struct { double grad_scale; } opt_common;
+typedef struct { double grad_scale; const nc_storage* arena; size_t arena_bytes; } opt_common;
 typedef struct { opt_common c; nc_sgd_config cfg; nc_tensor* velocity[NC_MAX_OPTIM_PARAMS]; } sgd_state;
 typedef struct { opt_common c; nc_adam_config cfg; nc_tensor* m[NC_MAX_OPTIM_PARAMS]; nc_tensor* v[NC_MAX_OPTIM_PARAMS]; nc_tensor* vmax[NC_MAX_OPTIM_PARAMS]; } adam_state;
 
@@ -21,6 +21,13 @@ void nc_optimizer_free(nc_optimizer* opt) {
 void nc_optimizer_step(nc_optimizer* opt) { if (opt && opt->step) opt->step(opt); }
 void nc_optimizer_zero_grad(nc_optimizer* opt) {
     if (!opt) return;
+    opt_common* c = opt->state;
+    if (c && c->arena) {
+        /* flattened gradients: one memset for the whole range when every gradient still lives there */
+        bool all = true;
+        for (size_t i = 0; i < opt->n_params && all; i++) all = opt->params[i]->grad && opt->params[i]->grad->storage == c->arena;
+        if (all) { nc_cuda_memset_async(c->arena->cuda_data, 0, c->arena_bytes, nci_stream()); return; }
+    }
     for (size_t i = 0; i < opt->n_params; i++) nc_tensor_zero_grad_(opt->params[i]);
 }
 void nc_optimizer_set_lr(nc_optimizer* opt, double lr) { if (opt) opt->lr = lr; }
@@ -37,6 +44,14 @@ void nc_optimizer_set_grad_scale(nc_optimizer* opt, double scale) { if (opt && o
  * view at a 256-byte aligned offset) and returns its device address and length in floats.  A data-parallel
  * caller sums that single range across ranks instead of one small buffer per parameter; padding between
  * views is zero and stays zero.  Gradients keep their values. */
+/* storages that hold flattened gradients: views into them are written in place although they share storage */
+#define NCI_MAX_ARENAS 16
+static const nc_storage* g_arenas[NCI_MAX_ARENAS];
+static int g_n_arenas = 0;
+bool nci_is_grad_arena(const nc_storage* st) {
+    for (int i = 0; i < g_n_arenas; i++) if (g_arenas[i] == st) return true;
+    return false;
+}
 void* nc_optimizer_flatten_grads(nc_optimizer* opt, size_t* n_floats) {
     if (!opt || !n_floats) return NULL;
     size_t total = 0;
@@ -49,6 +64,8 @@ void* nc_optimizer_flatten_grads(nc_optimizer* opt, size_t* n_floats) {
     nc_storage* arena = nc_storage_create_on(total * sizeof(float), NC_DEVICE_CUDA);
     if (!arena) return NULL;
     nc_cuda_memset_async(arena->cuda_data, 0, total * sizeof(float), nci_stream());
+    g_arenas[g_n_arenas % NCI_MAX_ARENAS] = arena; /* a reused slot only costs a copy, never correctness */
+    if (g_n_arenas < NCI_MAX_ARENAS) g_n_arenas++;
     size_t off = 0;
     for (size_t i = 0; i < opt->n_params; i++) {
         nc_tensor* p = opt->params[i];
@@ -69,6 +86,7 @@ void* nc_optimizer_flatten_grads(nc_optimizer* opt, size_t* n_floats) {
         off += (p->numel + 63) & ~(size_t)63;
     }
     void* base = arena->cuda_data;
+    if (opt->state) { ((opt_common*)opt->state)->arena = arena; ((opt_common*)opt->state)->arena_bytes = total * sizeof(float); }
     nc_storage_release(arena); /* the views keep it alive */
     *n_floats = total;
     return base;
