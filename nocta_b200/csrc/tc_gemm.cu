@@ -263,10 +263,9 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
             const int step = forA ? PC::NA_OWNERS : PC::NB_OWNERS;  // and the stride to its next one
             constexpr int NACH = A_MN ? BM / 32 : 1;  // copies of operand A per stage
             constexpr int NBCH = B_MN ? BN / 32 : 1;  // copies of operand B per stage
-            int my_n = 0;                             // copies this producer issues per stage
-            for (int c = own; c < (forA ? NACH : NBCH); c += step) my_n++;
-            const uint32_t my_bytes = forA ? (A_MN ? (uint32_t)my_n * CHUNK_BYTES : (uint32_t)A_BYTES)
-                                           : (B_MN ? (uint32_t)my_n * CHUNK_BYTES : (uint32_t)Cfg::B_BYTES);
+            // 32-wide chunks that lie entirely beyond the matrix edge (rows >= M, columns >= N) are not copied at
+            // all: their accumulator rows / columns are never stored, and skipping them saves issue slots and
+            // shared-memory writes (Cout = 64 fills only two of the four A chunks).
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
@@ -276,6 +275,11 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                 int kt_end = kt_begin + p.k_tiles_per_split;
                 if (kt_end > p.num_k_tiles) kt_end = p.num_k_tiles;
                 const int m0 = m_tile * BM, n0 = n_tile * BN;
+                const int edge = forA ? p.M - m0 : p.N - n0;  // chunks starting at or beyond it are skipped
+                int my_n = 0;                                 // copies this producer issues per stage of this tile
+                for (int c = own; c < (forA ? NACH : NBCH); c += step) my_n += (32 * c < edge) ? 1 : 0;
+                const bool chunked = forA ? A_MN : B_MN;
+                const uint32_t my_bytes = chunked ? (uint32_t)my_n * CHUNK_BYTES : (forA ? (uint32_t)A_BYTES : (uint32_t)Cfg::B_BYTES);
                 int dtw = 0, dth = 0, dtn = 0;
                 // DW: (first channel, tap) of this producer's B chunks
                 int ci0[4] = {0, 0, 0, 0}, dkh[4] = {0, 0, 0, 0}, dkw[4] = {0, 0, 0, 0};
@@ -298,7 +302,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                     const uint32_t full = smem_u32(&bar_full[s]);
                     const uint32_t a_dst = tiles_base + (uint32_t)s * Cfg::STAGE_BYTES;
                     const uint32_t b_dst = a_dst + A_BYTES;
-                    if (p.desc_variant == 13) {
+                    if (p.desc_variant == 13 || my_bytes == 0) {
                         mbar_arrive(full);
                     } else {
                         mbar_expect_tx(full, my_bytes);
@@ -310,7 +314,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
 #pragma unroll
                                     for (int i = 0; i < 4; i++) {
                                         const int c = own + i * step;
-                                        if (c < NACH) tma_2d(a_dst + c * CHUNK_BYTES, &tmA, m0 + 32 * c, k0, full);
+                                        if (c < NACH && 32 * c < edge) tma_2d(a_dst + c * CHUNK_BYTES, &tmA, m0 + 32 * c, k0, full);
                                     }
                                 }
                             } else if (!B_MN) {
@@ -319,7 +323,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
 #pragma unroll
                                 for (int i = 0; i < 4; i++) {
                                     const int c = own + i * step;
-                                    if (c < NBCH) tma_2d(b_dst + c * CHUNK_BYTES, &tmB, n0 + 32 * c, k0, full);
+                                    if (c < NBCH && 32 * c < edge) tma_2d(b_dst + c * CHUNK_BYTES, &tmB, n0 + 32 * c, k0, full);
                                 }
                             }
                         } else {  // KIND_DW (both operands MN-major)
@@ -328,13 +332,13 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
 #pragma unroll
                                 for (int i = 0; i < 4; i++) {
                                     const int c = own + i * step;
-                                    if (c < NACH) tma_4d(a_dst + c * CHUNK_BYTES, &tmA, m0 + 32 * c, w0, h0, nn0, full);
+                                    if (c < NACH && 32 * c < edge) tma_4d(a_dst + c * CHUNK_BYTES, &tmA, m0 + 32 * c, w0, h0, nn0, full);
                                 }
                             } else {
 #pragma unroll
                                 for (int i = 0; i < 4; i++) {
                                     const int c = own + i * step;
-                                    if (c < NBCH) tma_4d(b_dst + c * CHUNK_BYTES, &tmB, ci0[i], w0 + dkw[i] - p.pad, h0 + dkh[i] - p.pad, nn0, full);
+                                    if (c < NBCH && 32 * c < edge) tma_4d(b_dst + c * CHUNK_BYTES, &tmB, ci0[i], w0 + dkw[i] - p.pad, h0 + dkh[i] - p.pad, nn0, full);
                                 }
                             }
                         }
