@@ -315,6 +315,15 @@ int nc_cuda_sgd_update_f32_ex(float* param, float* velocity, float* grad, double
 int nc_cuda_adam_update_f32_ex(float* param, float* m, float* v, float* v_max, const float* grad,
                                double lr, double beta1, double beta2, double eps, double weight_decay,
                                double bias_corr1, double bias_corr2, double grad_scale, size_t n, void* stream);
+/* new: the same updates for `count` parameter tensors in one launch (per 48 tensors).  The four tables are HOST
+ * arrays of device pointers, read during the call; every tensor uses the same hyper-parameters. */
+int nc_cuda_sgd_update_multi_f32_ex(int count, float* const* params, float* const* velocities, float* const* grads,
+                                    const size_t* numel, double lr, double momentum, double dampening,
+                                    double weight_decay, int nesterov, int first_step, double grad_scale, void* stream);
+int nc_cuda_adam_update_multi_f32_ex(int count, float* const* params, float* const* m, float* const* v,
+                                     float* const* v_max, float* const* grads, const size_t* numel, double lr,
+                                     double beta1, double beta2, double eps, double weight_decay, double bias_corr1,
+                                     double bias_corr2, double grad_scale, void* stream);
 
 #ifdef __cplusplus
 }

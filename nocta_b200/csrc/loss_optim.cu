@@ -4,6 +4,7 @@
 // Semantics follow the reference CPU code: src/ops/loss.c:33-137,176-351, src/optim/sgd.c:13-115,
 // src/optim/adam.c:11-75, src/ops/reduction.c:158-198,473-513.
 #include "nc_common.cuh"
+#include <string.h>
 #include "../../include/nocta_cuda.h"
 
 using namespace ncc;
@@ -113,56 +114,99 @@ struct SgdArgs {
     int nesterov, first, write_grad;
 };
 
+__device__ __forceinline__ void sgd_element(float* __restrict__ p, float* __restrict__ v, float* __restrict__ g, const SgdArgs& a, size_t i) {
+    double gi = (double)g[i] * a.gscale;
+    double pi = (double)p[i];
+    if (a.wd != 0.0) {
+        // the CPU path stores the decayed gradient as f32 before using it (sgd.c:24-30)
+        float gf = (float)(gi + a.wd * pi);
+        if (a.write_grad) g[i] = gf;
+        gi = (double)gf;
+    }
+    double upd = gi;
+    if (v) {
+        double vi = (double)v[i];
+        vi = a.first ? gi : a.momentum * vi + (1.0 - a.dampening) * gi;
+        float vf = (float)vi;
+        v[i] = vf;
+        vi = (double)vf;
+        upd = a.nesterov ? gi + a.momentum * vi : vi;
+    }
+    p[i] = (float)(pi - a.lr * upd);
+}
+
 __global__ void __launch_bounds__(kThreads) sgd_kernel(float* __restrict__ p, float* __restrict__ v,
                                                        float* __restrict__ g, SgdArgs a, size_t n) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        double gi = (double)g[i] * a.gscale;
-        double pi = (double)p[i];
-        if (a.wd != 0.0) {
-            // the CPU path stores the decayed gradient as f32 before using it (sgd.c:24-30)
-            float gf = (float)(gi + a.wd * pi);
-            if (a.write_grad) g[i] = gf;
-            gi = (double)gf;
-        }
-        double upd = gi;
-        if (v) {
-            double vi = (double)v[i];
-            vi = a.first ? gi : a.momentum * vi + (1.0 - a.dampening) * gi;
-            float vf = (float)vi;
-            v[i] = vf;
-            vi = (double)vf;
-            upd = a.nesterov ? gi + a.momentum * vi : vi;
-        }
-        p[i] = (float)(pi - a.lr * upd);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) sgd_element(p, v, g, a, i);
+}
+
+// Several parameter tensors in one launch: the table travels as a kernel argument; a block owns a run of
+// kMultiChunk elements of one tensor (first_block[t] = index of tensor t's first block).
+constexpr int kMultiMax = 48;
+constexpr int kMultiChunk = 4096;
+struct MultiTable {
+    float* p[kMultiMax];
+    float* s1[kMultiMax];   // SGD: velocity; Adam: m
+    float* s2[kMultiMax];   // Adam: v
+    float* s3[kMultiMax];   // Adam: v_max (may be null)
+    float* g[kMultiMax];
+    unsigned int n[kMultiMax];
+    unsigned int first_block[kMultiMax + 1];
+    int count;
+};
+__device__ __forceinline__ int multi_find(const MultiTable& t, unsigned int block) {
+    int lo = 0, hi = t.count - 1;
+    while (lo < hi) {  // last tensor whose first block is <= block
+        const int mid = (lo + hi + 1) >> 1;
+        if (t.first_block[mid] <= block) lo = mid; else hi = mid - 1;
     }
+    return lo;
+}
+__global__ void __launch_bounds__(kThreads) sgd_multi_kernel(const __grid_constant__ MultiTable t, SgdArgs a) {
+    const int k = multi_find(t, blockIdx.x);
+    const size_t begin = (size_t)(blockIdx.x - t.first_block[k]) * kMultiChunk;
+    size_t end = begin + kMultiChunk;
+    if (end > t.n[k]) end = t.n[k];
+    for (size_t i = begin + threadIdx.x; i < end; i += kThreads) sgd_element(t.p[k], t.s1[k], t.g[k], a, i);
 }
 
 struct AdamArgs {
     double lr, b1, b2, eps, wd, bc1, bc2, gscale;
 };
 
+__device__ __forceinline__ void adam_element(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v, float* __restrict__ vmax,
+                                             const float* __restrict__ g, const AdamArgs& a, size_t i) {
+    double gi = (double)g[i] * a.gscale;
+    double pi = (double)p[i];
+    if (a.wd != 0.0) pi = pi - a.lr * a.wd * pi;
+    double mi = a.b1 * (double)m[i] + (1.0 - a.b1) * gi;
+    double vi = a.b2 * (double)v[i] + (1.0 - a.b2) * gi * gi;
+    m[i] = (float)mi;
+    v[i] = (float)vi;
+    double mh = mi / a.bc1, vh = vi / a.bc2;
+    if (vmax) {
+        double vm = fmax((double)vmax[i], vh);
+        float vmf = (float)vm;
+        vmax[i] = vmf;
+        vh = (double)vmf;
+    }
+    p[i] = (float)(pi - a.lr * mh / (sqrt(vh) + a.eps));
+}
+
 __global__ void __launch_bounds__(kThreads) adam_kernel(float* __restrict__ p, float* __restrict__ m,
                                                         float* __restrict__ v, float* __restrict__ vmax,
                                                         const float* __restrict__ g, AdamArgs a, size_t n) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        double gi = (double)g[i] * a.gscale;
-        double pi = (double)p[i];
-        if (a.wd != 0.0) pi = pi - a.lr * a.wd * pi;
-        double mi = a.b1 * (double)m[i] + (1.0 - a.b1) * gi;
-        double vi = a.b2 * (double)v[i] + (1.0 - a.b2) * gi * gi;
-        m[i] = (float)mi;
-        v[i] = (float)vi;
-        double mh = mi / a.bc1, vh = vi / a.bc2;
-        if (vmax) {
-            double vm = fmax((double)vmax[i], vh);
-            float vmf = (float)vm;
-            vmax[i] = vmf;
-            vh = (double)vmf;
-        }
-        p[i] = (float)(pi - a.lr * mh / (sqrt(vh) + a.eps));
-    }
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) adam_element(p, m, v, vmax, g, a, i);
+}
+
+__global__ void __launch_bounds__(kThreads) adam_multi_kernel(const __grid_constant__ MultiTable t, AdamArgs a) {
+    const int k = multi_find(t, blockIdx.x);
+    const size_t begin = (size_t)(blockIdx.x - t.first_block[k]) * kMultiChunk;
+    size_t end = begin + kMultiChunk;
+    if (end > t.n[k]) end = t.n[k];
+    for (size_t i = begin + threadIdx.x; i < end; i += kThreads) adam_element(t.p[k], t.s1[k], t.s2[k], t.s3[k], t.g[k], a, i);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -245,6 +289,40 @@ int loss_scratch(LossScratch* ls, long long work, cudaStream_t st) {
     return NC_CUDA_OK;
 }
 
+// Fills launch tables of at most kMultiMax tensors from the caller's host arrays and launches `launch` for each.
+template <class L>
+static int multi_launch(int count, float* const* params, float* const* s1, float* const* s2, float* const* s3, float* const* grads,
+                        const size_t* numel, const char* what, L launch) {
+    int done = 0;
+    while (done < count) {
+        MultiTable t;
+        memset(&t, 0, sizeof(t));
+        unsigned int blocks = 0;
+        while (done < count && t.count < kMultiMax) {
+            const size_t n = numel[done];
+            if (n == 0) { done++; continue; }
+            if (n > 0xffffffffull) return set_status(NC_CUDA_ERR_ARG, "%s: tensor %d has more than 2^32 elements", what, done);
+            const int k = t.count++;
+            t.p[k] = params[done];
+            t.s1[k] = s1 ? s1[done] : nullptr;
+            t.s2[k] = s2 ? s2[done] : nullptr;
+            t.s3[k] = s3 ? s3[done] : nullptr;
+            t.g[k] = grads[done];
+            t.n[k] = (unsigned int)n;
+            t.first_block[k] = blocks;
+            blocks += (unsigned int)((n + kMultiChunk - 1) / kMultiChunk);
+            done++;
+        }
+        t.first_block[t.count] = blocks;
+        if (t.count == 0) break;
+        launch(t, blocks);
+        NCC_COUNT_LAUNCH();
+        int rc = launch_status(what);
+        if (rc) return rc;
+    }
+    return NC_CUDA_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -304,6 +382,32 @@ int nc_cuda_adam_update_f32_ex(float* param, float* m, float* v, float* v_max, c
     adam_kernel<<<grid_for((long long)n, kThreads), kThreads, 0, (cudaStream_t)stream>>>(param, m, v, v_max, grad, a, n);
     NCC_COUNT_LAUNCH();
     return launch_status("adam");
+}
+
+int nc_cuda_sgd_update_multi_f32_ex(int count, float* const* params, float* const* velocities, float* const* grads,
+                                    const size_t* numel, double lr, double momentum, double dampening, double weight_decay,
+                                    int nesterov, int first_step, double grad_scale, void* stream) {
+    if (count <= 0) return NC_CUDA_OK;
+    NCC_REQUIRE(params && grads && numel && (momentum == 0.0 || velocities), "sgd_multi: null table");
+    for (int i = 0; i < count; i++)
+        NCC_REQUIRE(numel[i] == 0 || (params[i] && grads[i] && (momentum == 0.0 || velocities[i])), "sgd_multi: null pointer in entry %d", i);
+    SgdArgs a{lr, momentum, dampening, weight_decay, grad_scale, nesterov, first_step, 1};
+    cudaStream_t st = (cudaStream_t)stream;
+    return multi_launch(count, params, momentum != 0.0 ? velocities : nullptr, nullptr, nullptr, grads, numel, "sgd_multi",
+                        [&](const MultiTable& t, unsigned int blocks) { sgd_multi_kernel<<<blocks, kThreads, 0, st>>>(t, a); });
+}
+
+int nc_cuda_adam_update_multi_f32_ex(int count, float* const* params, float* const* m, float* const* v, float* const* v_max,
+                                     float* const* grads, const size_t* numel, double lr, double beta1, double beta2, double eps,
+                                     double weight_decay, double bias_corr1, double bias_corr2, double grad_scale, void* stream) {
+    if (count <= 0) return NC_CUDA_OK;
+    NCC_REQUIRE(params && m && v && grads && numel, "adam_multi: null table");
+    for (int i = 0; i < count; i++)
+        NCC_REQUIRE(numel[i] == 0 || (params[i] && m[i] && v[i] && grads[i]), "adam_multi: null pointer in entry %d", i);
+    AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2, grad_scale};
+    cudaStream_t st = (cudaStream_t)stream;
+    return multi_launch(count, params, m, v, v_max, grads, numel, "adam_multi",
+                        [&](const MultiTable& t, unsigned int blocks) { adam_multi_kernel<<<blocks, kThreads, 0, st>>>(t, a); });
 }
 
 void nc_cuda_sgd_step_f32(float* param, const float* grad, float lr, size_t n) {

@@ -136,6 +136,8 @@ SIGNATURES = {
     "nc_cuda_sgd_momentum_f32": (None, [_p, _p, _p, _f, _f, _f, _i, _z]),
     "nc_cuda_sgd_update_f32_ex": (_i, [_p, _p, _p, _d, _d, _d, _d, _i, _i, _d, _z, _p]),
     "nc_cuda_adam_update_f32_ex": (_i, [_p] * 5 + [_d] * 8 + [_z, _p]),
+    "nc_cuda_sgd_update_multi_f32_ex": (_i, [_i, _p, _p, _p, _p, _d, _d, _d, _d, _i, _i, _d, _p]),
+    "nc_cuda_adam_update_multi_f32_ex": (_i, [_i, _p, _p, _p, _p, _p, _p] + [_d] * 8 + [_p]),
 }
 
 

@@ -106,7 +106,11 @@ static bool param_ready(const nc_tensor* p, const char* who) {
 
 /* ------------------------------------------------------------------ SGD */
 static void sgd_step(nc_optimizer* self) {
+    /* one launch for all parameters that have a gradient (tables of device pointers gathered here) */
     sgd_state* st = self->state;
+    static float* P[NC_MAX_OPTIM_PARAMS]; static float* V[NC_MAX_OPTIM_PARAMS]; static float* G[NC_MAX_OPTIM_PARAMS];
+    static size_t Nn[NC_MAX_OPTIM_PARAMS];
+    int count = 0;
     for (size_t i = 0; i < self->n_params; i++) {
         nc_tensor* p = self->params[i];
         if (!param_ready(p, "sgd")) continue;
@@ -116,10 +120,12 @@ static void sgd_step(nc_optimizer* self) {
             if (!st->velocity[i]) continue;
             vel = nci_fptr(st->velocity[i]);
         }
-        nci_ok(nc_cuda_sgd_update_f32_ex(nci_fptr(p), vel, nci_fptr(p->grad), self->lr, st->cfg.momentum, st->cfg.dampening,
-                                         st->cfg.weight_decay, st->cfg.nesterov ? 1 : 0, self->t == 0 ? 1 : 0, st->c.grad_scale, p->numel,
-                                         nci_stream()), "sgd step");
+        P[count] = nci_fptr(p); V[count] = vel; G[count] = nci_fptr(p->grad); Nn[count] = p->numel;
+        count++;
     }
+    if (count)
+        nci_ok(nc_cuda_sgd_update_multi_f32_ex(count, P, V, G, Nn, self->lr, st->cfg.momentum, st->cfg.dampening, st->cfg.weight_decay,
+                                               st->cfg.nesterov ? 1 : 0, self->t == 0 ? 1 : 0, st->c.grad_scale, nci_stream()), "sgd step");
     self->t++;
 }
 static void sgd_free(void* state) {
@@ -153,6 +159,10 @@ static void adam_step(nc_optimizer* self) {
     adam_state* st = self->state;
     self->t++;
     const double bc1 = 1.0 - pow(st->cfg.beta1, (double)self->t), bc2 = 1.0 - pow(st->cfg.beta2, (double)self->t);
+    static float* P[NC_MAX_OPTIM_PARAMS]; static float* M[NC_MAX_OPTIM_PARAMS]; static float* V[NC_MAX_OPTIM_PARAMS];
+    static float* X[NC_MAX_OPTIM_PARAMS]; static float* G[NC_MAX_OPTIM_PARAMS];
+    static size_t Nn[NC_MAX_OPTIM_PARAMS];
+    int count = 0;
     for (size_t i = 0; i < self->n_params; i++) {
         nc_tensor* p = self->params[i];
         if (!param_ready(p, "adam")) continue;
@@ -162,10 +172,13 @@ static void adam_step(nc_optimizer* self) {
             if (st->cfg.amsgrad) st->vmax[i] = state_like(p);
         }
         if (!st->m[i] || !st->v[i]) continue;
-        nci_ok(nc_cuda_adam_update_f32_ex(nci_fptr(p), nci_fptr(st->m[i]), nci_fptr(st->v[i]), st->vmax[i] ? nci_fptr(st->vmax[i]) : NULL,
-                                          nci_fptr(p->grad), self->lr, st->cfg.beta1, st->cfg.beta2, st->cfg.eps, st->cfg.weight_decay, bc1,
-                                          bc2, st->c.grad_scale, p->numel, nci_stream()), "adam step");
+        P[count] = nci_fptr(p); M[count] = nci_fptr(st->m[i]); V[count] = nci_fptr(st->v[i]);
+        X[count] = st->vmax[i] ? nci_fptr(st->vmax[i]) : NULL; G[count] = nci_fptr(p->grad); Nn[count] = p->numel;
+        count++;
     }
+    if (count)
+        nci_ok(nc_cuda_adam_update_multi_f32_ex(count, P, M, V, X, G, Nn, self->lr, st->cfg.beta1, st->cfg.beta2, st->cfg.eps,
+                                                st->cfg.weight_decay, bc1, bc2, st->c.grad_scale, nci_stream()), "adam step");
 }
 static void adam_free(void* state) {
     adam_state* st = state;

@@ -543,3 +543,32 @@ def test_batchnorm_takes_statistics_offered_by_the_convolution(abi, shape):
         assert abi.nc_cuda_launch_count() - base == 3
     finally:
         abi.nc_cuda_set_conv_stats(prev)
+
+
+def test_multi_tensor_optimizer_updates_equal_the_single_tensor_kernels(abi):
+    """nc_cuda_sgd_update_multi_f32_ex / nc_cuda_adam_update_multi_f32_ex: bit-equal to one call per tensor, for
+    ragged sizes (1 element, not a multiple of the chunk, empty) and more tensors than one launch table holds."""
+    rng = np.random.default_rng(91)
+    sizes = [1, 7, 4096, 4097, 0, 100_003, 33] + [257] * 50
+    mk = lambda scale=1.0: [torch.from_numpy((rng.standard_normal(n) * scale).astype(np.float32)).cuda() for n in sizes]
+    p0, g0, v0, m0, s0 = mk(), mk(), mk(0.1), mk(0.1), [t.abs() for t in mk(0.01)]
+    tab = lambda ts: (C.c_void_p * len(ts))(*[t.data_ptr() if t.numel() else None for t in ts])
+    numel = (C.c_size_t * len(sizes))(*sizes)
+    # SGD momentum + weight decay + nesterov
+    pa, va = [t.clone() for t in p0], [t.clone() for t in v0]
+    for p_, v_, g_ in zip(pa, va, g0):
+        if p_.numel():
+            ok(abi, abi.nc_cuda_sgd_update_f32_ex(P(p_), P(v_), P(g_.clone()), 0.05, 0.9, 0.1, 1e-3, 1, 0, 0.5, p_.numel(), None))
+    pb, vb, gb = [t.clone() for t in p0], [t.clone() for t in v0], [t.clone() for t in g0]
+    ok(abi, abi.nc_cuda_sgd_update_multi_f32_ex(len(sizes), tab(pb), tab(vb), tab(gb), numel, 0.05, 0.9, 0.1, 1e-3, 1, 0, 0.5, None))
+    for a_, b_ in zip(pa + va, pb + vb):
+        assert torch.equal(a_, b_)
+    # AdamW
+    pa, ma, sa = [t.clone() for t in p0], [t.clone() for t in m0], [t.clone() for t in s0]
+    for p_, m_, s_, g_ in zip(pa, ma, sa, g0):
+        if p_.numel():
+            ok(abi, abi.nc_cuda_adam_update_f32_ex(P(p_), P(m_), P(s_), None, P(g_), 1e-3, 0.9, 0.999, 1e-8, 0.01, 0.1, 0.001, 1.0, p_.numel(), None))
+    pb, mb, sb = [t.clone() for t in p0], [t.clone() for t in m0], [t.clone() for t in s0]
+    ok(abi, abi.nc_cuda_adam_update_multi_f32_ex(len(sizes), tab(pb), tab(mb), tab(sb), None, tab(g0), numel, 1e-3, 0.9, 0.999, 1e-8, 0.01, 0.1, 0.001, 1.0, None))
+    for a_, b_ in zip(pa + ma + sa, pb + mb + sb):
+        assert torch.equal(a_, b_)
