@@ -434,10 +434,10 @@ int launch_colreduce(double** partial_out, int* slabs_out, size_t rows, int cols
 }
 inline bool al16(const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Stage 2: a block of 256 threads combines the slabs of 8 neighbouring columns; thread (tx, ty) adds slabs
-// ty, ty + 32, ... of column c0 + tx (a slab row of 8 columns is one 128-byte request), then thread (tx, 0)
-// adds the 32 lane sums in index order: the result does not depend on the launch geometry of stage 1.
-constexpr int kFinCols = 8, kFinLanes = 32;
+// Stage 2: a block of 256 threads combines the slabs of 4 neighbouring columns; thread (tx, ty) adds slabs
+// ty, ty + 64, ... of column c0 + tx (a slab row of 4 columns is one 64-byte request), then thread (tx, 0)
+// adds the 64 lane sums in index order: the result does not depend on the launch geometry of stage 1.
+constexpr int kFinCols = 4, kFinLanes = 64;
 __device__ __forceinline__ bool combine_slabs(const double* __restrict__ partial, int slabs, int C, int* c_out, double* s1, double* s2) {
     __shared__ double sh1[kFinLanes][kFinCols], sh2[kFinLanes][kFinCols];
     const int tx = threadIdx.x & (kFinCols - 1), ty = threadIdx.x / kFinCols;

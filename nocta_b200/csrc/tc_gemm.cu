@@ -1159,7 +1159,8 @@ static void pick_splits(int tiles, int nk, int* splits, int* kps) {
 
 int gemm(float* D, int ldd, const float* A, int lda, bool a_mn, const float* B, int ldb, bool b_mn, int M, int N, int K,
          const float* bias, float alpha, float beta, int mode, cudaStream_t st) {
-    if (M < 128 || N < 16 || K < 32) return NC_CUDA_ERR_UNSUPPORTED;
+    // rows beyond M inside the 128-row tile are zero-filled by TMA and never stored; tiny problems stay on the SIMT kernel
+    if (M < 32 || N < 16 || K < 32 || (long long)M * N * K < (1ll << 22)) return NC_CUDA_ERR_UNSUPPORTED;
     if ((lda & 3) || (ldb & 3)) return NC_CUDA_ERR_UNSUPPORTED;
     const int bn = pick_bn(N, mode);
     CUtensorMap ta, tb;
