@@ -323,6 +323,10 @@ int nc_cuda_conv2d_forward_f32_ex(float* y, const size_t ys[4], const float* x, 
         rc = tc::conv_nhwc(y, x, wp, bias, N, H, W, Cin, Cout, kH, kW, pad, tc_mode(), st);
         if (rc != NC_CUDA_ERR_UNSUPPORTED) return rc;
     }
+    if (tc_enabled() && stride == 1 && is_nhwc(g.ys, Cout, g.Ho, g.Wo) && tc::conv_few_channels_ok(Cin, Cout, kH, kW, g.Ho, g.Wo, tc_mode())) {
+        rc = tc::conv_few_channels(y, x, g.xs, w, bias, N, H, W, Cin, Cout, kH, kW, pad, round_in_relayout() != 0, st);
+        if (rc != NC_CUDA_ERR_UNSUPPORTED) return rc;
+    }
     if (convfirst::eligible(Cin, kH, kW, stride, Cout) && is_nhwc(g.ys, Cout, g.Ho, g.Wo)) {
         rc = convfirst::forward(y, x, g.xs, w, bias, N, H, W, Cout, pad, st);
         if (rc != NC_CUDA_ERR_UNSUPPORTED) return rc;

@@ -55,7 +55,10 @@ int set_round_outputs(int on);
 
 // Number of kernels launched by this library (bench bookkeeping).
 extern unsigned long long g_launches;
-#define NCC_COUNT_LAUNCH() (++ncc::g_launches)
+// g_epoch also advances when device memory is written by a copy or a memset of this library: together they
+// stamp "nothing this library does has touched device memory since".
+extern unsigned long long g_epoch;
+#define NCC_COUNT_LAUNCH() (++ncc::g_launches, ++ncc::g_epoch)
 
 // out[c] = sum over rows of in[r][c] for a dense row-major (rows x cols) matrix; two-stage,
 // double accumulation, fixed combine order (defined in pool_norm.cu).

@@ -13,6 +13,7 @@ static cudaStream_t g_stream = nullptr;
 static int g_sm_count = 0;
 static int g_math_mode = NC_CUDA_MATH_TF32;
 unsigned long long g_launches = 0;
+unsigned long long g_epoch = 0;
 
 static const int kScratchSlots = 9;
 static void* g_scratch[kScratchSlots] = {nullptr};
@@ -81,11 +82,11 @@ bool conv_stats_wanted() { return g_conv_stats_on != 0; }
 double* conv_stats_buffer(size_t slabs, int C, cudaStream_t st) { return (double*)scratch(8, sizeof(double) * 2 * slabs * (size_t)C, st); }
 void conv_stats_publish(const float* y, int C, long long rows, int slabs, double* partial) {
     g_offer.y = y; g_offer.C = C; g_offer.rows = rows; g_offer.slabs = slabs; g_offer.partial = partial;
-    g_offer.stamp = g_launches;
+    g_offer.stamp = g_epoch;
     g_offer.valid = true;
 }
 bool conv_stats_take(const float* x, int C, long long rows, double** partial, int* slabs) {
-    const bool hit = g_offer.valid && g_offer.y == x && g_offer.C == C && g_offer.rows == rows && g_offer.stamp == g_launches;
+    const bool hit = g_offer.valid && g_offer.y == x && g_offer.C == C && g_offer.rows == rows && g_offer.stamp == g_epoch;
     g_offer.valid = false;
     if (hit) { *partial = g_offer.partial; *slabs = g_offer.slabs; }
     return hit;
@@ -159,6 +160,7 @@ void nc_cuda_free(void* ptr) {
     if (ptr) cudaFree(ptr);
 }
 void nc_cuda_memcpy_h2d(void* dst, const void* src, size_t size) {
+    ++g_epoch;
     cudaError_t e = cudaMemcpyAsync(dst, src, size, cudaMemcpyHostToDevice, g_stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(g_stream);
     if (e != cudaSuccess) set_status(NC_CUDA_ERR_RUNTIME, "memcpy_h2d: %s", cudaGetErrorString(e));
@@ -169,10 +171,12 @@ void nc_cuda_memcpy_d2h(void* dst, const void* src, size_t size) {
     if (e != cudaSuccess) set_status(NC_CUDA_ERR_RUNTIME, "memcpy_d2h: %s", cudaGetErrorString(e));
 }
 void nc_cuda_memcpy_d2d(void* dst, const void* src, size_t size) {
+    ++g_epoch;
     cudaError_t e = cudaMemcpyAsync(dst, src, size, cudaMemcpyDeviceToDevice, g_stream);
     if (e != cudaSuccess) set_status(NC_CUDA_ERR_RUNTIME, "memcpy_d2d: %s", cudaGetErrorString(e));
 }
 void nc_cuda_memset(void* ptr, int value, size_t size) {
+    ++g_epoch;
     cudaError_t e = cudaMemsetAsync(ptr, value, size, g_stream);
     if (e != cudaSuccess) set_status(NC_CUDA_ERR_RUNTIME, "memset: %s", cudaGetErrorString(e));
 }
@@ -197,6 +201,7 @@ int nc_cuda_device_props(int index, char* name256, size_t* total_bytes, size_t* 
 void nc_cuda_set_stream(void* stream) { g_stream = (cudaStream_t)stream; }
 void* nc_cuda_get_stream(void) { return (void*)g_stream; }
 int nc_cuda_memcpy_h2d_async(void* dst, const void* src, size_t size, void* stream) {
+    ++g_epoch;
     NCC_TRY(cudaMemcpyAsync(dst, src, size, cudaMemcpyHostToDevice, (cudaStream_t)stream));
     return NC_CUDA_OK;
 }
@@ -205,6 +210,7 @@ int nc_cuda_memcpy_d2h_async(void* dst, const void* src, size_t size, void* stre
     return NC_CUDA_OK;
 }
 int nc_cuda_memset_async(void* ptr, int value, size_t size, void* stream) {
+    ++g_epoch;
     NCC_TRY(cudaMemsetAsync(ptr, value, size, (cudaStream_t)stream));
     return NC_CUDA_OK;
 }
@@ -284,6 +290,6 @@ unsigned int nc_cuda_device_error_word(void) {
     return h;
 }
 unsigned long long nc_cuda_launch_count(void) { return g_launches; }
-void nc_cuda_reset_launch_count(void) { g_launches = 0; }
+void nc_cuda_reset_launch_count(void) { g_launches = 0; }  // the epoch keeps counting
 
 }  // extern "C"

@@ -751,6 +751,9 @@ struct ConvhParams {
     int pitch;             // halo line pitch in pixels
     int halo_bytes, halo_stride;
     double* stat;          // non-null: per CTA and channel (sum, sum of squares) of the output it wrote, [gridDim.x][M][2]
+    int ksteps;            // MMA k-steps (of 8 channels) per chunk: 4, or fewer when the real channel count is small
+    int wtap_bytes;        // > 0: the weights of ALL taps stay resident in shared memory, this many bytes per tap
+                           //      (wrows rows of 128 B; one chunk only), loaded once per CTA instead of streaming
     int skip_loads;        // experiment: 1 = no weight copies, 2 = no halo copies, 3 = neither (timing only)
     unsigned int* err;
 };
@@ -829,6 +832,14 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
             if (lead < 0) lead = 0;
             int s = 0;
             uint32_t ph = 0;
+            if (p.wtap_bytes > 0) {
+                // all taps once, then only halos: one per tile, requested one tile ahead
+                const uint32_t full = smem_u32(&bar_wfull[0]);
+                mbar_expect_tx(full, (uint32_t)(ntaps * p.wtap_bytes));
+                for (int tap = 0; tap < ntaps; tap++) tma_2d(w_base + (uint32_t)(tap * p.wtap_bytes), &tmW, 0, tap * p.wrows, full);
+                issue_halo();
+                for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) issue_halo();
+            } else {
             issue_halo();
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const int m0 = (t / p.tiles_px) * BM;
@@ -848,6 +859,7 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                     }
                 }
             }
+            }
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -859,6 +871,9 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
             int s = 0;
             uint32_t ph = 0, tile_iter = 0, hcount = 0;
             bool ok = true;
+            const bool resident = p.wtap_bytes > 0;
+            if (resident && total_tiles > (int)blockIdx.x)
+                ok = mbar_wait(smem_u32(&bar_wfull[0]), 0u, p.err, 0x200u, abortp);
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, tile_iter++) {
                 const uint32_t ab = tile_iter & 1u;
                 if (!mbar_wait(smem_u32(&bar_acc_empty[ab]), ((tile_iter >> 1) & 1u) ^ 1u, p.err, 0x500u + ab, abortp)) { ok = false; break; }
@@ -870,19 +885,22 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                     const uint64_t dbs = db0 + (uint64_t)((slot * (uint32_t)p.halo_stride) >> 4);
                     int kh = 0, kw = 0;
                     for (int tap = 0; tap < ntaps; tap++) {
-                        if (!mbar_wait(smem_u32(&bar_wfull[s]), ph, p.err, 0x200u + s, abortp)) { ok = false; break; }
+                        if (!resident && !mbar_wait(smem_u32(&bar_wfull[s]), ph, p.err, 0x200u + s, abortp)) { ok = false; break; }
                         tc_fence_after();
-                        const uint64_t da = da0 + (uint64_t)(((uint32_t)s * (uint32_t)A_BYTES) >> 4);
+                        const uint64_t da = da0 + (uint64_t)((resident ? (uint32_t)(tap * p.wtap_bytes) : (uint32_t)s * (uint32_t)A_BYTES) >> 4);
                         const uint64_t db = dbs + (uint64_t)(((uint32_t)(kh * p.pitch + kw) * 128u) >> 4);
 #pragma unroll
                         for (int ks = 0; ks < BK / 8; ks++) {
+                            if (ks >= p.ksteps) break;
                             const uint32_t accum = (uint32_t)((cc | tap | ks) != 0);
 #pragma unroll
                             for (int sub = 0; sub < NSUB; sub++)  // sub-tile of 8 columns: + 8 pixel rows in the halo
                                 umma_tf32(acc + (uint32_t)(sub * NMMA), da + (uint64_t)(ks * 2), db + (uint64_t)(ks * 2 + sub * 64), idesc, accum);
                         }
-                        umma_commit(smem_u32(&bar_wempty[s]));
-                        if (++s == WS) { s = 0; ph ^= 1u; }
+                        if (!resident) {
+                            umma_commit(smem_u32(&bar_wempty[s]));
+                            if (++s == WS) { s = 0; ph ^= 1u; }
+                        }
                         if (++kw == p.kW) { kw = 0; kh++; }
                     }
                     if (ok) umma_commit(smem_u32(&bar_hempty[slot]));
@@ -1262,6 +1280,7 @@ static int conv_halo_launch(float* y, const float* x, const float* wpacked, cons
     p.halo_bytes = p.pitch * (TH + kH - 1) * 128;
     p.halo_stride = (p.halo_bytes + 1023) & ~1023;
     p.skip_loads = (g_desc_variant >= 11 && g_desc_variant <= 13) ? g_desc_variant - 10 : 0;
+    p.ksteps = BK / 8;
     p.err = ncc::device_error_word();
     const long long total = (long long)p.tiles_px * p.tiles_m;
     const int sms = ncc::sm_count();
@@ -1294,6 +1313,113 @@ static int conv_halo_nhwc(float* y, const float* x, const float* wpacked, const 
     const bool tall = (Ho % 32 == 0 && Wo % 8 == 0), square = (Ho % 16 == 0 && Wo % 16 == 0);
     if (tall && !(square && g_desc_variant == 8)) return conv_halo_launch<8, 32>(y, x, wpacked, bias, N, H, W, Cin, Cout, kH, kW, pad, st);
     return conv_halo_launch<16, 16>(y, x, wpacked, bias, N, H, W, Cin, Cout, kH, kW, pad, st);
+}
+
+// ---- few-channel first layer on the halo-resident kernel ----
+// The network input (3 channels) is copied once per call into a channels-last buffer of 128-byte pixel records of
+// which only the first 8 channels are written (channels 3..7 zero; the rest of a record is never read by an MMA:
+// a halo row is an ordinary 128-byte K-major row and only its first k-step, one MMA per tap, is issued).  Letting
+// TMA zero-fill the missing channels of an 8-channel tensor instead was measured 5x slower than moving whole
+// records.  The weights of all taps (Cout rows of 128 bytes each, 3 real values per row) stay resident in shared
+// memory, so per tile only the halo moves.
+__global__ void __launch_bounds__(256) few_channels_to_cl8_kernel(float4* __restrict__ out, const float* __restrict__ in, size_t pixels_per_image,
+                                                                  size_t total_pixels, int W, long long sn, long long sc, long long sh,
+                                                                  long long sw, int C, int round) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t p = (size_t)blockIdx.x * blockDim.x + threadIdx.x; p < total_pixels; p += stride) {
+        const size_t n = p / pixels_per_image, r = p % pixels_per_image;
+        const size_t h = r / (size_t)W, w = r % (size_t)W;
+        const float* src = in + (long long)n * sn + (long long)h * sh + (long long)w * sw;
+        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int c = 0; c < C; c++) { const float t = src[(long long)c * sc]; v[c] = round ? ncc::round_tf32(t) : t; }
+        out[8 * p] = make_float4(v[0], v[1], v[2], v[3]);      // a pixel record is 128 bytes; only its first 32 are ever used
+        out[8 * p + 1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+}
+// wp[(kh*kW + kw)][co][32]: channels ci < Cin from w (Cout, Cin, kH, kW), the rest zero
+__global__ void __launch_bounds__(256) pack_few_channel_weights_kernel(float* __restrict__ wp, const float* __restrict__ w, int Cout, int Cin,
+                                                                       int kH, int kW, int round) {
+    const int total = kH * kW * Cout * 32;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int ci = i & 31, co = (i >> 5) % Cout, tap = (i >> 5) / Cout;
+        float v = 0.f;
+        if (ci < Cin) {
+            v = w[((size_t)(co * Cin + ci) * kH + tap / kW) * kW + tap % kW];
+            if (round) v = ncc::round_tf32(v);
+        }
+        wp[i] = v;
+    }
+}
+
+bool conv_few_channels_ok(int Cin, int Cout, int kH, int kW, int Ho, int Wo, int mode) {
+    // off unless asked for (experiment switch 7): the CUDA-core first-layer kernel is the default path
+    return g_desc_variant == 7 && mode == NC_CUDA_MATH_TF32 && Cin >= 1 && Cin <= 8 && kH >= 1 && kW >= 1 && kH <= 3 && kW <= 3 &&
+           (Cout == 16 || Cout == 32 || Cout == 64) && Ho > 0 && Wo > 0 && (Ho % 32 == 0) && (Wo % 8 == 0);
+}
+
+// x: (N, Cin, H, W) with arbitrary element strides xs; y channels-last (N, Ho, Wo, Cout); w in the reference layout
+int conv_few_channels(float* y, const float* x, const long long xs[4], const float* w, const float* bias, int N, int H, int W, int Cin,
+                      int Cout, int kH, int kW, int pad, bool round, cudaStream_t st) {
+    constexpr int TW = 8, TH = 32;
+    const int Ho = H + 2 * pad - kH + 1, Wo = W + 2 * pad - kW + 1, ntaps = kH * kW;
+    if ((long long)N * Ho * Wo * Cout >= 0x7fffffffLL) return NC_CUDA_ERR_UNSUPPORTED;
+    const size_t pixels = (size_t)N * H * W;
+    float* x8 = (float*)ncc::scratch(4, sizeof(float) * 32 * pixels, st);
+    float* wp = (float*)ncc::scratch(3, sizeof(float) * 32 * (size_t)ntaps * Cout, st);
+    if (!x8 || !wp) return NC_CUDA_ERR_RUNTIME;
+    few_channels_to_cl8_kernel<<<ncc::grid_for((long long)pixels, 256), 256, 0, st>>>((float4*)x8, x, (size_t)H * W, pixels, W, xs[0], xs[1], xs[2],
+                                                                                    xs[3], Cin, round ? 1 : 0);
+    NCC_COUNT_LAUNCH();
+    pack_few_channel_weights_kernel<<<ncc::grid_for((long long)ntaps * Cout * 32, 256), 256, 0, st>>>(wp, w, Cout, Cin, kH, kW, round ? 1 : 0);
+    NCC_COUNT_LAUNCH();
+    CUtensorMap tw, tx;
+    unsigned long long wd[2] = {32, (unsigned long long)ntaps * Cout};
+    unsigned long long ws[1] = {32};
+    unsigned wb[2] = {32, (unsigned)Cout};
+    if (!make_map(&tw, wp, 2, wd, ws, wb, false)) return NC_CUDA_ERR_UNSUPPORTED;
+    unsigned long long dims[4] = {32, (unsigned long long)W, (unsigned long long)H, (unsigned long long)N};
+    unsigned long long str[3] = {32, (unsigned long long)W * 32, (unsigned long long)H * W * 32};
+    unsigned box[4] = {32, (unsigned)(TW + kW - 1), (unsigned)(TH + kH - 1), 1};
+    if (!make_map(&tx, x8, 4, dims, str, box, false)) return NC_CUDA_ERR_UNSUPPORTED;
+    ConvhParams p = {};
+    p.D = y; p.ldd = Cout; p.bias = bias; p.M = Cout;
+    p.Ho = Ho; p.Wo = Wo;
+    p.tiles_w = Wo / TW; p.tiles_h = Ho / TH;
+    p.tiles_px = N * p.tiles_w * p.tiles_h;
+    p.tiles_m = 1;
+    p.kH = kH; p.kW = kW; p.pad = pad;
+    p.cchunks = 1;
+    p.wrows = Cout;
+    p.pitch = TW + kW - 1;
+    p.halo_bytes = p.pitch * (TH + kH - 1) * 128;
+    p.halo_stride = (p.halo_bytes + 1023) & ~1023;
+    p.ksteps = 1;
+    p.wtap_bytes = Cout * 128;
+    p.err = ncc::device_error_word();
+    const int sms = ncc::sm_count();
+    const unsigned grid = (unsigned)(p.tiles_px < sms ? p.tiles_px : sms);
+    if (ncc::conv_stats_wanted()) p.stat = ncc::conv_stats_buffer(grid, Cout, st);
+    // resident weights: ntaps * Cout rows, plus the rows an M = 128 descriptor of the last tap reaches beyond them
+    const int smem = 2 * p.halo_stride + (ntaps * Cout + (BM - Cout)) * 128 + 1024;
+    if (smem > 2 * 44 * 1024 + kConvhWStages * A_BYTES + 1024) return NC_CUDA_ERR_UNSUPPORTED;
+    static bool attr_set = false;
+    if (!attr_set) {
+        NCC_TRY(cudaFuncSetAttribute(convh_kernel<TW, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     2 * 44 * 1024 + kConvhWStages * A_BYTES + 1024));
+        attr_set = true;
+    }
+    g_prof.next_flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
+    const bool prof = g_prof.on && g_prof.n < g_prof.cap;
+    if (prof) cudaEventRecord(g_prof.start[g_prof.n], st);
+    convh_kernel<TW, TH><<<grid, 192, smem, st>>>(tw, tx, p);
+    if (prof) {
+        cudaEventRecord(g_prof.stop[g_prof.n], st);
+        g_prof.n++;
+        g_prof.flops += g_prof.next_flops;
+    }
+    NCC_COUNT_LAUNCH();
+    if (p.stat) ncc::conv_stats_publish(y, Cout, (long long)N * Ho * Wo, (int)grid, p.stat);
+    return ncc::launch_status("convh_kernel(few channels)");
 }
 
 int conv_nhwc(float* y, const float* x, const float* wpacked, const float* bias, int N, int H, int W, int Cin, int Cout,

@@ -26,6 +26,11 @@ int conv_dw_nhwc(float* dW, const float* dy, const float* x, int N, int H, int W
                  int pad, int mode, cudaStream_t st);
 
 // (Cout,Cin,kH,kW) -> (kH,kW,Cout,Cin) for the forward; -> flipped (kH,kW,Cin,Cout) for dX.
+// Few-channel (network input) convolution on the halo-resident tensor-core kernel: x (N, Cin <= 8, H, W) with element
+// strides xs, y channels-last, w in the reference layout; plain TF32 mode, Cout in {16, 32, 64}, Ho % 32 == 0, Wo % 8 == 0.
+bool conv_few_channels_ok(int Cin, int Cout, int kH, int kW, int Ho, int Wo, int mode);
+int conv_few_channels(float* y, const float* x, const long long xs[4], const float* w, const float* bias, int N, int H, int W, int Cin,
+                      int Cout, int kH, int kW, int pad, bool round, cudaStream_t st);
 int pack_weights_fwd(float* wp, const float* w, int Cout, int Cin, int kH, int kW, bool round, cudaStream_t st);
 int pack_weights_dx(float* wp, const float* w, int Cout, int Cin, int kH, int kW, bool round, cudaStream_t st);
 

@@ -11,6 +11,7 @@
  * written (copy-on-write), so every activation gradient is touched once instead of twice.
  */
 #include "internal.h"
+#include <string.h>
 
 static int g_grad_enabled = 1;
 static nc_grad_mode g_grad_mode = NC_GRAD_ACCUMULATE;
@@ -118,8 +119,32 @@ static nc_grad_ready_fn g_ready_fn = NULL;
 static void* g_ready_ctx = NULL;
 void nc_set_grad_ready_hook(nc_grad_ready_fn fn, void* ctx) { g_ready_fn = fn; g_ready_ctx = ctx; }
 
+/* destinations offered to the backward callback that is running (see nci_param_grad_out) */
+static nc_tensor* g_dest[NC_MAX_INPUTS];
+nc_tensor* nci_param_grad_out(size_t input_index, const nc_tensor* like) {
+    nc_tensor* d = input_index < NC_MAX_INPUTS ? g_dest[input_index] : NULL;
+    if (d && d->dtype == like->dtype && d->is_contiguous && nc_tensor_shape_eq(d, like)) {
+        nc_tensor* a = nci_alias(d);
+        if (a) return a;
+    }
+    return nci_empty_on(like->shape, like->ndim, like->dtype, NC_DEVICE_CUDA);
+}
+static void offer_destinations(const nc_node* node) {
+    for (size_t j = 0; j < NC_MAX_INPUTS; j++) {
+        const nc_tensor* in = j < node->n_inputs ? node->inputs[j] : NULL;
+        g_dest[j] = (in && in->is_leaf && in->requires_grad && in->grad && !in->grad->is_reachable && in->grad->storage &&
+                     nci_is_grad_arena(in->grad->storage)) ? in->grad : NULL;
+    }
+}
+
 static void accumulate_leaf(nc_tensor* leaf, nc_tensor* g) {
     if (!leaf->requires_grad || leaf->numel != g->numel) return;
+    if (leaf->grad && g->storage == leaf->grad->storage && g->offset == leaf->grad->offset) {
+        /* the backward kernel wrote straight into the parameter's (cleared) arena slot */
+        leaf->grad->is_reachable = true;
+        if (g_ready_fn) g_ready_fn(leaf, g_ready_ctx);
+        return;
+    }
     if (!leaf->grad) {
         /* first contribution since the gradient was cleared: take it over instead of adding it to zeros.  The
          * new header shares g's storage; a later in-place add goes through add_into, which copies first while
@@ -182,7 +207,9 @@ nc_error nc_backward(nc_tensor* t, nc_tensor* grad_output) {
         nc_node* node = topo[i];
         nc_tensor* g = pending[i];
         if (!node || !g || !node->backward) continue;
+        offer_destinations(node);
         nc_tensor** in_grads = node->backward(g, node->saved_tensors, node->n_saved);
+        memset(g_dest, 0, sizeof(g_dest));
         if (!in_grads) { if (nc_last_error != NC_OK) rc = nc_last_error; continue; }
         /* callbacks return one distinct tensor object per input (views may share storage) */
         for (size_t j = 0; j < node->n_inputs; j++) {

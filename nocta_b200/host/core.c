@@ -654,6 +654,7 @@ void nc_tensor_zero_grad_(nc_tensor* t) {
         return;
     }
     nc_tensor_fill_(g, 0.0);
+    g->is_reachable = false; /* zero since cleared */
 }
 bool nc_tensor_shape_eq(const nc_tensor* a, const nc_tensor* b) {
     if (!a || !b || a->ndim != b->ndim) return false;

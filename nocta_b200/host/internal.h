@@ -23,6 +23,11 @@ nc_tensor* nci_empty_like(const nc_tensor* like);
 nc_tensor* nci_alias(const nc_tensor* t);
 
 bool nci_on_cuda(const nc_tensor* t);
+/* Where a backward function should put the gradient of its node's input `input_index` when that input is a
+ * parameter: a view of the parameter's slot in the flattened-gradient arena if that slot is still zero since it
+ * was cleared (so the kernel's result lands where the all-reduce reads it, with no accumulate launch), else a new
+ * tensor shaped like `like`.  Only valid inside a backward callback (autograd.c). */
+nc_tensor* nci_param_grad_out(size_t input_index, const nc_tensor* like);
 /* the storage is a flattened-gradient arena of some optimizer (optim.c) */
 bool nci_is_grad_arena(const nc_storage* st);
 /* device pointer to element 0 (honours offset) */

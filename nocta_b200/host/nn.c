@@ -134,8 +134,8 @@ static nc_tensor** bwd_linear(nc_tensor* g, nc_tensor** saved, size_t n) {
     if (!gc) return out;
     const int B = (int)(x->numel / W->shape[1]), in_f = (int)W->shape[1], out_f = (int)W->shape[0];
     if (xin->requires_grad) out[0] = nci_empty_on(xin->shape, xin->ndim, NC_F32, NC_DEVICE_CUDA);
-    if (W->requires_grad) out[1] = nci_empty_on(W->shape, 2, NC_F32, NC_DEVICE_CUDA);
-    if (b && b->requires_grad) out[2] = nci_empty_on(b->shape, b->ndim, NC_F32, NC_DEVICE_CUDA);
+    if (W->requires_grad) out[1] = nci_param_grad_out(1, W);
+    if (b && b->requires_grad) out[2] = nci_param_grad_out(2, b);
     nci_ok(nc_cuda_linear_backward_f32_ex(out[0] ? nci_fptr(out[0]) : NULL, out[1] ? nci_fptr(out[1]) : NULL,
                                           out[2] ? nci_fptr(out[2]) : NULL, nci_fptr(gc), nci_fptr(x), nci_fptr(W), B, in_f, out_f,
                                           nci_stream()), "linear backward");
@@ -241,8 +241,8 @@ static nc_tensor** bwd_conv2d(nc_tensor* g, nc_tensor** saved, size_t n) {
                                                                 stride, pad, nci_stream()), "conv2d backward (input)");
     }
     const bool need_w = W->requires_grad, need_b = b && b->requires_grad;
-    if (need_w) out[1] = nci_empty_on(W->shape, 4, NC_F32, NC_DEVICE_CUDA);
-    if (need_b) out[2] = nci_empty_on(b->shape, b->ndim, NC_F32, NC_DEVICE_CUDA);
+    if (need_w) out[1] = nci_param_grad_out(1, W);
+    if (need_b) out[2] = nci_param_grad_out(2, b);
     if (need_w || need_b)
         nci_ok(nc_cuda_conv2d_backward_weight_f32_ex(out[1] ? nci_fptr(out[1]) : NULL, out[2] ? nci_fptr(out[2]) : NULL, nci_fptr(gd), ys,
                                                      nci_fptr(x), xs, N, Cin, H, Wd, Cout, kH, kW, stride, pad, nci_stream()),
@@ -451,7 +451,7 @@ static nc_tensor** bwd_batchnorm2d(nc_tensor* g, nc_tensor** saved, size_t n) {
     nci_round_outputs(true);
     out[0] = nci_empty_like(x);
     /* node inputs are (input[, weight, bias]): parameter gradients exist only for an affine layer */
-    if (gamma) { out[1] = nci_empty_on(&cs, 1, NC_F32, NC_DEVICE_CUDA); out[2] = nci_empty_on(&cs, 1, NC_F32, NC_DEVICE_CUDA); }
+    if (gamma) { out[1] = nci_param_grad_out(1, gamma); out[2] = nci_param_grad_out(2, gamma); }
     if (out[0] && (!gamma || (out[1] && out[2])))
         nci_ok(nc_cuda_batchnorm_backward_f32_ex(nci_fptr(out[0]), gamma ? nci_fptr(out[1]) : NULL, gamma ? nci_fptr(out[2]) : NULL, nci_fptr(gd), nci_fptr(x),
                                                  gamma ? nci_fptr(gamma) : NULL, nci_fptr(mean), nci_fptr(var), NULL, beta ? nci_fptr(beta) : NULL,
@@ -547,7 +547,7 @@ static nc_tensor** bwd_bn_relu_pool(nc_tensor* g, nc_tensor** saved, size_t n) {
     size_t cs = (size_t)C;
     nci_round_outputs(true);
     out[0] = nci_empty_like(x);
-    if (gamma) { out[1] = nci_empty_on(&cs, 1, NC_F32, NC_DEVICE_CUDA); out[2] = nci_empty_on(&cs, 1, NC_F32, NC_DEVICE_CUDA); }
+    if (gamma) { out[1] = nci_param_grad_out(1, gamma); out[2] = nci_param_grad_out(2, gamma); }
     if (out[0] && (!gamma || (out[1] && out[2])))
         nci_ok(nc_cuda_batchnorm_relu_maxpool2_backward_f32_ex(nci_fptr(out[0]), gamma ? nci_fptr(out[1]) : NULL, gamma ? nci_fptr(out[2]) : NULL,
                                                                nci_fptr(gd), (const uint8_t*)nci_dptr(idx), nci_fptr(x), gamma ? nci_fptr(gamma) : NULL,

@@ -26,7 +26,11 @@ void nc_optimizer_zero_grad(nc_optimizer* opt) {
         /* flattened gradients: one memset for the whole range when every gradient still lives there */
         bool all = true;
         for (size_t i = 0; i < opt->n_params && all; i++) all = opt->params[i]->grad && opt->params[i]->grad->storage == c->arena;
-        if (all) { nc_cuda_memset_async(c->arena->cuda_data, 0, c->arena_bytes, nci_stream()); return; }
+        if (all) {
+            nc_cuda_memset_async(c->arena->cuda_data, 0, c->arena_bytes, nci_stream());
+            for (size_t i = 0; i < opt->n_params; i++) opt->params[i]->grad->is_reachable = false; /* zero since cleared */
+            return;
+        }
     }
     for (size_t i = 0; i < opt->n_params; i++) nc_tensor_zero_grad_(opt->params[i]);
 }

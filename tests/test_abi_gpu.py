@@ -535,6 +535,12 @@ def test_batchnorm_takes_statistics_offered_by_the_convolution(abi, shape):
         ok(abi, abi.nc_cuda_scalar_f32_ex(2, P(y), P(y), 2.0, y.numel(), None))   # y *= 2 in place (op 2 = mul)
         out2, m2, v2 = bn(y)
         close(host(m2), 2 * host(ref_m), 2e-6)
+        # a copy into the tensor through the library voids it too
+        conv()
+        fresh = np.ascontiguousarray(rng.standard_normal((N, H, H, Cout)).astype(np.float32))
+        abi.nc_cuda_memcpy_h2d(P(y), fresh.ctypes.data_as(C.c_void_p), fresh.nbytes)
+        out3, m3, v3 = bn(y)
+        close(host(m3), fresh.reshape(-1, Cout).mean(0), 2e-5)
         # and it is tied to the tensor
         conv()
         other = y.clone()
@@ -572,3 +578,31 @@ def test_multi_tensor_optimizer_updates_equal_the_single_tensor_kernels(abi):
     ok(abi, abi.nc_cuda_adam_update_multi_f32_ex(len(sizes), tab(pb), tab(mb), tab(sb), None, tab(g0), numel, 1e-3, 0.9, 0.999, 1e-8, 0.01, 0.1, 0.001, 1.0, None))
     for a_, b_ in zip(pa + ma + sa, pb + mb + sb):
         assert torch.equal(a_, b_)
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 32, 8, 16, 1), (3, 3, 64, 64, 64, 1), (2, 3, 34, 10, 32, 0), (2, 1, 32, 16, 64, 1), (1, 8, 32, 24, 64, 1)])
+def test_few_channel_convolution_on_tensor_cores(abi, shape):
+    """Network-input convolutions (<= 8 channels) in plain TF32 mode run on the halo-resident tensor-core kernel
+    (8-channel padded copy of the input, weights of all taps resident): against the oracle at the TF32 bar, with
+    NCHW input strides as the first layer sees them."""
+    from nocta_b200 import cuda_abi
+    N, Cin, H, W, Cout, pad = shape
+    Ho, Wo = H + 2 * pad - 2, W + 2 * pad - 2
+    rng = np.random.default_rng(H * W + Cout)
+    x = rng.standard_normal((N, Cin, H, W)).astype(np.float32)
+    w = (rng.standard_normal((Cout, Cin, 3, 3)) / 3).astype(np.float32)
+    b = rng.standard_normal(Cout).astype(np.float32)
+    y = torch.empty(N, Ho, Wo, Cout, device="cuda")
+    xs = cuda_abi.size4([Cin * H * W, H * W, W, 1])                 # dense NCHW input
+    ys = cuda_abi.size4([Ho * Wo * Cout, 1, Wo * Cout, Cout])       # channels-last output
+    abi.nc_cuda_set_math_mode(MODE_TF32)
+    abi.lib.nc_cuda_debug_desc_variant.argtypes = [C.c_int]
+    abi.lib.nc_cuda_debug_desc_variant(7)                           # this path is selected by the experiment switch
+    try:
+        before = abi.nc_cuda_launch_count()
+        ok(abi, abi.nc_cuda_conv2d_forward_f32_ex(P(y), ys, P(dev(x)), xs, P(dev(w)), P(dev(b)), N, Cin, H, W, Cout, 3, 3, 1, pad, None))
+        assert abi.nc_cuda_launch_count() - before == 3             # input copy, weight pack, convolution
+    finally:
+        abi.lib.nc_cuda_debug_desc_variant(0)
+    ref = O.conv2d_forward(x, w, b, 1, pad).transpose(0, 2, 3, 1)
+    close(host(y), ref, TOL_TF32)

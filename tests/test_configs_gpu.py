@@ -152,3 +152,44 @@ def test_eval_mode_predictions_match_reference(ours, theirs, name, kw):
     assert float((top2[:, 1] - top2[:, 0]).min()) > 1e-4 * float(np.abs(exp_logits).max())
     assert np.array_equal(pred, exp_pred)
     assert correct == exp_correct
+
+
+@pytest.mark.parametrize("name,kw", [("lenet", dict()), ("vgg", dict(batch=8, size=16, widths=(32, 64, 128), classes=10)), ("convbn", dict(batch=16))])
+def test_flattened_gradient_arena_gives_identical_updates(ours, name, kw):
+    """The data-parallel layout (all gradients re-homed into one arena by nc_optimizer_flatten_grads, backward kernels
+    writing straight into its slots, one memset per step) must not change a single bit of the training result."""
+    import ctypes as C
+    from nocta_b200 import capi, configs
+    lib = ours.api.lib
+    lib.nc_optimizer_flatten_grads.restype = C.c_void_p
+    lib.nc_optimizer_flatten_grads.argtypes = [capi.OptimizerP, C.POINTER(C.c_size_t)]
+
+    def go(flatten):
+        net, forward, kind, data = configs.BUILDERS[name](ours, **kw)
+        tensors = configs.upload(ours, kind, data)
+        configs.train_step(ours, net, forward, kind, tensors)   # gradients exist after the first step
+        net.free_step_tensors()
+        if flatten:
+            n = C.c_size_t(0)
+            assert lib.nc_optimizer_flatten_grads(net.optimizer, C.byref(n)) and n.value > 0
+        losses = []
+        for _ in range(3):
+            loss = configs.train_step(ours, net, forward, kind, tensors)
+            losses.append(float(ours.api.to_numpy(loss).ravel()[0]))
+            net.free_step_tensors()
+        params = {n_: ours.api.to_numpy(p) for n_, p in net.named_params()}
+        grads = {n_: ours.api.grad_numpy(p) for n_, p in net.named_params()}
+        configs.free_inputs(ours, kind, tensors)
+        return losses, params, grads
+
+    ours.api.lib.nc_cuda_set_math_mode(MODE_SIMT)
+    try:
+        l0, p0, g0 = go(False)
+        l1, p1, g1 = go(True)
+    finally:
+        ours.api.lib.nc_cuda_set_math_mode(MODE_TF32)
+    assert l0 == l1
+    for k in p0:
+        assert np.array_equal(p0[k], p1[k]), k
+        if g0[k] is not None and g1[k] is not None:
+            assert np.array_equal(g0[k], g1[k]), k
