@@ -55,6 +55,10 @@ struct TcParams {
     unsigned int* err;
 };
 
+// Experiment switch (nc_cuda_debug_desc_variant), 0 in production.  1..6: cap the operand ring of tc_kernel at that
+// many stages; 7: network-input convolutions (<= 8 channels) on the halo-resident kernel instead of the CUDA-core
+// first-layer kernel; 8: allow 16 x 16 halo tiles; 9: never use the halo-resident kernel; 11 / 12 / 13: timing runs
+// without weight copies / halo copies / any operand copy (results are garbage, the barriers still complete).
 static int g_desc_variant = 0;
 void set_desc_variant(int v) { g_desc_variant = v; }
 
@@ -1319,9 +1323,10 @@ static int conv_halo_nhwc(float* y, const float* x, const float* wpacked, const 
 // The network input (3 channels) is copied once per call into a channels-last buffer of 128-byte pixel records of
 // which only the first 8 channels are written (channels 3..7 zero; the rest of a record is never read by an MMA:
 // a halo row is an ordinary 128-byte K-major row and only its first k-step, one MMA per tap, is issued).  Letting
-// TMA zero-fill the missing channels of an 8-channel tensor instead was measured 5x slower than moving whole
-// records.  The weights of all taps (Cout rows of 128 bytes each, 3 real values per row) stay resident in shared
-// memory, so per tile only the halo moves.
+// TMA zero-fill the missing channels of an 8-channel tensor instead was slower than moving whole records.  The weights of all taps (Cout rows of 128 bytes each, 3 real values per row) stay resident in shared
+// memory, so per tile only the halo moves.  Measured on the 256 x 3 x 64 x 64 -> 64 channel layer: 114 us in
+// isolation (copy + pack + kernel) against 127 us for the CUDA-core kernel, but slower than it inside a training
+// step, so the path stays behind the experiment switch.
 __global__ void __launch_bounds__(256) few_channels_to_cl8_kernel(float4* __restrict__ out, const float* __restrict__ in, size_t pixels_per_image,
                                                                   size_t total_pixels, int W, long long sn, long long sc, long long sh,
                                                                   long long sw, int C, int round) {
