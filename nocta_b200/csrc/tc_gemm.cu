@@ -762,7 +762,9 @@ struct ConvhParams {
     unsigned int* err;
 };
 
-template <int TW, int TH>  // pixel tile: 16 x 16 (two MMAs of N = 128 per k-step) or 8 x 32 (one MMA of N = 256)
+// FEW: the few-channel variant (weights of all taps resident, p.ksteps MMAs per tap) is a separate instantiation so
+// that the single-thread issue loops of the production kernel carry none of its branches.
+template <int TW, int TH, bool FEW = false>  // pixel tile: 16 x 16 (two MMAs of N = 128 per k-step) or 8 x 32 (one MMA of N = 256)
 __global__ void __launch_bounds__(192, 1)
 convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const ConvhParams p) {
     static_assert(TW * TH == 256 && TW % 8 == 0, "256 pixels per tile");
@@ -836,7 +838,7 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
             if (lead < 0) lead = 0;
             int s = 0;
             uint32_t ph = 0;
-            if (p.wtap_bytes > 0) {
+            if (FEW) {
                 // all taps once, then only halos: one per tile, requested one tile ahead
                 const uint32_t full = smem_u32(&bar_wfull[0]);
                 mbar_expect_tx(full, (uint32_t)(ntaps * p.wtap_bytes));
@@ -875,7 +877,7 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
             int s = 0;
             uint32_t ph = 0, tile_iter = 0, hcount = 0;
             bool ok = true;
-            const bool resident = p.wtap_bytes > 0;
+            constexpr bool resident = FEW;
             if (resident && total_tiles > (int)blockIdx.x)
                 ok = mbar_wait(smem_u32(&bar_wfull[0]), 0u, p.err, 0x200u, abortp);
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, tile_iter++) {
@@ -895,7 +897,7 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                         const uint64_t db = dbs + (uint64_t)(((uint32_t)(kh * p.pitch + kw) * 128u) >> 4);
 #pragma unroll
                         for (int ks = 0; ks < BK / 8; ks++) {
-                            if (ks >= p.ksteps) break;
+                            if (FEW && ks >= p.ksteps) break;
                             const uint32_t accum = (uint32_t)((cc | tap | ks) != 0);
 #pragma unroll
                             for (int sub = 0; sub < NSUB; sub++)  // sub-tile of 8 columns: + 8 pixel rows in the halo
@@ -1409,14 +1411,14 @@ int conv_few_channels(float* y, const float* x, const long long xs[4], const flo
     if (smem > 2 * 44 * 1024 + kConvhWStages * A_BYTES + 1024) return NC_CUDA_ERR_UNSUPPORTED;
     static bool attr_set = false;
     if (!attr_set) {
-        NCC_TRY(cudaFuncSetAttribute(convh_kernel<TW, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        NCC_TRY(cudaFuncSetAttribute(convh_kernel<TW, TH, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      2 * 44 * 1024 + kConvhWStages * A_BYTES + 1024));
         attr_set = true;
     }
     g_prof.next_flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
     const bool prof = g_prof.on && g_prof.n < g_prof.cap;
     if (prof) cudaEventRecord(g_prof.start[g_prof.n], st);
-    convh_kernel<TW, TH><<<grid, 192, smem, st>>>(tw, tx, p);
+    convh_kernel<TW, TH, true><<<grid, 192, smem, st>>>(tw, tx, p);
     if (prof) {
         cudaEventRecord(g_prof.stop[g_prof.n], st);
         g_prof.n++;
