@@ -57,8 +57,7 @@ struct TcParams {
 
 // Experiment switch (nc_cuda_debug_desc_variant), 0 in production.  1..6: cap the operand ring of tc_kernel at that
 // many stages; 7: network-input convolutions (<= 8 channels) on the halo-resident kernel instead of the CUDA-core
-// first-layer kernel; 8: allow 16 x 16 halo tiles; 9: never use the halo-resident kernel; 11 / 12 / 13: timing runs
-// without weight copies / halo copies / any operand copy (results are garbage, the barriers still complete).
+// first-layer kernel; 8: allow 16 x 16 halo tiles; 9: never use the halo-resident kernel.
 static int g_desc_variant = 0;
 void set_desc_variant(int v) { g_desc_variant = v; }
 
@@ -306,7 +305,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                     const uint32_t full = smem_u32(&bar_full[s]);
                     const uint32_t a_dst = tiles_base + (uint32_t)s * Cfg::STAGE_BYTES;
                     const uint32_t b_dst = a_dst + A_BYTES;
-                    if (p.desc_variant == 13 || my_bytes == 0) {
+                    if (my_bytes == 0) {
                         mbar_arrive(full);
                     } else {
                         mbar_expect_tx(full, my_bytes);
@@ -391,11 +390,6 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                 for (int kt = kt_begin; kt < kt_end; kt++) {
                     if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, p.err, 0x100u + s, abortp)) { ok = false; break; }
                     const uint32_t full = smem_u32(&bar_full[s]);
-                    if (p.desc_variant == 13) {  // timing experiment: no copies, the MMAs run on whatever is in shared memory
-                        mbar_arrive(full);
-                        if (++s == STAGES) { s = 0; ph ^= 1u; }
-                        continue;
-                    }
                     mbar_expect_tx(full, (uint32_t)Cfg::OPER_BYTES);
                     const uint32_t a_dst = tiles_base + (uint32_t)s * Cfg::STAGE_BYTES;
                     const uint32_t b_dst = a_dst + A_BYTES;
@@ -758,7 +752,6 @@ struct ConvhParams {
     int ksteps;            // MMA k-steps (of 8 channels) per chunk: 4, or fewer when the real channel count is small
     int wtap_bytes;        // > 0: the weights of ALL taps stay resident in shared memory, this many bytes per tap
                            //      (wrows rows of 128 B; one chunk only), loaded once per CTA instead of streaming
-    int skip_loads;        // experiment: 1 = no weight copies, 2 = no halo copies, 3 = neither (timing only)
     unsigned int* err;
 };
 
@@ -826,11 +819,8 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                 const int tw = pt % p.tiles_w, tt = pt / p.tiles_w;
                 const int th = tt % p.tiles_h, n = tt / p.tiles_h;
                 const uint32_t full = smem_u32(&bar_hfull[slot]);
-                if (p.skip_loads & 2) mbar_arrive(full);
-                else {
-                    mbar_expect_tx(full, (uint32_t)p.halo_bytes);
-                    tma_4d(halo_base + slot * (uint32_t)p.halo_stride, &tmX, hcc * 32, tw * TW - p.pad, th * TH - p.pad, n, full);
-                }
+                mbar_expect_tx(full, (uint32_t)p.halo_bytes);
+                tma_4d(halo_base + slot * (uint32_t)p.halo_stride, &tmX, hcc * 32, tw * TW - p.pad, th * TH - p.pad, n, full);
                 hcount++;
                 if (++hcc == p.cchunks) { hcc = 0; ht += gridDim.x; }
             };
@@ -856,11 +846,8 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                         if (!ok) break;
                         if (!mbar_wait(smem_u32(&bar_wempty[s]), ph ^ 1u, p.err, 0x100u + s, abortp)) { ok = false; break; }
                         const uint32_t full = smem_u32(&bar_wfull[s]);
-                        if (p.skip_loads & 1) mbar_arrive(full);
-                        else {
-                            mbar_expect_tx(full, (uint32_t)A_BYTES);
-                            tma_2d(w_base + (uint32_t)s * A_BYTES, &tmW, cc * 32, wrow, full);
-                        }
+                        mbar_expect_tx(full, (uint32_t)A_BYTES);
+                        tma_2d(w_base + (uint32_t)s * A_BYTES, &tmW, cc * 32, wrow, full);
                         if (++s == WS) { s = 0; ph ^= 1u; }
                     }
                 }
@@ -1285,7 +1272,6 @@ static int conv_halo_launch(float* y, const float* x, const float* wpacked, cons
     p.pitch = TW + kW - 1;
     p.halo_bytes = p.pitch * (TH + kH - 1) * 128;
     p.halo_stride = (p.halo_bytes + 1023) & ~1023;
-    p.skip_loads = (g_desc_variant >= 11 && g_desc_variant <= 13) ? g_desc_variant - 10 : 0;
     p.ksteps = BK / 8;
     p.err = ncc::device_error_word();
     const long long total = (long long)p.tiles_px * p.tiles_m;
