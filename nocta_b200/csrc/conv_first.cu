@@ -88,7 +88,7 @@ struct TileGeo {
     static constexpr int TR = PG / (TW / 4);  // output rows per CTA
 };
 template <int COUT>
-__global__ void __launch_bounds__(256) fwd_tile_kernel(float* __restrict__ y, const float* __restrict__ in,
+__global__ void __launch_bounds__(256, 4) fwd_tile_kernel(float* __restrict__ y, const float* __restrict__ in,
                                                        const float* __restrict__ w, const float* __restrict__ bias, Geo g,
                                                        int tiles_h, int tiles_w, int ntiles) {
     using T = TileGeo<COUT>;
@@ -173,7 +173,7 @@ template <int COUT>
 static void launch_fwd_tile(float* y, const float* x, const float* w, const float* bias, const Geo& g, cudaStream_t st) {
     const int tiles_h = (g.Ho + TileGeo<COUT>::TR - 1) / TileGeo<COUT>::TR, tiles_w = (g.Wo + TW - 1) / TW;
     const long long ntiles = (long long)g.N * tiles_h * tiles_w;
-    const long long cap = (long long)ncc::sm_count() * 3;  // 3 CTAs of 71 registers x 256 threads fit an SM
+    const long long cap = (long long)ncc::sm_count() * 4;  // 4 CTAs of 64 registers x 256 threads fit an SM
     fwd_tile_kernel<COUT><<<(int)(ntiles < cap ? ntiles : cap), 256, 0, st>>>(y, x, w, bias, g, tiles_h, tiles_w, (int)ntiles);
 }
 
