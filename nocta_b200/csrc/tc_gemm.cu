@@ -1,5 +1,6 @@
 // Tensor-core contractions for sm_100a: TMA-fed, tcgen05.mma (kind::tf32) with the accumulator in
-// tensor memory, written with inline PTX.  One kernel template serves three problem kinds:
+// tensor memory, written with inline PTX.  tc_kernel serves four problem kinds; convh_kernel (further down) is the
+// halo-resident convolution used for forward / input gradient wherever whole 8 x 32 pixel tiles fit.
 //
 //   GEMM   D(M,N) = A * B^T        either operand K-major or MN-major in memory
 //   CONV   channels-last implicit GEMM, stride 1: rows = 128 output pixels (a w x h x n box),
@@ -15,7 +16,8 @@
 //   DW     weight gradient: rows = output channels, cols = (kh, kw, ci), reduction = 32-pixel
 //          boxes; both operands MN-major; split over the reduction with an ordered second stage.
 //
-// CTA = 6 warps: warp 0 issues TMA, warp 1 allocates TMEM and issues MMAs (one lane), warps 2-5
+// CTA = 6 warps (kernels with an MN-major operand add up to five more TMA-issuing warps): warp 0 issues TMA, warp 1
+// allocates TMEM and issues MMAs (one lane), warps 2-5
 // convert operands in shared memory when the math mode asks for it (round-to-nearest TF32, or the
 // hi/lo split of 3xTF32) and then run the epilogue (tcgen05.ld -> registers -> global).
 // Every mbarrier wait is bounded: on expiry the kernel records a code in the device error word,
