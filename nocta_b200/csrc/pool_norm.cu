@@ -435,8 +435,8 @@ int launch_colreduce(double** partial_out, int* slabs_out, size_t rows, int cols
 inline bool al16(const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Stage 2: a block of 256 threads combines the slabs of 4 neighbouring columns; thread (tx, ty) adds slabs
-// ty, ty + 64, ... of column c0 + tx (a slab row of 4 columns is one 64-byte request), then thread (tx, 0)
-// adds the 64 lane sums in index order: the result does not depend on the launch geometry of stage 1.
+// ty, ty + 64, ... of column c0 + tx (a slab row of 4 columns is one 64-byte request), then a pairwise tree of
+// fixed shape adds the 64 lane sums: the same partials always give the same bits.
 constexpr int kFinCols = 4, kFinLanes = 64;
 __device__ __forceinline__ bool combine_slabs(const double* __restrict__ partial, int slabs, int C, int* c_out, double* s1, double* s2) {
     __shared__ double sh1[kFinLanes][kFinCols], sh2[kFinLanes][kFinCols];
@@ -444,7 +444,7 @@ __device__ __forceinline__ bool combine_slabs(const double* __restrict__ partial
     const int c = blockIdx.x * kFinCols + tx;
     double a = 0.0, b = 0.0;
     if (c < C) {
-#pragma unroll 4
+#pragma unroll 8
         for (int s = ty; s < slabs; s += kFinLanes) {
             const double2 v = *reinterpret_cast<const double2*>(partial + ((size_t)s * C + c) * 2);
             a += v.x;
@@ -454,11 +454,17 @@ __device__ __forceinline__ bool combine_slabs(const double* __restrict__ partial
     sh1[ty][tx] = a;
     sh2[ty][tx] = b;
     __syncthreads();
-    if (ty != 0 || c >= C) return false;
-    a = 0.0; b = 0.0;
+    // fixed-shape pairwise tree over the lanes (the same order whatever the data)
 #pragma unroll
-    for (int k = 0; k < kFinLanes; k++) { a += sh1[k][tx]; b += sh2[k][tx]; }
-    *c_out = c; *s1 = a; *s2 = b;
+    for (int half = kFinLanes / 2; half >= 1; half >>= 1) {
+        if (ty < half) {
+            sh1[ty][tx] += sh1[ty + half][tx];
+            sh2[ty][tx] += sh2[ty + half][tx];
+        }
+        __syncthreads();
+    }
+    if (ty != 0 || c >= C) return false;
+    *c_out = c; *s1 = sh1[0][tx]; *s2 = sh2[0][tx];
     return true;
 }
 inline int fin_grid(int C) { return (C + kFinCols - 1) / kFinCols; }
