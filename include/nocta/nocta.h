@@ -10,8 +10,8 @@
  *
  * Differences a caller can observe:
  *   - Arithmetic runs on the CUDA device only.  nc_init() makes CUDA the default device, so
- *     tensors created afterwards live in device memory; an op given a CPU-resident tensor
- *     fails with NC_ERR_DEVICE instead of computing on the host.
+ *     tensors created afterwards live in device memory; an op given a CPU-resident tensor moves it
+ *     to the device first (NC_ERR_DEVICE when there is no GPU): nothing is ever computed on the host.
  *   - Element accessors (the nc_tensor_get / nc_tensor_set family) work on device tensors by copying the one element.
  *   - 4-D activations produced by conv / batchnorm / relu / maxpool on the device are stored
  *     channels-last; their shape is still (N,C,H,W) and their strides say so.
@@ -256,6 +256,7 @@ void nc_mul_scalar_(nc_tensor* a, double s);
 nc_tensor* nc_matmul(nc_tensor* a, nc_tensor* b); /* 2-D f32 */
 nc_tensor* nc_relu(nc_tensor* x);
 nc_tensor* nc_gelu(nc_tensor* x);
+nc_tensor* nc_sigmoid(nc_tensor* x);
 nc_tensor* nc_softmax(nc_tensor* x, int dim);
 nc_tensor* nc_sum(nc_tensor* x, int axis, bool keepdim);
 nc_tensor* nc_sum_all(nc_tensor* x);
@@ -363,6 +364,14 @@ nc_tensor* nc_layernorm_forward_fn(nc_tensor* input, const size_t* normalized_sh
                                    nc_tensor* weight, nc_tensor* bias, double eps);
 /* new: dropout with a caller-supplied keep mask already scaled by 1/(1-p): y = x * mask */
 nc_tensor* nc_dropout_mask_fn(nc_tensor* x, nc_tensor* mask);
+/* the reference's dropout (nn/dropout.h): the keep mask is drawn with rand() on the host exactly as the reference draws it */
+nc_tensor* nc_dropout_fn(nc_tensor* x, double p, bool training);
+nc_module* nc_dropout(double p);
+/* nn/batchnorm.h: BatchNorm1d over (N, C) or (N, C, L) */
+nc_module* nc_batchnorm1d(size_t num_features);
+nc_module* nc_batchnorm1d_ex(nc_batchnorm2d_config config);
+nc_tensor* nc_batchnorm1d_forward_fn(nc_tensor* input, nc_tensor* running_mean, nc_tensor* running_var, nc_tensor* weight,
+                                     nc_tensor* bias, bool training, double momentum, double eps);
 
 /* ------------------------------------------------------------------ optimizers (the optim headers) */
 #define NC_MAX_OPTIM_PARAMS 256

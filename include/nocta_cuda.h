@@ -80,7 +80,8 @@ int   nc_cuda_event_synchronize(void* event);
 int   nc_cuda_last_status(void);
 const char* nc_cuda_last_message(void);
 void  nc_cuda_clear_status(void);
-/* new: math mode for contractions (NC_CUDA_MATH_*); returns the previous mode */
+/* new: math mode for contractions (NC_CUDA_MATH_*); returns the previous mode.  The initial mode is TF32, or the
+ * digit in the environment variable NOCTA_CUDA_MATH_MODE when the library is loaded. */
 int   nc_cuda_set_math_mode(int mode);
 int   nc_cuda_get_math_mode(void);
 /* new: operand conditioning for NC_CUDA_MATH_TF32.  While on, the activation / gradient kernels (relu, gelu,
@@ -141,6 +142,9 @@ void nc_cuda_relu_backward_f32(float* grad_in, const float* grad_out, const floa
 void nc_cuda_softmax_f32(float* out, const float* in, size_t batch, size_t dim);                         /* :58 */
 int nc_cuda_relu_f32_ex(float* out, const float* in, size_t n, void* stream);
 int nc_cuda_relu_backward_f32_ex(float* grad_in, const float* grad_out, const float* input, size_t n, void* stream);
+void nc_cuda_sigmoid_f32(float* out, const float* in, size_t n);                      /* :56 */
+int nc_cuda_sigmoid_f32_ex(float* out, const float* in, size_t n, void* stream);
+int nc_cuda_sigmoid_backward_f32_ex(float* grad_in, const float* grad_out, const float* input, size_t n, void* stream);
 int nc_cuda_softmax_f32_ex(float* out, const float* in, size_t batch, size_t dim, void* stream);
 /* new (the reference has GELU forward on the CPU only and no backward at all) */
 int nc_cuda_gelu_f32_ex(float* out, const float* in, size_t n, void* stream);

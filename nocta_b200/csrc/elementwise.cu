@@ -94,6 +94,11 @@ __device__ __forceinline__ float gelu_grad(float x) {
     float th = tanhf(u);
     return 0.5f * (1.f + th) + 0.5f * x * (1.f - th * th) * c * (1.f + 3.f * a * x * x);
 }
+// sigmoid and its derivative s * (1 - s) taken on the saved input (src/ops/activation.c:72-105, 312-340)
+struct SigmoidF { __device__ float operator()(float a, float) const { return 1.f / (1.f + expf(-a)); } };
+struct SigmoidBwdF {
+    __device__ float operator()(float dy, float x) const { const float sg = 1.f / (1.f + expf(-x)); return dy * sg * (1.f - sg); }
+};
 struct GeluF { __device__ float operator()(float a, float) const { return gelu_fwd(a); } };
 struct GeluBwdF { __device__ float operator()(float dy, float x) const { return dy * gelu_grad(x); } };
 
@@ -276,6 +281,13 @@ void nc_cuda_mul_scalar_f32(float* o, const float* a, float s, size_t n) { nc_cu
 void nc_cuda_add_broadcast_batch_f32(float* o, const float* a, const float* b, size_t t, int inner) {
     nc_cuda_add_broadcast_batch_f32_ex(o, a, b, t, inner, current_stream());
 }
+int nc_cuda_sigmoid_f32_ex(float* out, const float* in, size_t n, void* stream) {
+    return launch_ew<1>(out, in, nullptr, n, (cudaStream_t)stream, SigmoidF{}, "sigmoid", round_outputs());
+}
+int nc_cuda_sigmoid_backward_f32_ex(float* gi, const float* go, const float* input, size_t n, void* stream) {
+    return launch_ew<2>(gi, go, input, n, (cudaStream_t)stream, SigmoidBwdF{}, "sigmoid_backward", round_outputs());
+}
+void nc_cuda_sigmoid_f32(float* o, const float* in, size_t n) { nc_cuda_sigmoid_f32_ex(o, in, n, current_stream()); }
 void nc_cuda_relu_f32(float* o, const float* in, size_t n) { nc_cuda_relu_f32_ex(o, in, n, current_stream()); }
 void nc_cuda_relu_backward_f32(float* gi, const float* go, const float* in, size_t n) {
     nc_cuda_relu_backward_f32_ex(gi, go, in, n, current_stream());

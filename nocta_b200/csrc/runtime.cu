@@ -4,6 +4,7 @@
 #include "../../include/nocta_cuda.h"
 #include <stdarg.h>
 #include <string.h>
+#include <stdlib.h>
 
 namespace ncc {
 
@@ -11,7 +12,14 @@ static int g_status = NC_CUDA_OK;
 static char g_message[512] = {0};
 static cudaStream_t g_stream = nullptr;
 static int g_sm_count = 0;
-static int g_math_mode = NC_CUDA_MATH_TF32;
+// Default TF32; a program that cannot call nc_cuda_set_math_mode (one built against the reference's API only) can
+// choose through the environment: NOCTA_CUDA_MATH_MODE = 0 (TF32), 1 (TF32 rounded in the kernel), 2 (3xTF32), 3 (FP32).
+static int initial_math_mode() {
+    const char* e = getenv("NOCTA_CUDA_MATH_MODE");
+    if (e && e[0] >= '0' && e[0] <= '3' && e[1] == 0) return e[0] - '0';
+    return NC_CUDA_MATH_TF32;
+}
+static int g_math_mode = initial_math_mode();
 unsigned long long g_launches = 0;
 unsigned long long g_epoch = 0;
 

@@ -88,6 +88,9 @@ SIGNATURES = {
     "nc_cuda_softmax_f32": (None, [_p, _p, _z, _z]),
     "nc_cuda_relu_f32_ex": (_i, [_p, _p, _z, _p]),
     "nc_cuda_relu_backward_f32_ex": (_i, [_p, _p, _p, _z, _p]),
+    "nc_cuda_sigmoid_f32": (None, [_p, _p, _z]),
+    "nc_cuda_sigmoid_f32_ex": (_i, [_p, _p, _z, _p]),
+    "nc_cuda_sigmoid_backward_f32_ex": (_i, [_p, _p, _p, _z, _p]),
     "nc_cuda_softmax_f32_ex": (_i, [_p, _p, _z, _z, _p]),
     "nc_cuda_gelu_f32_ex": (_i, [_p, _p, _z, _p]),
     "nc_cuda_gelu_backward_f32_ex": (_i, [_p, _p, _p, _z, _p]),

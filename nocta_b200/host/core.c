@@ -265,8 +265,15 @@ bool nci_need_cuda_f32(const nc_tensor* t, const char* op) {
     if (!t) { NC_SET_ERROR(NC_ERR_NULL_PTR, "%s: null tensor", op); return false; }
     if (t->dtype != NC_F32) { NC_SET_ERROR(NC_ERR_INVALID_DTYPE, "%s: float32 tensor required", op); return false; }
     if (!nci_on_cuda(t)) {
-        NC_SET_ERROR(NC_ERR_DEVICE, "%s: tensor is not on the CUDA device (this library has no CPU compute path)", op);
-        return false;
+        /* a host-resident operand (created before nc_init, or by a program that never calls it) is moved to the
+         * device, storage and all its views with it; there is no host compute path to fall back to */
+        static int have_gpu = -1;
+        if (have_gpu < 0) have_gpu = nc_cuda_available() ? 1 : 0;
+        if (have_gpu && t->storage) nc_tensor_to_device((nc_tensor*)t, NC_DEVICE_CUDA);
+        if (!nci_on_cuda(t)) {
+            NC_SET_ERROR(NC_ERR_DEVICE, "%s: tensor is not on the CUDA device (this library has no CPU compute path)", op);
+            return false;
+        }
     }
     return true;
 }
@@ -453,8 +460,11 @@ nc_tensor* nc_tensor_arange(double start, double end, double step, nc_dtype dtyp
     return h;
 }
 
-/* xorshift128+ with an explicit seed (the reference seeds from time(): src/core/tensor.c:21-47) */
-static uint64_t g_rng[2] = {0x9E3779B97F4A7C15ull, 0xD1B54A32D192ED03ull};
+/* Random tensors follow the reference's generator (src/core/tensor.c:21-47): xorshift128+ with shifts 23 / 17 / 26,
+ * uniform = top 53 bits / 2^53, normal = sqrt(-2 ln(u1 + 1e-10)) cos(2 pi u2); unseeded, the state starts from
+ * time(NULL) as there, so a program run at the same second draws the same values from either library.
+ * nc_manual_seed (new) fixes the state instead. */
+static uint64_t g_rng[2] = {0, 0};
 void nc_manual_seed(uint64_t seed) {
     uint64_t z = seed + 0x9E3779B97F4A7C15ull;
     for (int i = 0; i < 2; i++) {
@@ -467,18 +477,21 @@ void nc_manual_seed(uint64_t seed) {
     if (!g_rng[0] && !g_rng[1]) g_rng[0] = 1;
 }
 static uint64_t rng_next(void) {
-    uint64_t s1 = g_rng[0];
-    const uint64_t s0 = g_rng[1];
-    g_rng[0] = s0;
-    s1 ^= s1 << 23;
-    g_rng[1] = s1 ^ s0 ^ (s1 >> 18) ^ (s0 >> 5);
-    return g_rng[1] + s0;
+    if (g_rng[0] == 0) {
+        g_rng[0] = (uint64_t)time(NULL);
+        g_rng[1] = g_rng[0] ^ 0x5DEECE66DULL;
+    }
+    uint64_t x = g_rng[0];
+    const uint64_t y = g_rng[1];
+    g_rng[0] = y;
+    x ^= x << 23;
+    g_rng[1] = x ^ y ^ (x >> 17) ^ (y >> 26);
+    return g_rng[1] + y;
 }
 static double rng_uniform(void) { return (double)(rng_next() >> 11) * (1.0 / 9007199254740992.0); }
 static double rng_normal(void) {
-    double u1 = rng_uniform(), u2 = rng_uniform();
-    if (u1 < 1e-300) u1 = 1e-300;
-    return sqrt(-2.0 * log(u1)) * cos(6.283185307179586 * u2);
+    const double u1 = rng_uniform(), u2 = rng_uniform();
+    return sqrt(-2.0 * log(u1 + 1e-10)) * cos(2.0 * 3.14159265358979323846 * u2);
 }
 static nc_tensor* random_tensor(const size_t* shape, size_t ndim, nc_dtype dtype, bool normal) {
     nc_tensor* h = nci_empty_on(shape, ndim, dtype, NC_DEVICE_CPU);

@@ -10,6 +10,7 @@
  * to dense NCHW order so the Linear weights keep the reference's (C,H,W) column order.
  */
 #include "internal.h"
+#include <stdlib.h>
 #include <math.h>
 
 static nc_tensor** grad_array(size_t n) { return nc_calloc(n, sizeof(nc_tensor*)); }
@@ -649,6 +650,99 @@ nc_module* nc_batchnorm2d(size_t num_features) {
     c.num_features = num_features;
     return nc_batchnorm2d_ex(c);
 }
+/* ------------------------------------------------------------------ BatchNorm1d (src/nn/batchnorm.c:705-860)
+ * input (N, C) or (N, C, L): statistics per channel over N (and L).  (N, C) row-major is the channels-last case of the
+ * 2-D kernels with one pixel per row; (N, C, L) is their channel-major case.
+ * saved: [x (dense), gamma, batch_mean, batch_var, host scalars (eps, layout, N, C, L)] */
+static nc_tensor** bwd_batchnorm1d(nc_tensor* g, nc_tensor** saved, size_t n) {
+    (void)n;
+    nc_tensor** out = grad_array(3);
+    if (!out) return NULL;
+    nc_tensor* x = saved[0];
+    nc_tensor* gamma = saved[1];
+    const double eps = nc_tensor_get_flat(saved[4], 0);
+    const int layout = (int)nc_tensor_get_flat(saved[4], 1);
+    const int N = (int)nc_tensor_get_flat(saved[4], 2), C = (int)nc_tensor_get_flat(saved[4], 3), L = (int)nc_tensor_get_flat(saved[4], 4);
+    nc_tensor* gd = g->is_contiguous ? g : nc_tensor_contiguous(g);
+    if (!gd) return out;
+    nci_round_outputs(true);
+    out[0] = nci_empty_on(x->shape, x->ndim, NC_F32, NC_DEVICE_CUDA);
+    if (gamma) { out[1] = nci_param_grad_out(1, gamma); out[2] = nci_param_grad_out(2, gamma); }
+    if (out[0] && (!gamma || (out[1] && out[2])))
+        nci_ok(nc_cuda_batchnorm_backward_f32_ex(nci_fptr(out[0]), gamma ? nci_fptr(out[1]) : NULL, gamma ? nci_fptr(out[2]) : NULL, nci_fptr(gd),
+                                                 nci_fptr(x), gamma ? nci_fptr(gamma) : NULL, nci_fptr(saved[2]), nci_fptr(saved[3]), NULL, NULL, 0,
+                                                 N, C, L, eps, layout, nci_stream()), "batchnorm1d backward");
+    if (gd != g) nc_tensor_free(gd);
+    return out;
+}
+nc_tensor* nc_batchnorm1d_forward_fn(nc_tensor* input, nc_tensor* running_mean, nc_tensor* running_var, nc_tensor* weight,
+                                     nc_tensor* bias, bool training, double momentum, double eps) {
+    if (!input || (input->ndim != 2 && input->ndim != 3)) { NC_SET_ERROR(NC_ERR_SHAPE_MISMATCH, "BatchNorm1D requires (N,C) or (N,C,L) input"); return NULL; }
+    if (!nci_need_cuda_f32(input, "batchnorm1d")) return NULL;
+    nc_tensor* opt[4] = {running_mean, running_var, weight, bias};
+    for (int i = 0; i < 4; i++)
+        if (opt[i] && (!nci_need_cuda_f32(opt[i], "batchnorm1d") || opt[i]->numel != input->shape[1])) {
+            if (nc_last_error == NC_OK) NC_SET_ERROR(NC_ERR_SHAPE_MISMATCH, "batchnorm1d: per-channel tensor of the wrong size");
+            return NULL;
+        }
+    nc_tensor* x = input->is_contiguous ? input : nc_tensor_contiguous(input);
+    if (!x) return NULL;
+    const int N = (int)x->shape[0], C = (int)x->shape[1], L = x->ndim == 3 ? (int)x->shape[2] : 1;
+    const int layout = x->ndim == 2 ? 1 : 0;
+    size_t cs = (size_t)C;
+    nci_round_outputs(true);
+    nc_tensor* y = nci_empty_on(x->shape, x->ndim, NC_F32, NC_DEVICE_CUDA);
+    nc_tensor* mean = nci_empty_on(&cs, 1, NC_F32, NC_DEVICE_CUDA);
+    nc_tensor* var = nci_empty_on(&cs, 1, NC_F32, NC_DEVICE_CUDA);
+    bool ok = y && mean && var &&
+              nci_ok(nc_cuda_batchnorm_forward_f32_ex(nci_fptr(y), nci_fptr(x), weight ? nci_fptr(weight) : NULL, bias ? nci_fptr(bias) : NULL,
+                                                      running_mean ? nci_fptr(running_mean) : NULL, running_var ? nci_fptr(running_var) : NULL,
+                                                      nci_fptr(mean), nci_fptr(var), N, C, L, momentum, eps, training ? 1 : 0, layout, 0,
+                                                      nci_stream()), "batchnorm1d");
+    bool wired = false;
+    if (ok && any_grad(input, weight, bias)) {
+        nc_node* nd = nci_attach(y, "batchnorm1d", bwd_batchnorm1d);
+        if (nd) {
+            nc_node_add_input(nd, input);
+            if (weight) nc_node_add_input(nd, weight);
+            if (bias) nc_node_add_input(nd, bias);
+            if (x != input) { nc_node_save_owned_tensor(nd, x); x = input; } else nc_node_save_tensor(nd, input);
+            nc_node_save_tensor(nd, weight);
+            nc_node_save_owned_tensor(nd, mean);
+            nc_node_save_owned_tensor(nd, var);
+            size_t five = 5;
+            nc_tensor* hp = nci_empty_on(&five, 1, NC_F64, NC_DEVICE_CPU);
+            if (hp) {
+                nc_tensor_set_flat(hp, 0, eps); nc_tensor_set_flat(hp, 1, (double)layout); nc_tensor_set_flat(hp, 2, (double)N);
+                nc_tensor_set_flat(hp, 3, (double)C); nc_tensor_set_flat(hp, 4, (double)L);
+            }
+            nc_node_save_owned_tensor(nd, hp);
+            wired = true;
+        }
+    }
+    if (!wired) { nc_tensor_free(mean); nc_tensor_free(var); }
+    if (x != input) nc_tensor_free(x);
+    if (!ok) { nc_tensor_free(y); return NULL; }
+    return y;
+}
+static nc_tensor* bn1d_module_forward(nc_module* self, nc_tensor* x) {
+    bn_cfg* c = self->extra;
+    if (self->training) c->batches++;
+    return nc_batchnorm1d_forward_fn(x, nc_module_get_param(self, "running_mean"), nc_module_get_param(self, "running_var"),
+                                     nc_module_get_param(self, "weight"), nc_module_get_param(self, "bias"), self->training, c->momentum,
+                                     c->eps);
+}
+nc_module* nc_batchnorm1d_ex(nc_batchnorm2d_config config) {
+    nc_module* m = nc_batchnorm2d_ex(config); /* same parameters and buffers */
+    if (m) { snprintf(m->name, sizeof(m->name), "BatchNorm1D"); m->forward = bn1d_module_forward; }
+    return m;
+}
+nc_module* nc_batchnorm1d(size_t num_features) {
+    nc_batchnorm2d_config c = NC_BATCHNORM2D_DEFAULT;
+    c.num_features = num_features;
+    return nc_batchnorm1d_ex(c);
+}
+
 nc_tensor* nc_batchnorm2d_weight(nc_module* bn) { return nc_module_get_param(bn, "weight"); }
 nc_tensor* nc_batchnorm2d_bias(nc_module* bn) { return nc_module_get_param(bn, "bias"); }
 nc_tensor* nc_batchnorm2d_running_mean(nc_module* bn) { return nc_module_get_param(bn, "running_mean"); }
@@ -744,3 +838,37 @@ nc_module* nc_layernorm(const size_t* normalized_shape, size_t ndim) {
 
 /* ------------------------------------------------------------------ dropout with a supplied mask */
 nc_tensor* nc_dropout_mask_fn(nc_tensor* x, nc_tensor* mask) { return nc_mul(x, mask); }
+/* Dropout with the reference's mask rule (src/nn/dropout.c:52-97): element i (logical order) is kept when
+ * rand() / RAND_MAX > p and scaled by 1 / (1 - p).  The mask is drawn on the host from the C library generator,
+ * exactly as the reference draws it, so the same srand() seed gives the same mask; it is uploaded already scaled and
+ * the device does y = x * mask (the gradient is g * mask).  Evaluation mode, p == 0 and an invalid p return a copy. */
+nc_tensor* nc_dropout_fn(nc_tensor* x, double p, bool training) {
+    if (!x) { NC_SET_ERROR(NC_ERR_NULL_PTR, "dropout: null input"); return NULL; }
+    if (!training || p == 0.0 || p < 0.0 || p >= 1.0) return nc_tensor_clone(x);
+    if (!nci_need_cuda_f32(x, "dropout")) return NULL;
+    const float scale = (float)(1.0 / (1.0 - p));
+    float* h = nc_alloc(sizeof(float) * (x->numel ? x->numel : 1));
+    if (!h) return NULL;
+    for (size_t i = 0; i < x->numel; i++) h[i] = ((double)rand() / RAND_MAX > p) ? scale : 0.f;
+    nc_device_type dev = nc_get_default_device();
+    nc_set_default_device(NC_DEVICE_CUDA);
+    nc_tensor* mask = nc_tensor_from_data(h, x->shape, x->ndim, NC_F32);
+    nc_set_default_device(dev);
+    nc_free(h);
+    if (!mask) return NULL;
+    nc_tensor* y = nc_mul(x, mask);
+    /* with a graph the multiply node needs the mask in backward: hand it over; else it is done */
+    if (y && y->grad_fn) nc_node_save_owned_tensor(y->grad_fn, mask);
+    else nc_tensor_free(mask);
+    return y;
+}
+typedef struct { double p; } dropout_cfg;
+static nc_tensor* dropout_module_forward(nc_module* self, nc_tensor* x) { return nc_dropout_fn(x, ((dropout_cfg*)self->extra)->p, self->training); }
+nc_module* nc_dropout(double p) {
+    nc_module* m = nc_module_create("Dropout");
+    dropout_cfg* cfg = m ? nc_alloc(sizeof(*cfg)) : NULL;
+    if (!cfg) { nc_module_free(m); return NULL; }
+    cfg->p = p;
+    m->extra = cfg; m->free_extra = nc_free; m->forward = dropout_module_forward;
+    return m;
+}

@@ -18,9 +18,15 @@ static nc_tensor* operand_like(nc_tensor* t, const nc_tensor* like) { return nci
 
 /* ------------------------------------------------------------------ elementwise binary */
 /* shapes equal -> plain; b is 1-D of length a.shape[last] -> row broadcast (bias add) */
+/* b is one row of a: its last dimension equals a's and every other dimension of b is 1 ((8), (1, 8), (1, 1, 8) ...) */
+static bool is_row_of(const nc_tensor* a, const nc_tensor* b) {
+    if (a->ndim < 1 || b->ndim < 1 || b->ndim > a->ndim || !b->is_contiguous) return false;
+    if (b->shape[b->ndim - 1] != a->shape[a->ndim - 1] || b->numel != b->shape[b->ndim - 1]) return false;
+    return true;
+}
 static int classify(const nc_tensor* a, const nc_tensor* b) {
     if (nc_tensor_shape_eq(a, b)) return 0;
-    if (b->ndim == 1 && a->ndim >= 1 && b->shape[0] == a->shape[a->ndim - 1] && a->is_contiguous) return 1;
+    if (is_row_of(a, b) && a->is_contiguous) return 1;
     if (b->numel == 1) return 2;
     return -1;
 }
@@ -34,12 +40,19 @@ static nc_tensor** bwd_add(nc_tensor* g, nc_tensor** saved, size_t n) {
     if (a->requires_grad) out[0] = nci_alias(g);
     if (b->requires_grad) {
         if (nc_tensor_shape_eq(a, b)) out[1] = nci_alias(g);
-        else { /* reduce over the broadcast rows: column sums (src/ops/arithmetic.c:53-127) */
+        else {
+            /* the reference's reduce_grad_to_shape (src/ops/arithmetic.c:53-127): a 1-D operand (bias) gets the column
+             * sums, a one-element operand the sum of everything, and any other broadcast operand (e.g. a (1, C)
+             * matrix) gets the FIRST numel elements of the gradient, i.e. its first row only.  The last rule is
+             * reproduced as it is so that programs written against the reference train identically. */
             nc_tensor* gc = nc_tensor_contiguous(g);
             out[1] = nci_empty_on(b->shape, b->ndim, NC_F32, NC_DEVICE_CUDA);
             if (gc && out[1]) {
                 size_t cols = b->numel, rows = g->numel / (cols ? cols : 1);
-                nci_ok(nc_cuda_sum_axis_f32_ex(nci_fptr(out[1]), nci_fptr(gc), 1, rows, cols, nci_stream()), "add backward");
+                if (b->ndim == 1 || b->numel == 1)
+                    nci_ok(nc_cuda_sum_axis_f32_ex(nci_fptr(out[1]), nci_fptr(gc), 1, rows, cols, nci_stream()), "add backward");
+                else
+                    nc_cuda_memcpy_d2d(nci_dptr(out[1]), nci_dptr(gc), b->numel * sizeof(float));
             }
             if (gc && gc != g) nc_tensor_free(gc);
         }
@@ -240,6 +253,19 @@ static nc_tensor** bwd_gelu(nc_tensor* g, nc_tensor** saved, size_t n) {
     if (gd != g) nc_tensor_free(gd);
     return out;
 }
+static nc_tensor** bwd_sigmoid(nc_tensor* g, nc_tensor** saved, size_t n) {
+    (void)n;
+    nc_tensor** out = grad_array(1);
+    if (!out) return NULL;
+    nc_tensor* x = saved[0];
+    nc_tensor* gd = operand_like(g, x);
+    if (!gd) return out;
+    out[0] = nci_empty_like(x);
+    nci_round_outputs(true);
+    if (out[0]) nci_ok(nc_cuda_sigmoid_backward_f32_ex(nci_fptr(out[0]), nci_fptr(gd), nci_fptr(x), x->numel, nci_stream()), "sigmoid backward");
+    if (gd != g) nc_tensor_free(gd);
+    return out;
+}
 typedef int (*unary_kernel)(float*, const float*, size_t, void*);
 static nc_tensor* unary(nc_tensor* x, unary_kernel k, const char* name, nc_backward_fn bwd) {
     if (!nci_need_cuda_f32(x, name)) return NULL;
@@ -261,6 +287,7 @@ static nc_tensor* unary(nc_tensor* x, unary_kernel k, const char* name, nc_backw
 }
 nc_tensor* nc_relu(nc_tensor* x) { return unary(x, nc_cuda_relu_f32_ex, "relu", bwd_relu); }
 nc_tensor* nc_gelu(nc_tensor* x) { return unary(x, nc_cuda_gelu_f32_ex, "gelu", bwd_gelu); }
+nc_tensor* nc_sigmoid(nc_tensor* x) { return unary(x, nc_cuda_sigmoid_f32_ex, "sigmoid", bwd_sigmoid); }
 
 nc_tensor* nc_softmax(nc_tensor* x, int dim) {
     if (!nci_need_cuda_f32(x, "softmax")) return NULL;

@@ -27,6 +27,13 @@ def build(reference_root: Path = REFERENCE_ROOT) -> bool:
     return REF_SO.exists()
 
 
+def build_apps(reference_root: Path = REFERENCE_ROOT) -> list:
+    """Compile the reference's example programs against this repository's libraries (oracle/_ref/apps/)."""
+    if (reference_root / "examples" / "xor.c").exists():
+        subprocess.run(["make", "-C", str(HERE), f"REF={reference_root}", "apps"], check=True, capture_output=True)
+    return sorted((HERE / "_ref" / "apps").glob("*")) if (HERE / "_ref" / "apps").exists() else []
+
+
 def available() -> bool:
     return REF_SO.exists()
 
