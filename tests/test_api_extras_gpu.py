@@ -146,10 +146,10 @@ def run_app(name, timeout=300):
 
 
 def test_reference_example_xor_trains():
-    """The program seeds its weights from the clock.  Most seeds reach the reference's final loss (about 9e-5); some
-    stop on a plateau at 0.125 with this library (observed 1 run in 4) although the reference itself converged in 24 of
-    24 runs and single-step gradients of this graph are identical (test_xor_graph_matches_reference), so the test asks
-    for convergence within three attempts and for a falling loss every time."""
+    """The program seeds its weights from the clock, and the optimisation (a ReLU network at learning rate 1) stops on
+    a plateau for some seeds on either library: test_xor_trajectory_matches_reference follows both from identical
+    weights and sees the same plateau on both.  So the test asks for convergence within three attempts (three clock
+    seconds) and for a falling loss every time."""
     import time
     best = None
     for attempt in range(3):
@@ -214,3 +214,47 @@ def test_xor_graph_matches_reference(both):
         if max(emax, el2) > TOL:
             bad.append((n, emax, el2, got.ravel()[:8], exp.ravel()[:8]))
     assert not bad, bad
+
+
+def test_xor_trajectory_matches_reference(both):
+    """The xor example's whole loop (zero_grad, forward, backward, w -= grad through get_flat/set_flat, biases starting
+    at exactly 0 so that row 0 sits on the ReLU boundary) from identical weights on both libraries.  The loss follows
+    the reference's for hundreds of steps; a pre-activation within rounding of 0 may flip a ReLU on one side only, so
+    the bound on the loss is loose (1 %) where the single-step test is tight.  Seed 7 stops on the plateau at 0.25 on
+    both libraries."""
+    from nocta_b200 import capi
+    X = np.array([[0, 0], [0, 1], [1, 0], [1, 1]], np.float32)
+    Y = np.array([[0], [1], [1], [0]], np.float32)
+    for r in both:
+        r.api.lib.nc_tensor_set_flat.restype = None
+        r.api.lib.nc_tensor_set_flat.argtypes = [capi.TensorP, C.c_size_t, C.c_double]
+    for seed, steps in ((0, 300), (3, 300), (7, 300)):
+        rng = np.random.default_rng(seed)
+        init = [(rng.standard_normal((2, 8)) * 0.5).astype(np.float32), np.zeros((1, 8), np.float32),
+                (rng.standard_normal((8, 1)) * 0.5).astype(np.float32), np.zeros((1, 1), np.float32)]
+        curves = []
+        for r in both:
+            a = r.api
+            tX, tY = r.tensor(X), r.tensor(Y)
+            p = [r.tensor(v, True) for v in init]
+            curve = []
+            for _ in range(steps):
+                for t in p:
+                    a.nc_tensor_zero_grad_(t)
+                h = a.nc_relu(a.nc_add(a.nc_matmul(tX, p[0]), p[1]))
+                pred = a.lib.nc_sigmoid(a.nc_add(a.nc_matmul(h, p[2]), p[3]))
+                diff = a.lib.nc_sub(pred, tY)
+                loss = a.lib.nc_mean_all(a.nc_mul(diff, diff))
+                assert a.nc_backward_scalar(loss) == 0
+                curve.append(a.nc_tensor_get_flat(loss, 0))
+                for t in p:
+                    g = a.grad_numpy(t).ravel()
+                    for i in range(g.size):
+                        a.lib.nc_tensor_set_flat(t, i, a.nc_tensor_get_flat(t, i) - float(g[i]))
+            curves.append(np.array(curve))
+        ours, theirs = curves
+        assert np.all(np.isfinite(ours))
+        assert np.abs(ours[:50] - theirs[:50]).max() <= 1e-5, (seed, np.abs(ours[:50] - theirs[:50]).max())
+        assert np.abs(ours - theirs).max() <= 1e-2 * max(theirs.max(), 1e-3), (seed, ours[-1], theirs[-1])
+        if seed == 7:
+            assert abs(ours[-1] - 0.25) < 1e-3 and abs(theirs[-1] - 0.25) < 1e-3
