@@ -87,10 +87,10 @@ struct TileGeo {
     static constexpr int PG = 256 / CG;     // 4-pixel groups per CTA
     static constexpr int TR = PG / (TW / 4);  // output rows per CTA
 };
-template <int COUT>
+template <int COUT, bool STAT>
 __global__ void __launch_bounds__(256, 4) fwd_tile_kernel(float* __restrict__ y, const float* __restrict__ in,
                                                        const float* __restrict__ w, const float* __restrict__ bias, Geo g,
-                                                       int tiles_h, int tiles_w, int ntiles) {
+                                                       int tiles_h, int tiles_w, int ntiles, double* __restrict__ stat) {
     using T = TileGeo<COUT>;
     constexpr int CG = T::CG, TR = T::TR, ROWS = TR + 2;
     __shared__ __align__(16) float ws[K * COUT];
@@ -101,6 +101,11 @@ __global__ void __launch_bounds__(256, 4) fwd_tile_kernel(float* __restrict__ y,
         ws[i] = w[co * K + k];
     }
     for (int i = threadIdx.x; i < COUT; i += 256) bs[i] = bias ? bias[i] : 0.f;
+    // per-channel sum and sum of squares of this CTA's outputs, one private row per warp (no atomics: the result
+    // does not depend on the order in which warps run)
+    __shared__ float ssum[STAT ? 8 : 1][STAT ? 2 * COUT : 1];
+    if (STAT)
+        for (int i = threadIdx.x; i < 8 * 2 * COUT; i += 256) (&ssum[0][0])[i] = 0.f;
     const int cg = threadIdx.x % CG, pg = threadIdx.x / CG;
     const int prow = pg / (TW / 4), pcol = (pg % (TW / 4)) * 4;
     const float* wlo = ws + cg * 4;
@@ -166,15 +171,65 @@ __global__ void __launch_bounds__(256, 4) fwd_tile_kernel(float* __restrict__ y,
                 }
             }
         }
+        if (STAT) {
+            // The thread's 4 pixels, then the lanes of the warp that own the same channels (same lane % CG), then one
+            // add per channel into the warp's row of shared memory.  Pixels outside the image count for nothing.
+            static_assert(CG <= 16 && 32 % CG == 0, "lanes with equal lane % CG own the same channels");
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                float sv = 0.f, qv = 0.f;
+#pragma unroll
+                for (int p = 0; p < 4; p++) {
+                    const bool in_img = ho < g.Ho && wo0 + pcol + p < g.Wo;
+                    const float o = in_img ? acc[p][c] : 0.f;
+                    sv += o;
+                    qv = fmaf(o, o, qv);
+                }
+#pragma unroll
+                for (int d = 16; d >= CG; d >>= 1) {
+                    sv += __shfl_xor_sync(0xffffffffu, sv, d);
+                    qv += __shfl_xor_sync(0xffffffffu, qv, d);
+                }
+                if ((threadIdx.x & 31) < CG) {
+                    const int ch = (c < 4 ? 0 : COUT / 2) + cg * 4 + (c & 3);
+                    float* mine = ssum[threadIdx.x >> 5];
+                    mine[ch] += sv;
+                    mine[COUT + ch] += qv;
+                }
+            }
+        }
+    }
+    if (STAT) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < COUT; i += 256) {
+            double* sd = stat + ((size_t)blockIdx.x * COUT + i) * 2;
+            double a = 0.0, b = 0.0;
+#pragma unroll
+            for (int wp = 0; wp < 8; wp++) {
+                a += (double)ssum[wp][i];
+                b += (double)ssum[wp][COUT + i];
+            }
+            sd[0] = a;
+            sd[1] = b;
+        }
     }
 }
 
 template <int COUT>
-static void launch_fwd_tile(float* y, const float* x, const float* w, const float* bias, const Geo& g, cudaStream_t st) {
+static int launch_fwd_tile(float* y, const float* x, const float* w, const float* bias, const Geo& g, cudaStream_t st, double** stat_out) {
     const int tiles_h = (g.Ho + TileGeo<COUT>::TR - 1) / TileGeo<COUT>::TR, tiles_w = (g.Wo + TW - 1) / TW;
     const long long ntiles = (long long)g.N * tiles_h * tiles_w;
     const long long cap = (long long)ncc::sm_count() * 4;  // 4 CTAs of 64 registers x 256 threads fit an SM
-    fwd_tile_kernel<COUT><<<(int)(ntiles < cap ? ntiles : cap), 256, 0, st>>>(y, x, w, bias, g, tiles_h, tiles_w, (int)ntiles);
+    const int grid = (int)(ntiles < cap ? ntiles : cap);
+    // a BatchNorm that follows can take the per-channel sums from here instead of reading y again (one slab per CTA)
+    double* stat = ncc::conv_stats_wanted() ? ncc::conv_stats_buffer((size_t)grid, COUT, st) : nullptr;
+    if (stat) {
+        fwd_tile_kernel<COUT, true><<<grid, 256, 0, st>>>(y, x, w, bias, g, tiles_h, tiles_w, (int)ntiles, stat);
+    } else {
+        fwd_tile_kernel<COUT, false><<<grid, 256, 0, st>>>(y, x, w, bias, g, tiles_h, tiles_w, (int)ntiles, nullptr);
+    }
+    *stat_out = stat;
+    return grid;
 }
 
 // Tiled weight gradient for Cout in {32, 64}.  A CTA walks strips of 4 output rows x 64 columns; the
@@ -298,12 +353,16 @@ int forward(float* y, const float* x, const long long xs[4], const float* w, con
     if (!fits_int(N, H, W, xs, g.Ho, g.Wo)) return NC_CUDA_ERR_UNSUPPORTED;
     const int pixels = N * g.Ho * g.Wo;
     if (Cout == 16 || Cout == 32 || Cout == 64 || Cout == 128) {
-        if (Cout == 16) launch_fwd_tile<16>(y, x, w, bias, g, st);
-        else if (Cout == 32) launch_fwd_tile<32>(y, x, w, bias, g, st);
-        else if (Cout == 64) launch_fwd_tile<64>(y, x, w, bias, g, st);
-        else launch_fwd_tile<128>(y, x, w, bias, g, st);
+        double* stat = nullptr;
+        int slabs;
+        if (Cout == 16) slabs = launch_fwd_tile<16>(y, x, w, bias, g, st, &stat);
+        else if (Cout == 32) slabs = launch_fwd_tile<32>(y, x, w, bias, g, st, &stat);
+        else if (Cout == 64) slabs = launch_fwd_tile<64>(y, x, w, bias, g, st, &stat);
+        else slabs = launch_fwd_tile<128>(y, x, w, bias, g, st, &stat);
         NCC_COUNT_LAUNCH();
-        return ncc::launch_status("conv_first forward");
+        const int rc = ncc::launch_status("conv_first forward");
+        if (rc == NC_CUDA_OK && stat) ncc::conv_stats_publish(y, Cout, (long long)pixels, slabs, stat);
+        return rc;
     }
     const int ppb = 256 / (Cout / 16);
     long long need = ((long long)pixels + ppb - 1) / ppb;

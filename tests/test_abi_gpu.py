@@ -491,7 +491,8 @@ def test_fused_batchnorm_relu_maxpool_equals_the_separate_kernels(abi, shape, ro
     abi.nc_cuda_clear_status()
 
 
-@pytest.mark.parametrize("shape", [(8, 64, 32, 64), (4, 128, 16, 256), (6, 32, 32, 48)])
+@pytest.mark.parametrize("shape", [(8, 64, 32, 64), (4, 128, 16, 256), (6, 32, 32, 48),
+                                   (8, 3, 64, 64), (5, 3, 38, 32), (3, 3, 70, 128), (4, 3, 24, 16)])  # 3 channels: the first-layer kernel
 def test_batchnorm_takes_statistics_offered_by_the_convolution(abi, shape):
     """With nc_cuda_set_conv_stats(1) the forward convolution leaves per-channel sums behind and the BatchNorm
     called right after it uses them: same result (2e-6) as BatchNorm reading the tensor; the offer is void after
