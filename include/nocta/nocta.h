@@ -399,6 +399,44 @@ void nc_optimizer_set_grad_scale(nc_optimizer* opt, double scale);
  * returns its device address and length in floats, so data-parallel code can all-reduce one range */
 void* nc_optimizer_flatten_grads(nc_optimizer* opt, size_t* n_floats);
 
+/* ------------------------------------------------------------------ data parallel (new; the reference has no distributed layer)
+ * One process per GPU, every rank a full replica on its own shard of the batch.  The step of examples/mnist.c:471-508
+ * becomes: nc_optimizer_zero_grad, forward, loss, nc_backward_scalar, nc_dist_allreduce_grads, nc_optimizer_step.
+ *
+ * nc_bucket_plan is the host-only scheduling logic (usable without a GPU): the flat gradient arena is cut into
+ * contiguous buckets of about bucket_floats elements, built from the end of the arena because the backward sweep
+ * produces the last layer's gradients first.  on_ready(i) reports that entry i's gradient is final for this step and
+ * returns the index of a bucket that has just become complete (or -1); next_unfired() hands out, after the sweep, the
+ * buckets that did not complete by themselves; end_step() closes the step and returns how many notifications arrived
+ * after their bucket had already been handed out (0 in a static graph).  Which entries report, and how often (a shared
+ * weight reports once per use), is learned from the first step: that step sends nothing early. */
+typedef struct nc_bucket_plan nc_bucket_plan;
+nc_bucket_plan* nc_bucket_plan_create(size_t n_entries, const size_t* offsets, const size_t* numels, size_t arena_floats,
+                                      size_t bucket_floats);
+void nc_bucket_plan_free(nc_bucket_plan* p);
+size_t nc_bucket_plan_count(const nc_bucket_plan* p);
+void nc_bucket_plan_range(const nc_bucket_plan* p, size_t b, size_t* start, size_t* stop);
+void nc_bucket_plan_begin_step(nc_bucket_plan* p);
+int nc_bucket_plan_on_ready(nc_bucket_plan* p, size_t entry);
+int nc_bucket_plan_next_unfired(nc_bucket_plan* p);
+int nc_bucket_plan_end_step(nc_bucket_plan* p);
+
+/* nc_dist: the plan driven by the backward sweep (through nc_set_grad_ready_hook, which it takes over) over one NCCL
+ * communicator.  Rank 0 obtains 128 bytes from nc_dist_unique_id and hands them to every rank by any means; each rank,
+ * with its device current, calls nc_dist_init, which also moves the optimizer's gradients into one arena
+ * (nc_optimizer_flatten_grads) and sets the gradient scale to 1/world.  nc_dist_allreduce_grads queues whatever has
+ * not been sent, makes the compute stream wait for every bucket and returns without blocking the host; it returns an
+ * error (and relearns) if a gradient became final after its bucket had been sent.  NCCL is loaded at run time. */
+typedef struct nc_dist nc_dist;
+int nc_dist_unique_id(void* id128);
+nc_dist* nc_dist_init(int rank, int world, const void* id128, nc_optimizer* opt, size_t bucket_floats);
+int nc_dist_allreduce_grads(nc_dist* d);
+size_t nc_dist_num_buckets(const nc_dist* d);
+float* nc_dist_arena(const nc_dist* d, size_t* n_floats);
+/* device time between the end of the last backward sweep and the end of its last all-reduce; blocks the host */
+double nc_dist_exposed_ms(nc_dist* d);
+void nc_dist_free(nc_dist* d);
+
 /* ------------------------------------------------------------------ .ncta files (core/serialize.h)
  * Same byte layout as the reference (see nocta_b200/host/serialize.c); tensors may live on the CUDA device. */
 #define NC_FILE_MAGIC 0x4154434E /* "NCTA" */

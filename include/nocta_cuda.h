@@ -77,6 +77,9 @@ void  nc_cuda_event_destroy(void* event);
 int   nc_cuda_event_record(void* event, void* stream);
 int   nc_cuda_stream_wait_event(void* stream, void* event);
 int   nc_cuda_event_synchronize(void* event);
+/* new: an event that records time, and the device time between two such events that have completed */
+void* nc_cuda_event_create_timed(void);
+int   nc_cuda_event_elapsed_ms(void* start, void* stop, float* ms);
 int   nc_cuda_last_status(void);
 const char* nc_cuda_last_message(void);
 void  nc_cuda_clear_status(void);
@@ -101,11 +104,19 @@ unsigned int nc_cuda_device_error_word(void);
 unsigned long long nc_cuda_launch_count(void);
 void  nc_cuda_reset_launch_count(void);
 
-/* new: per-launch CUDA-event timing of the tensor-core contraction kernel on its launching stream.
- * begin() arms it; end() waits for the last timed launch and returns the summed kernel time, the
- * number of timed launches and their algorithmic FLOPs (2*M*N*K of each logical contraction). */
-int nc_cuda_tc_profile_begin(void);
-int nc_cuda_tc_profile_end(double* total_ms, unsigned long long* launches, double* flops);
+/* new: device timing per kernel family (CUDA events on the launching stream).  begin() arms it; every call of a profiled
+ * entry point is then bracketed by an event pair and filed under one category with its algorithmic work: FLOPs
+ * (2*M*N*K of the logical contraction) for the tensor-core families, which are timed per kernel launch (conv_fwd, conv_dx,
+ * conv_dw, gemm_nt = Linear forward, gemm_nn = Linear dX, gemm_tn = Linear dW, gemm_tt), and bytes that must cross HBM for
+ * the memory-bound ones, which are timed per outermost entry-point call (conv_first, batchnorm, layernorm, activation,
+ * elementwise, maxpool, loss, sgd, adam, reduce, relayout).  end() disarms and waits for the last timed call; read()
+ * then returns the summed device time, the number of timed calls and their summed work for one category.  The events cost
+ * a few microseconds of host time per call: measure throughput with profiling off. */
+int nc_cuda_profile_begin(void);
+int nc_cuda_profile_end(void);
+int nc_cuda_profile_categories(void);
+const char* nc_cuda_profile_category_name(int category);
+int nc_cuda_profile_read(int category, double* total_ms, unsigned long long* calls, double* work);
 
 /* ---------------- elementwise (reference: cuda_kernels.h:26-49, src/cuda/cuda_elementwise.cu) ---- */
 void nc_cuda_fill_f32(float* data, float value, size_t n);                        /* :26 */
@@ -293,9 +304,12 @@ int nc_cuda_cross_entropy_fused_f32_ex(float* loss, float* grad_logits, const fl
  * for callers that must not trigger a device allocation (all memory already handed to their own arena;
  * a collective in flight on another stream that an allocation's device-wide synchronisation would stall):
  * the partial sums live in a fixed array inside the library, so no allocating routine is ever called.
- * At most NC_CUDA_CE_STATIC_MAX_ROWS rows per call (more: NC_CUDA_ERR_ARG).  The first call on each
- * device resolves the array's address; make that call before beginning a stream capture.  All calls on a
- * device share the array: calls that may run concurrently race and must be serialised by the caller. */
+ * At most NC_CUDA_CE_STATIC_MAX_ROWS rows per call (more: status 5, "exceeds a stated fixed capacity", nothing is
+ * launched).  The first call on each device resolves the array's address; make that call before beginning a stream
+ * capture.  All calls on a device share the array: calls that may run concurrently race and must be serialised by the
+ * caller.  The resolved address is kept per device ordinal for the life of the process, so a process that resets a
+ * device must reload the library before calling again; `stream` must belong to the device that is current at the
+ * call (it is not checked). */
 #define NC_CUDA_CE_STATIC_MAX_ROWS 4096
 int nc_cuda_cross_entropy_fused_static_f32_ex(float* loss, float* grad_logits, const float* logits,
                                               const int64_t* targets, int N, int C, float grad_scale, void* stream);

@@ -82,6 +82,7 @@ _SIGS = {
     "nc_tensor_free": (None, [TensorP]),
     "nc_tensor_reshape": (TensorP, [TensorP, _szp, _sz]),
     "nc_tensor_contiguous": (TensorP, [TensorP]),
+    "nc_tensor_transpose": (TensorP, [TensorP, _sz, _sz]),
     "nc_tensor_requires_grad_": (None, [TensorP, C.c_bool]),
     "nc_tensor_zero_grad_": (None, [TensorP]),
     "nc_tensor_fill_": (None, [TensorP, C.c_double]),

@@ -55,9 +55,11 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 // rnd: round results to TF32 (activations / gradients in plain TF32 mode); never for fill / copy
 template <int NIN, class F>
-int launch_ew(float* out, const float* a, const float* b, size_t n, cudaStream_t st, F f, const char* what, bool rnd = false) {
+int launch_ew(float* out, const float* a, const float* b, size_t n, cudaStream_t st, F f, const char* what, bool rnd = false,
+              int category = PROF_ELEMENTWISE) {
     if (n == 0) return NC_CUDA_OK;
     NCC_REQUIRE(out && (NIN < 1 || a) && (NIN < 2 || b), "%s: null pointer", what);
+    ProfScope prof(category, 4.0 * (NIN + 1) * (double)n, st);
     bool vec = aligned16(out) && (NIN < 1 || aligned16(a)) && (NIN < 2 || aligned16(b));
     size_t n4 = vec ? n / 4 : 0;
     int grid = grid_for((long long)(vec ? (n + 3) / 4 : n), kThreads, 8);
@@ -175,6 +177,7 @@ int transpose_batched(float* dst, const float* src, int batch, int R, int Cc, bo
     if (batch <= 0 || R <= 0 || Cc <= 0) return NC_CUDA_OK;
     NCC_REQUIRE(dst && src, "transpose: null pointer");
     NCC_REQUIRE(batch <= 65535 && ceil_div(R, 32) <= 65535, "transpose: grid too large");
+    ProfScope prof(PROF_RELAYOUT, 8.0 * (double)batch * R * Cc, st);
     dim3 grid(ceil_div(Cc, 32), ceil_div(R, 32), batch);
     if (round) transpose_kernel<true><<<grid, 256, 0, st>>>(dst, src, R, Cc);
     else transpose_kernel<false><<<grid, 256, 0, st>>>(dst, src, R, Cc);
@@ -216,6 +219,7 @@ int nc_cuda_add_broadcast_batch_f32_ex(float* out, const float* a, const float* 
                                        void* stream) {
     if (total == 0) return NC_CUDA_OK;
     NCC_REQUIRE(out && a && b && inner > 0, "add_broadcast: bad argument");
+    ProfScope prof(PROF_ELEMENTWISE, 8.0 * (double)total, (cudaStream_t)stream);
     bias_rows_kernel<<<grid_for((long long)total, kThreads), kThreads, 0, (cudaStream_t)stream>>>(out, a, b, total, inner, round_outputs() ? 1 : 0);
     NCC_COUNT_LAUNCH();
     return launch_status("add_broadcast");
@@ -250,16 +254,16 @@ int nc_cuda_round_tf32_f32_ex(float* dst, const float* src, size_t n, void* stre
     return launch_ew<1>(dst, src, nullptr, n, (cudaStream_t)stream, RoundF{}, "round_tf32");
 }
 int nc_cuda_relu_f32_ex(float* out, const float* in, size_t n, void* stream) {
-    return launch_ew<1>(out, in, nullptr, n, (cudaStream_t)stream, ReluF{}, "relu", round_outputs());
+    return launch_ew<1>(out, in, nullptr, n, (cudaStream_t)stream, ReluF{}, "relu", round_outputs(), PROF_ACTIVATION);
 }
 int nc_cuda_relu_backward_f32_ex(float* gi, const float* go, const float* input, size_t n, void* stream) {
-    return launch_ew<2>(gi, go, input, n, (cudaStream_t)stream, ReluBwdF{}, "relu_backward", round_outputs());
+    return launch_ew<2>(gi, go, input, n, (cudaStream_t)stream, ReluBwdF{}, "relu_backward", round_outputs(), PROF_ACTIVATION);
 }
 int nc_cuda_gelu_f32_ex(float* out, const float* in, size_t n, void* stream) {
-    return launch_ew<1>(out, in, nullptr, n, (cudaStream_t)stream, GeluF{}, "gelu", round_outputs());
+    return launch_ew<1>(out, in, nullptr, n, (cudaStream_t)stream, GeluF{}, "gelu", round_outputs(), PROF_ACTIVATION);
 }
 int nc_cuda_gelu_backward_f32_ex(float* gi, const float* go, const float* input, size_t n, void* stream) {
-    return launch_ew<2>(gi, go, input, n, (cudaStream_t)stream, GeluBwdF{}, "gelu_backward", round_outputs());
+    return launch_ew<2>(gi, go, input, n, (cudaStream_t)stream, GeluBwdF{}, "gelu_backward", round_outputs(), PROF_ACTIVATION);
 }
 int nc_cuda_softmax_f32_ex(float* out, const float* in, size_t batch, size_t dim, void* stream) {
     if (batch == 0 || dim == 0) return NC_CUDA_OK;
@@ -282,10 +286,10 @@ void nc_cuda_add_broadcast_batch_f32(float* o, const float* a, const float* b, s
     nc_cuda_add_broadcast_batch_f32_ex(o, a, b, t, inner, current_stream());
 }
 int nc_cuda_sigmoid_f32_ex(float* out, const float* in, size_t n, void* stream) {
-    return launch_ew<1>(out, in, nullptr, n, (cudaStream_t)stream, SigmoidF{}, "sigmoid", round_outputs());
+    return launch_ew<1>(out, in, nullptr, n, (cudaStream_t)stream, SigmoidF{}, "sigmoid", round_outputs(), PROF_ACTIVATION);
 }
 int nc_cuda_sigmoid_backward_f32_ex(float* gi, const float* go, const float* input, size_t n, void* stream) {
-    return launch_ew<2>(gi, go, input, n, (cudaStream_t)stream, SigmoidBwdF{}, "sigmoid_backward", round_outputs());
+    return launch_ew<2>(gi, go, input, n, (cudaStream_t)stream, SigmoidBwdF{}, "sigmoid_backward", round_outputs(), PROF_ACTIVATION);
 }
 void nc_cuda_sigmoid_f32(float* o, const float* in, size_t n) { nc_cuda_sigmoid_f32_ex(o, in, n, current_stream()); }
 void nc_cuda_relu_f32(float* o, const float* in, size_t n) { nc_cuda_relu_f32_ex(o, in, n, current_stream()); }

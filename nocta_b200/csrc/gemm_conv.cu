@@ -205,6 +205,7 @@ int gemm_dispatch(float* C, int ldc, const float* A, int lda, bool a_mn, const f
     if (M <= 0 || N <= 0) return NC_CUDA_OK;
     NCC_REQUIRE(C && (K == 0 || (A && B)), "gemm: null pointer");
     if (tc_enabled() && K > 0) {
+        prof_set_role(a_mn ? (b_mn ? PROF_GEMM_TN : PROF_GEMM_TT) : (b_mn ? PROF_GEMM_NN : PROF_GEMM_NT));
         int rc = tc::gemm(C, ldc, A, lda, a_mn, B, ldb, b_mn, M, N, K, bias, alpha, beta, tc_mode(), st);
         if (rc != NC_CUDA_ERR_UNSUPPORTED) return rc;
     }
@@ -320,14 +321,12 @@ int nc_cuda_conv2d_forward_f32_ex(float* y, const size_t ys[4], const float* x, 
         if (!wp) return NC_CUDA_ERR_RUNTIME;
         rc = tc::pack_weights_fwd(wp, w, Cout, Cin, kH, kW, round_in_relayout() != 0, st);
         if (rc) return rc;
+        prof_set_role(PROF_CONV_FWD);
         rc = tc::conv_nhwc(y, x, wp, bias, N, H, W, Cin, Cout, kH, kW, pad, tc_mode(), st);
         if (rc != NC_CUDA_ERR_UNSUPPORTED) return rc;
     }
-    if (tc_enabled() && stride == 1 && is_nhwc(g.ys, Cout, g.Ho, g.Wo) && tc::conv_few_channels_ok(Cin, Cout, kH, kW, g.Ho, g.Wo, tc_mode())) {
-        rc = tc::conv_few_channels(y, x, g.xs, w, bias, N, H, W, Cin, Cout, kH, kW, pad, round_in_relayout() != 0, st);
-        if (rc != NC_CUDA_ERR_UNSUPPORTED) return rc;
-    }
     if (convfirst::eligible(Cin, kH, kW, stride, Cout) && is_nhwc(g.ys, Cout, g.Ho, g.Wo)) {
+        ProfScope prof(PROF_CONV_FIRST, 4.0 * ((double)N * g.Ho * g.Wo * Cout + (double)N * Cin * H * W), st);
         rc = convfirst::forward(y, x, g.xs, w, bias, N, H, W, Cout, pad, st);
         if (rc != NC_CUDA_ERR_UNSUPPORTED) return rc;
     }
@@ -351,6 +350,7 @@ int nc_cuda_conv2d_backward_input_f32_ex(float* dx, const size_t xs[4], const fl
         rc = tc::pack_weights_dx(wp, w, Cout, Cin, kH, kW, round_in_relayout() != 0, st);
         if (rc) return rc;
         // dx = conv(dy, flipped weights) with padding k-1-pad; roles of Cin and Cout swap
+        prof_set_role(PROF_CONV_DX);
         rc = tc::conv_nhwc(dx, dy, wp, nullptr, N, g.Ho, g.Wo, Cout, Cin, kH, kW, kH - 1 - pad, tc_mode(), st);
         if (rc != NC_CUDA_ERR_UNSUPPORTED) return rc;
     }
@@ -385,10 +385,12 @@ int nc_cuda_conv2d_backward_weight_f32_ex(float* dW, float* db, const float* dy,
     }
     if (!dW) return NC_CUDA_OK;
     if (tc_enabled() && stride == 1 && is_nhwc(g.xs, Cin, H, W) && is_nhwc(g.ys, Cout, g.Ho, g.Wo)) {
+        prof_set_role(PROF_CONV_DW);
         rc = tc::conv_dw_nhwc(dW, dy, x, N, H, W, Cin, Cout, kH, kW, pad, tc_mode(), st);
         if (rc != NC_CUDA_ERR_UNSUPPORTED) return rc;
     }
     if (convfirst::eligible(Cin, kH, kW, stride, Cout) && is_nhwc(g.ys, Cout, g.Ho, g.Wo)) {
+        ProfScope prof(PROF_CONV_FIRST, 4.0 * ((double)N * g.Ho * g.Wo * Cout + (double)N * Cin * H * W), st);
         rc = convfirst::weight_grad(dW, dy, x, g.xs, N, H, W, Cout, pad, st);
         if (rc != NC_CUDA_ERR_UNSUPPORTED) return rc;
     }

@@ -172,33 +172,66 @@ __global__ void __launch_bounds__(kThreads) sgd_multi_kernel(const __grid_consta
 }
 
 struct AdamArgs {
-    double lr, b1, b2, eps, wd, bc1, bc2, gscale;
+    double lr, b1, b2, eps, wd, inv_bc1, inv_bc2, gscale;
 };
 
-__device__ __forceinline__ void adam_element(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v, float* __restrict__ vmax,
-                                             const float* __restrict__ g, const AdamArgs& a, size_t i) {
-    double gi = (double)g[i] * a.gscale;
-    double pi = (double)p[i];
+// One element, following src/optim/adam.c:39-73: the moments are updated in double and stored as f32 like the CPU path.
+// The two bias-correction divisions are multiplications by reciprocals formed on the host, and the square root and the
+// final quotient are f32: their rounding (6e-8 relative) acts on an update of size lr, far below the f32 spacing of the
+// parameter it is added to, and keeps the kernel off the double-precision divide / square-root sequences.
+__device__ __forceinline__ void adam_math(float& p, float& m, float& v, float* vmax, float g, const AdamArgs& a) {
+    const double gi = (double)g * a.gscale;
+    double pi = (double)p;
     if (a.wd != 0.0) pi = pi - a.lr * a.wd * pi;
-    double mi = a.b1 * (double)m[i] + (1.0 - a.b1) * gi;
-    double vi = a.b2 * (double)v[i] + (1.0 - a.b2) * gi * gi;
-    m[i] = (float)mi;
-    v[i] = (float)vi;
-    double mh = mi / a.bc1, vh = vi / a.bc2;
+    const double mi = a.b1 * (double)m + (1.0 - a.b1) * gi;
+    const double vi = a.b2 * (double)v + (1.0 - a.b2) * gi * gi;
+    m = (float)mi;
+    v = (float)vi;
+    const double mh = mi * a.inv_bc1;
+    double vh = vi * a.inv_bc2;
     if (vmax) {
-        double vm = fmax((double)vmax[i], vh);
-        float vmf = (float)vm;
-        vmax[i] = vmf;
+        const float vmf = (float)fmax((double)*vmax, vh);
+        *vmax = vmf;
         vh = (double)vmf;
     }
-    p[i] = (float)(pi - a.lr * mh / (sqrt(vh) + a.eps));
+    const float step = (float)mh / (sqrtf((float)vh) + (float)a.eps);
+    p = (float)(pi - a.lr * (double)step);
+}
+__device__ __forceinline__ void adam_element(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v, float* __restrict__ vmax,
+                                             const float* __restrict__ g, const AdamArgs& a, size_t i) {
+    adam_math(p[i], m[i], v[i], vmax ? vmax + i : nullptr, g[i], a);
+}
+// Elements [begin, end) of one tensor by one block: float4 accesses when the four arrays allow it.
+__device__ __forceinline__ void adam_range(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v, float* __restrict__ vmax,
+                                           const float* __restrict__ g, const AdamArgs& a, size_t begin, size_t end, size_t first,
+                                           size_t stride) {
+    const bool vec = ((begin & 3) == 0) && !vmax &&
+                     (((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
+                        reinterpret_cast<uintptr_t>(g)) & 15u) == 0);
+    if (!vec) {
+        for (size_t i = begin + first; i < end; i += stride) adam_element(p, m, v, vmax, g, a, i);
+        return;
+    }
+    const size_t n4 = (end - begin) >> 2;
+    for (size_t q = first; q < n4; q += stride) {
+        const size_t i = begin + 4 * q;
+        float4 p4 = *reinterpret_cast<float4*>(p + i), m4 = *reinterpret_cast<float4*>(m + i), v4 = *reinterpret_cast<float4*>(v + i);
+        const float4 g4 = *reinterpret_cast<const float4*>(g + i);
+        adam_math(p4.x, m4.x, v4.x, nullptr, g4.x, a);
+        adam_math(p4.y, m4.y, v4.y, nullptr, g4.y, a);
+        adam_math(p4.z, m4.z, v4.z, nullptr, g4.z, a);
+        adam_math(p4.w, m4.w, v4.w, nullptr, g4.w, a);
+        *reinterpret_cast<float4*>(p + i) = p4;
+        *reinterpret_cast<float4*>(m + i) = m4;
+        *reinterpret_cast<float4*>(v + i) = v4;
+    }
+    for (size_t i = begin + 4 * n4 + first; i < end; i += stride) adam_element(p, m, v, vmax, g, a, i);
 }
 
 __global__ void __launch_bounds__(kThreads) adam_kernel(float* __restrict__ p, float* __restrict__ m,
                                                         float* __restrict__ v, float* __restrict__ vmax,
                                                         const float* __restrict__ g, AdamArgs a, size_t n) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) adam_element(p, m, v, vmax, g, a, i);
+    adam_range(p, m, v, vmax, g, a, 0, n, (size_t)blockIdx.x * blockDim.x + threadIdx.x, (size_t)gridDim.x * blockDim.x);
 }
 
 __global__ void __launch_bounds__(kThreads) adam_multi_kernel(const __grid_constant__ MultiTable t, AdamArgs a) {
@@ -206,7 +239,7 @@ __global__ void __launch_bounds__(kThreads) adam_multi_kernel(const __grid_const
     const size_t begin = (size_t)(blockIdx.x - t.first_block[k]) * kMultiChunk;
     size_t end = begin + kMultiChunk;
     if (end > t.n[k]) end = t.n[k];
-    for (size_t i = begin + threadIdx.x; i < end; i += kThreads) adam_element(t.p[k], t.s1[k], t.s2[k], t.s3[k], t.g[k], a, i);
+    adam_range(t.p[k], t.s1[k], t.s2[k], t.s3[k], t.g[k], a, begin, end, threadIdx.x, kThreads);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -277,12 +310,12 @@ int loss_scratch(LossScratch* ls, long long work, cudaStream_t st) {
     // layout: [ticket (16 B)] [partials]
     char* base = (char*)scratch(0, 16 + sizeof(double) * (size_t)blocks, st);
     if (!base) return NC_CUDA_ERR_RUNTIME;
-    static void* zeroed = nullptr;
-    if (zeroed != base) {  // (re)allocated: the ticket must start at zero
-        cudaError_t e = cudaMemsetAsync(base, 0, 16, st);
-        if (e != cudaSuccess) return set_status(NC_CUDA_ERR_RUNTIME, "loss scratch memset failed");
-        zeroed = base;
-    }
+    // The ticket must start at zero.  A kernel resets it when it ends, but not after a failed or aborted launch, and a
+    // regrown block starts with arbitrary contents: clear it in stream order on every call (calls on different streams
+    // share this one block and must not overlap).
+    cudaError_t e = cudaMemsetAsync(base, 0, 16, st);
+    if (e != cudaSuccess) return set_status(NC_CUDA_ERR_RUNTIME, "loss scratch memset failed");
+    ++g_epoch;
     ls->ticket = (unsigned int*)base;
     ls->partial = (double*)(base + 16);
     ls->blocks = blocks;
@@ -331,6 +364,7 @@ int nc_cuda_cross_entropy_fused_f32_ex(float* loss, float* grad, const float* lo
                                        int N, int C, float grad_scale, void* stream) {
     NCC_REQUIRE(logits && targets && N > 0 && C > 0, "cross_entropy: bad argument");
     cudaStream_t st = (cudaStream_t)stream;
+    ProfScope prof(PROF_LOSS, (grad ? 8.0 : 4.0) * (double)N * C + 8.0 * N, st);
     LossScratch ls;
     int rc = loss_scratch(&ls, (long long)N * 32, st);
     if (rc) return rc;
@@ -344,6 +378,7 @@ int nc_cuda_mse_fused_f32_ex(float* loss, float* gp, float* gt, const float* pre
                              float grad_scale, void* stream) {
     NCC_REQUIRE(pred && target && n > 0, "mse: bad argument");
     cudaStream_t st = (cudaStream_t)stream;
+    ProfScope prof(PROF_LOSS, (8.0 + (gp ? 4.0 : 0.0) + (gt ? 4.0 : 0.0)) * (double)n, st);
     LossScratch ls;
     int rc = loss_scratch(&ls, (long long)n, st);
     if (rc) return rc;
@@ -368,6 +403,7 @@ int nc_cuda_sgd_update_f32_ex(float* param, float* velocity, float* grad, double
     SgdArgs a{lr, momentum, dampening, weight_decay, grad_scale, nesterov, first_step, 1};
     float* v = (momentum != 0.0) ? velocity : nullptr;
     NCC_REQUIRE(momentum == 0.0 || v, "sgd: momentum without a velocity buffer");
+    ProfScope prof(PROF_SGD, (v ? 20.0 : 12.0) * (double)n, (cudaStream_t)stream);
     sgd_kernel<<<grid_for((long long)n, kThreads), kThreads, 0, (cudaStream_t)stream>>>(param, v, grad, a, n);
     NCC_COUNT_LAUNCH();
     return launch_status("sgd");
@@ -378,7 +414,8 @@ int nc_cuda_adam_update_f32_ex(float* param, float* m, float* v, float* v_max, c
                                double bias_corr2, double grad_scale, size_t n, void* stream) {
     if (n == 0) return NC_CUDA_OK;
     NCC_REQUIRE(param && m && v && grad, "adam: null pointer");
-    AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2, grad_scale};
+    AdamArgs a{lr, beta1, beta2, eps, weight_decay, 1.0 / bias_corr1, 1.0 / bias_corr2, grad_scale};
+    ProfScope prof(PROF_ADAM, (v_max ? 36.0 : 28.0) * (double)n, (cudaStream_t)stream);
     adam_kernel<<<grid_for((long long)n, kThreads), kThreads, 0, (cudaStream_t)stream>>>(param, m, v, v_max, grad, a, n);
     NCC_COUNT_LAUNCH();
     return launch_status("adam");
@@ -393,6 +430,9 @@ int nc_cuda_sgd_update_multi_f32_ex(int count, float* const* params, float* cons
         NCC_REQUIRE(numel[i] == 0 || (params[i] && grads[i] && (momentum == 0.0 || velocities[i])), "sgd_multi: null pointer in entry %d", i);
     SgdArgs a{lr, momentum, dampening, weight_decay, grad_scale, nesterov, first_step, 1};
     cudaStream_t st = (cudaStream_t)stream;
+    double total = 0.0;
+    for (int i = 0; i < count; i++) total += (double)numel[i];
+    ProfScope prof(PROF_SGD, (momentum != 0.0 ? 20.0 : 12.0) * total, st);
     return multi_launch(count, params, momentum != 0.0 ? velocities : nullptr, nullptr, nullptr, grads, numel, "sgd_multi",
                         [&](const MultiTable& t, unsigned int blocks) { sgd_multi_kernel<<<blocks, kThreads, 0, st>>>(t, a); });
 }
@@ -404,8 +444,11 @@ int nc_cuda_adam_update_multi_f32_ex(int count, float* const* params, float* con
     NCC_REQUIRE(params && m && v && grads && numel, "adam_multi: null table");
     for (int i = 0; i < count; i++)
         NCC_REQUIRE(numel[i] == 0 || (params[i] && m[i] && v[i] && grads[i]), "adam_multi: null pointer in entry %d", i);
-    AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2, grad_scale};
+    AdamArgs a{lr, beta1, beta2, eps, weight_decay, 1.0 / bias_corr1, 1.0 / bias_corr2, grad_scale};
     cudaStream_t st = (cudaStream_t)stream;
+    double total = 0.0;
+    for (int i = 0; i < count; i++) total += (double)numel[i];
+    ProfScope prof(PROF_ADAM, (v_max ? 36.0 : 28.0) * total, st);
     return multi_launch(count, params, m, v, v_max, grads, numel, "adam_multi",
                         [&](const MultiTable& t, unsigned int blocks) { adam_multi_kernel<<<blocks, kThreads, 0, st>>>(t, a); });
 }
@@ -425,6 +468,7 @@ int nc_cuda_sum_axis_f32_ex(float* out, const float* in, size_t outer, size_t re
     if (outer == 0 || inner == 0) return NC_CUDA_OK;
     NCC_REQUIRE(out && in, "sum_axis: null pointer");
     cudaStream_t st = (cudaStream_t)stream;
+    ProfScope prof(PROF_REDUCE, 4.0 * (double)outer * reduce_dim * inner, st);
     if (inner == 1) {
         sum_rows_kernel<<<grid_for((long long)outer * 32, kThreads), kThreads, 0, st>>>(out, in, outer, reduce_dim);
     } else {

@@ -116,13 +116,14 @@ extern "C" int nc_cuda_cross_entropy_fused_static_f32_ex(float* loss, float* gra
                                                           const int64_t* targets, int N, int C, float grad_scale,
                                                           void* stream) {
     NCC_REQUIRE(logits && targets && N > 0 && C > 0, "cross_entropy_static: bad argument");
-    NCC_REQUIRE(N <= kMaxRows, "cross_entropy_static: %d rows exceed the fixed scratch (at most %d rows per call)", N, kMaxRows);
+    if (N > kMaxRows)
+        return set_status(NC_CUDA_ERR_LIMIT, "cross_entropy_static: %d rows exceed the fixed scratch (at most %d rows per call)", N, kMaxRows);
     cudaStream_t st = (cudaStream_t)stream;
     unsigned char* base = nullptr;
     int rc = scratch_for_current_device(&base);
     if (rc) return rc;
     const int blocks = grid_for((long long)N * 32, kThreads, 4);  // same grid as the allocating entry point
-    if (blocks > kMaxBlocks) return set_status(NC_CUDA_ERR_ARG, "cross_entropy_static: %d CTAs exceed the fixed scratch", blocks);
+    if (blocks > kMaxBlocks) return set_status(NC_CUDA_ERR_LIMIT, "cross_entropy_static: %d CTAs exceed the fixed scratch", blocks);
     // the ticket must start at zero whatever an earlier, possibly failed, call left behind
     NCC_TRY(cudaMemsetAsync(base, 0, 16, st));
     ce_static_kernel<<<blocks, kThreads, 0, st>>>(loss, grad, logits, targets, N, C, grad_scale / (float)N,

@@ -60,6 +60,33 @@ extern unsigned long long g_launches;
 extern unsigned long long g_epoch;
 #define NCC_COUNT_LAUNCH() (++ncc::g_launches, ++ncc::g_epoch)
 
+// ---- device timing per kernel family (nc_cuda_profile_begin / _read) ----
+// While armed, every profiled call is bracketed by a pair of CUDA events on its launching stream and filed under one
+// category together with its algorithmic work: FLOPs (2 * M * N * K of the logical contraction) for the tensor-core
+// families, bytes that must cross HBM for the memory-bound ones.  Tensor-core kernels are timed per launch; the
+// memory-bound families per entry point (all launches of one call), outermost call only.
+enum {
+    PROF_CONV_FWD = 0, PROF_CONV_DX, PROF_CONV_DW,         // tcgen05 convolutions: forward, input gradient, weight gradient
+    PROF_GEMM_NT, PROF_GEMM_NN, PROF_GEMM_TN, PROF_GEMM_TT,  // tcgen05 GEMM by operand layout (Linear forward / dX / dW / other)
+    PROF_CONV_FIRST,                                        // CUDA-core kernels of the 3-channel input layer
+    PROF_BATCHNORM, PROF_LAYERNORM, PROF_ACTIVATION, PROF_ELEMENTWISE, PROF_MAXPOOL, PROF_LOSS, PROF_SGD, PROF_ADAM,
+    PROF_REDUCE, PROF_RELAYOUT,
+    PROF_CATEGORIES
+};
+bool prof_armed();
+// Category the next tensor-core launch is filed under (set by the entry point that knows which pass it is).
+void prof_set_role(int cat);
+int prof_role();
+struct ProfScope {
+    int slot;
+    cudaStream_t st;
+    bool outer;
+    // kernel_level: a single tensor-core launch (always recorded); otherwise an entry point (recorded when outermost)
+    ProfScope(int cat, double work, cudaStream_t stream, bool kernel_level = false);
+    ~ProfScope();
+    void add_work(double more);   // for work only known after the scope opened
+};
+
 // out[c] = sum over rows of in[r][c] for a dense row-major (rows x cols) matrix; two-stage,
 // double accumulation, fixed combine order (defined in pool_norm.cu).
 int column_sums(float* out, const float* in, size_t rows, int cols, cudaStream_t st);

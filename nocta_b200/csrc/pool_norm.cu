@@ -640,9 +640,14 @@ __global__ void __launch_bounds__(kThreads) bn_relu_pool2_fwd_kernel(float4* __r
             for (int v = 0; v < 4; v++) {
                 float o = g[v] * ((xv[v] - mu[v]) * is[v]) + b[v];
                 if (!(o > 0.f)) o = 0.f;
-                if (rnd) o = round_tf32(o);
+                // the window offset is decided on the unrounded value, as the reference decides it: two candidates
+                // closer than a TF32 step must not turn into a tie that the scan order breaks
                 if (o > best[v]) { best[v] = o; bi[v] = pos; }
             }
+        }
+        if (rnd) {   // rounding is monotonic: the rounded maximum is the maximum of the rounded values
+#pragma unroll
+            for (int v = 0; v < 4; v++) best[v] = round_tf32(best[v]);
         }
         pooled[i] = make_float4(best[0], best[1], best[2], best[3]);
         if (idx) idx[i] = make_uchar4((uint8_t)bi[0], (uint8_t)bi[1], (uint8_t)bi[2], (uint8_t)bi[3]);
@@ -904,6 +909,7 @@ struct ColSum {  // (x, 0)
 int ncc::column_sums(float* out, const float* in, size_t rows, int cols, cudaStream_t st) {
     if (cols <= 0) return NC_CUDA_OK;
     NCC_REQUIRE(out && (in || rows == 0), "column_sums: null pointer");
+    ProfScope prof(PROF_REDUCE, 4.0 * (double)rows * cols, st);
     if (rows == 0) { NCC_TRY(cudaMemsetAsync(out, 0, sizeof(float) * cols, st)); return NC_CUDA_OK; }
     double* partial = nullptr;
     int slabs = 0;
@@ -920,6 +926,9 @@ int nc_cuda_maxpool2d_forward_idx_f32_ex(float* out, uint8_t* argmax, const floa
                                          int k, int stride, int layout, void* stream) {
     NCC_REQUIRE(out && in && N >= 0 && C > 0 && k > 0 && stride > 0 && H >= k && W >= k && k * k <= 255,
                 "maxpool_forward: bad argument");
+    // algorithmic bytes: the input once, the pooled output, one byte of window offset per output
+    const double n_out = (double)N * C * ((H - k) / stride + 1) * ((W - k) / stride + 1);
+    ProfScope prof(PROF_MAXPOOL, 4.0 * N * C * (double)H * W + n_out * (4.0 + (argmax ? 1.0 : 0.0)), (cudaStream_t)stream);
     if (layout == 0) return maxpool_fwd<0>(out, argmax, in, N, C, H, W, k, stride, (cudaStream_t)stream);
     return maxpool_fwd<1>(out, argmax, in, N, C, H, W, k, stride, (cudaStream_t)stream);
 }
@@ -927,6 +936,8 @@ int nc_cuda_maxpool2d_backward_idx_f32_ex(float* gin, const float* gout, const u
                                           int W, int k, int stride, int layout, void* stream) {
     NCC_REQUIRE(gin && gout && argmax && C > 0 && k > 0 && stride > 0 && H >= k && W >= k,
                 "maxpool_backward: bad argument");
+    const double n_out = (double)N * C * ((H - k) / stride + 1) * ((W - k) / stride + 1);
+    ProfScope prof(PROF_MAXPOOL, 4.0 * N * C * (double)H * W + n_out * 5.0, (cudaStream_t)stream);
     if (layout == 0) return maxpool_bwd<0>(gin, gout, argmax, N, C, H, W, k, stride, (cudaStream_t)stream);
     return maxpool_bwd<1>(gin, gout, argmax, N, C, H, W, k, stride, (cudaStream_t)stream);
 }
@@ -956,11 +967,13 @@ int nc_cuda_batchnorm_forward_f32_ex(float* y, const float* x, const float* gamm
     NCC_REQUIRE(y && x && save_mean && save_var && N > 0 && C > 0 && spatial > 0, "batchnorm_forward: bad argument");
     cudaStream_t st = (cudaStream_t)stream;
     const size_t total = (size_t)N * C * spatial;
+    ProfScope prof(PROF_BATCHNORM, 8.0 * (double)total, st);   // read x, write y (+ read x for the statistics, below)
     if (training) {
         double* partial = nullptr;
         int slabs = 0;
         // the convolution that produced x may have left its per-channel sums behind (see nc_cuda_set_conv_stats)
         if (!(layout == 1 && conv_stats_take(x, C, (long long)N * spatial, &partial, &slabs))) {
+            prof.add_work(4.0 * (double)total);
             int rc = channel_reduce(&partial, &slabs, N, C, spatial, layout, BnFwdSum{x, C}, BnFwdSumFlat{x}, al16(x), st);
             if (rc) return rc;
         }
@@ -999,6 +1012,8 @@ int nc_cuda_batchnorm_backward_f32_ex(float* dx, float* dgamma, float* dbeta, co
     const float fe = (float)eps;
     double* partial = nullptr;
     int slabs = 0;
+    // sums pass reads dy and x (and the saved ReLU output when there is one), apply pass reads them again and writes dx
+    ProfScope prof(PROF_BATCHNORM, (relu_out ? 28.0 : 20.0) * (double)total, st);
     const ReluMask mask{relu_out, gamma, relu_beta, relu_out ? 0 : (relu_recompute ? 1 : 0)};
     int rc = channel_reduce(&partial, &slabs, N, C, spatial, layout,
                             BnBwdSum{dy, x, mask, save_mean, save_var, fe, C},
@@ -1040,10 +1055,13 @@ int nc_cuda_batchnorm_relu_maxpool2_forward_f32_ex(float* pooled, uint8_t* argma
     NCC_REQUIRE(al16(pooled) && al16(x) && ((uintptr_t)argmax % 4 == 0), "batchnorm_relu_maxpool2_forward: misaligned operand");
     NCC_REQUIRE((size_t)N * (H / 2) * (W / 2) < 0xffffffffull, "batchnorm_relu_maxpool2_forward: too many pixels");
     cudaStream_t st = (cudaStream_t)stream;
+    // read x, write the pooled quarter and one byte of window offset per pooled element (+ x again for the statistics)
+    ProfScope prof(PROF_BATCHNORM, (4.0 + 1.0 + 0.25) * (double)N * C * H * W, st);
     if (training) {
         double* partial = nullptr;
         int slabs = 0;
         if (!conv_stats_take(x, C, (long long)N * H * W, &partial, &slabs)) {
+            prof.add_work(4.0 * (double)N * C * H * W);
             int rc = channel_reduce(&partial, &slabs, N, C, H * W, 1, BnFwdSum{x, C}, BnFwdSumFlat{x}, true, st);
             if (rc) return rc;
         }
@@ -1075,6 +1093,8 @@ int nc_cuda_batchnorm_relu_maxpool2_backward_f32_ex(float* dx, float* dgamma, fl
     double* partial = nullptr;
     int slabs = 0;
     const size_t prow = (size_t)N * (H / 2) * (W / 2);
+    // both passes read x, the pooled gradient and the window offsets; the second writes dx
+    ProfScope prof(PROF_BATCHNORM, (2.0 * (4.0 + 1.0 + 0.25) + 4.0) * (double)N * C * H * W, st);
     int rc = launch_colreduce(&partial, &slabs, prow, C, true, BnPoolBwdSum{dpooled, argmax, x, gamma, beta, save_mean, save_var, fe, C, H, W}, st);
     if (rc) return rc;
     float* sums = (float*)scratch(6, sizeof(float) * 2 * (size_t)C, st);
@@ -1107,6 +1127,7 @@ int nc_cuda_layernorm_forward_f32_ex(float* y, const float* x, const float* gamm
                                      size_t cols, double eps, void* stream) {
     if (rows == 0 || cols == 0) return NC_CUDA_OK;
     NCC_REQUIRE(y && x && cols <= 0x7fffffff, "layernorm_forward: bad argument");
+    ProfScope prof(PROF_LAYERNORM, 8.0 * (double)rows * cols, (cudaStream_t)stream);
     ln_fwd_kernel<<<grid_for((long long)rows * 32, kThreads), kThreads, 0, (cudaStream_t)stream>>>(y, x, gamma, beta, rows, (int)cols, (float)eps, round_outputs() ? 1 : 0);
     NCC_COUNT_LAUNCH();
     return launch_status("layernorm_forward");
@@ -1118,6 +1139,8 @@ int nc_cuda_layernorm_backward_f32_ex(float* dx, float* dgamma, float* dbeta, co
     NCC_REQUIRE(dx && dy && x && cols <= 0x7fffffff, "layernorm_backward: bad argument");
     cudaStream_t st = (cudaStream_t)stream;
     const bool params = dgamma || dbeta;
+    // rows pass: read dy, x, write dx; parameter pass: read dy, x again
+    ProfScope prof(PROF_LAYERNORM, (params ? 20.0 : 12.0) * (double)rows * cols, st);
     float2* stats = nullptr;
     if (params) {
         stats = (float2*)scratch(6, sizeof(float2) * rows, st);

@@ -108,6 +108,40 @@ unsigned int* device_error_word() {
     return g_err_word;
 }
 
+// ---- per-category device timing ----
+static const char* const kProfNames[PROF_CATEGORIES] = {
+    "conv_fwd", "conv_dx", "conv_dw", "gemm_nt", "gemm_nn", "gemm_tn", "gemm_tt", "conv_first", "batchnorm", "layernorm",
+    "activation", "elementwise", "maxpool", "loss", "sgd", "adam", "reduce", "relayout"};
+static const int kProfCap = 32768;
+static struct {
+    bool on = false;
+    int n = 0, depth = 0, role = PROF_GEMM_NT;
+    cudaEvent_t* start = nullptr;
+    cudaEvent_t* stop = nullptr;
+    unsigned char* cat = nullptr;
+    double* work = nullptr;
+} g_prof;
+bool prof_armed() { return g_prof.on; }
+void prof_set_role(int cat) { g_prof.role = cat; }
+int prof_role() { return g_prof.role; }
+ProfScope::ProfScope(int cat, double work, cudaStream_t stream, bool kernel_level) : slot(-1), st(stream), outer(false) {
+    if (!g_prof.on) return;
+    if (!kernel_level) {
+        outer = true;
+        if (g_prof.depth++ > 0) return;
+    }
+    if (g_prof.n >= kProfCap || cat < 0 || cat >= PROF_CATEGORIES) return;
+    slot = g_prof.n++;
+    g_prof.cat[slot] = (unsigned char)cat;
+    g_prof.work[slot] = work;
+    cudaEventRecord(g_prof.start[slot], st);
+}
+void ProfScope::add_work(double more) { if (slot >= 0) g_prof.work[slot] += more; }
+ProfScope::~ProfScope() {
+    if (outer) g_prof.depth--;
+    if (slot >= 0) cudaEventRecord(g_prof.stop[slot], st);
+}
+
 static void release_all() {
     for (int i = 0; i < kScratchSlots; i++) {
         if (g_scratch[i]) cudaFree(g_scratch[i]);
@@ -256,6 +290,19 @@ void* nc_cuda_event_create(void) {
     }
     return ev;
 }
+void* nc_cuda_event_create_timed(void) {
+    cudaEvent_t ev = nullptr;
+    if (cudaEventCreate(&ev) != cudaSuccess) {
+        set_status(NC_CUDA_ERR_RUNTIME, "cudaEventCreate failed");
+        return nullptr;
+    }
+    return ev;
+}
+int nc_cuda_event_elapsed_ms(void* start, void* stop, float* ms) {
+    NCC_REQUIRE(start && stop && ms, "event_elapsed: null argument");
+    NCC_TRY(cudaEventElapsedTime(ms, (cudaEvent_t)start, (cudaEvent_t)stop));
+    return NC_CUDA_OK;
+}
 void nc_cuda_event_destroy(void* event) {
     if (event) cudaEventDestroy((cudaEvent_t)event);
 }
@@ -296,6 +343,46 @@ unsigned int nc_cuda_device_error_word(void) {
     if (cudaMemcpy(&h, w, sizeof(h), cudaMemcpyDeviceToHost) != cudaSuccess) return 0xffffffffu;
     if (h) cudaMemset(w, 0, sizeof(h));
     return h;
+}
+int nc_cuda_profile_begin(void) {
+    if (!g_prof.start) {
+        g_prof.start = new cudaEvent_t[kProfCap];
+        g_prof.stop = new cudaEvent_t[kProfCap];
+        g_prof.cat = new unsigned char[kProfCap];
+        g_prof.work = new double[kProfCap];
+        for (int i = 0; i < kProfCap; i++)
+            if (cudaEventCreate(&g_prof.start[i]) != cudaSuccess || cudaEventCreate(&g_prof.stop[i]) != cudaSuccess)
+                return set_status(NC_CUDA_ERR_RUNTIME, "profile: cudaEventCreate failed");
+    }
+    g_prof.n = 0;
+    g_prof.depth = 0;
+    g_prof.on = true;
+    return NC_CUDA_OK;
+}
+int nc_cuda_profile_end(void) {
+    g_prof.on = false;
+    if (g_prof.n > 0 && cudaEventSynchronize(g_prof.stop[g_prof.n - 1]) != cudaSuccess)
+        return set_status(NC_CUDA_ERR_RUNTIME, "profile: cudaEventSynchronize failed");
+    return NC_CUDA_OK;
+}
+int nc_cuda_profile_categories(void) { return PROF_CATEGORIES; }
+const char* nc_cuda_profile_category_name(int category) {
+    return (category >= 0 && category < PROF_CATEGORIES) ? kProfNames[category] : "";
+}
+int nc_cuda_profile_read(int category, double* total_ms, unsigned long long* calls, double* work) {
+    if (g_prof.on) return set_status(NC_CUDA_ERR_ARG, "profile_read: call nc_cuda_profile_end first");
+    double ms = 0.0, w = 0.0;
+    unsigned long long n = 0;
+    for (int i = 0; i < g_prof.n; i++) {
+        if (g_prof.cat[i] != category) continue;
+        float t = 0.f;
+        if (cudaEventElapsedTime(&t, g_prof.start[i], g_prof.stop[i]) != cudaSuccess) continue;
+        ms += t; w += g_prof.work[i]; n++;
+    }
+    if (total_ms) *total_ms = ms;
+    if (calls) *calls = n;
+    if (work) *work = w;
+    return NC_CUDA_OK;
 }
 unsigned long long nc_cuda_launch_count(void) { return g_launches; }
 void nc_cuda_reset_launch_count(void) { g_launches = 0; }  // the epoch keeps counting

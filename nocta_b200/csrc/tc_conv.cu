@@ -1,0 +1,878 @@
+// Halo-resident tensor-core kernels for stride-1 convolutions with filters up to 3 x 3 (plain TF32 mode), sm_100a:
+// TMA-fed tcgen05.mma (kind::tf32), accumulators in tensor memory, inline PTX.
+//
+// The operand traffic from L2 into shared memory, not the tensor pipe, bounds an implicit-GEMM convolution that streams
+// one operand tile per filter tap: every tap re-reads the same pixels.  The kernels here load a pixel tile WITH its halo
+// once and address every tap inside it by moving the start address of the shared-memory matrix descriptor: the swizzle
+// of a TMA-written tile is a function of the absolute shared-memory address, so a descriptor may start at any 128-byte
+// pixel row and use any stride between its 8-row groups.
+//
+//   convh_kernel<false>  forward / input gradient, output channels on M (weights = A, streamed per tap), 8 x <=32 pixels
+//                        of one image on N (halo = B).  One MMA of N = 8 * rows per k-step.
+//   convh_kernel<true>   the same convolution with the roles swapped for layers with at most 96 output channels: 8 x 16
+//                        pixels on M (halo = A), all output channels on N (weights = B).  An MMA costs
+//                        max(N / 2, operand bytes / 128, ~46) cycles whatever M is, so 64 channels on M run at half
+//                        rate while 128 pixels on M with N = 64 run at two thirds.
+//   dwh_kernel<false>    weight gradient for Cin % 128 == 0: A = dY tile (128 output channels, MN-major), B = x halo
+//                        tile (128 input channels, MN-major); one filter row per work item, the kW taps of the row are kW
+//                        MMAs per 8-pixel k-step against the same two tiles (B start moved by kw pixel rows) into kW
+//                        accumulators.  dY and x cross from L2 to shared memory kH times instead of kH * kW times, as a
+//                        few large copies per stage instead of twelve 4 KB ones.
+//   dwh_kernel<true>     weight gradient for narrower inputs: A = ONE 32-channel x halo chunk addressed with a leading
+//                        byte offset of one pixel row, so the four 32-row chunks of M are the same channels shifted by
+//                        0..3 pixels = the kW taps of a filter row (kW = 3: three quarters of M useful); B = dY tile;
+//                        one accumulator per filter row, all kH * kW taps per work item.
+//
+// Pixel tiles may hang over the image edge: TMA zero-fills what it loads there (which is also the padding) and the
+// epilogues mask what they store.  No cluster launch and no multicast: each CTA loads its own tiles.  Every mbarrier
+// wait is bounded; on expiry the kernel records a code in the device error word, drains, frees its TMEM and returns.
+#include "tc_gemm.cuh"
+#include "tc_ptx.cuh"
+#include "../../include/nocta_cuda.h"
+
+namespace tc {
+
+namespace {
+constexpr int kBM = 128;
+constexpr int kWTileBytes = 128 * 128;  // one weight stage: up to 128 rows of 32 floats
+constexpr int kConvhWStages = 12;       // ring slots available; a launch uses as many as fit into the 96 KB weight region
+constexpr int kTW = 8, kTH = 32;        // pixel tile of the convolution kernels
+constexpr int kMaxDynSmem = 227 * 1024 - 2048;
+
+__device__ __forceinline__ uint32_t idesc_tf32(uint32_t M, uint32_t N, bool a_mn, bool b_mn) {
+    // D = f32, A = B = tf32, operand majors, N / 8, M / 16
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+}  // namespace
+
+// ------------------------------------------------------------------------------------------
+// convh_kernel
+// ------------------------------------------------------------------------------------------
+struct ConvhParams {
+    float* D;
+    int ldd;
+    const float* bias;
+    int M;                 // output channels
+    int Ho, Wo;
+    int tiles_w, tiles_h;  // pixel tiles per image
+    int tiles_px;          // pixel tiles in total (images * tiles_h * tiles_w)
+    int tiles_m;           // 128-channel tiles (1 when the pixels are on M)
+    int kH, kW, pad;
+    int cchunks;           // 32-channel chunks of the input channels
+    int wrows;             // rows per tap in the packed weights
+    int wbox_bytes;        // bytes one weight copy delivers
+    int wstages;           // weight ring depth: slots of wslot_bytes in the 96 KB weight region
+    int wslot_bytes;       // one slot holds the kW taps of a filter row (one mbarrier round trip per 4 * kW MMAs)
+    int pitch;             // halo line pitch in pixels
+    int halo_bytes, halo_stride;
+    double* stat;          // non-null: per CTA and channel (sum, sum of squares) of the output it wrote, [gridDim.x][M][2]
+    unsigned int* err;
+};
+
+// PXM: pixels on M.  NCH: output channels / 32 (PXM only; 0 otherwise).
+template <bool PXM, int NCH>
+__global__ void __launch_bounds__(288, 1)
+convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const ConvhParams p) {
+    constexpr int WSMAX = kConvhWStages;
+    // MMA-issuing warps.  Channels on M: one.  Pixels on M: one per 8 x 16 pixel block of the tile, and with at most 64
+    // output channels a second pair that takes k-steps 2 and 3 of every tap into accumulators of its own (added by the
+    // epilogue): the short N <= 64 MMAs need four issuing threads to keep the tensor pipe busy.
+    constexpr int KSPLIT = (PXM && NCH <= 2) ? 2 : 1;
+    constexpr int NISS = PXM ? 2 * KSPLIT : 1;
+    const int WS = p.wstages;
+    extern __shared__ uint8_t dyn_smem[];
+    __shared__ __align__(8) uint64_t bar_hfull[2];
+    __shared__ __align__(8) uint64_t bar_hempty[2];
+    __shared__ __align__(8) uint64_t bar_wfull[WSMAX];
+    __shared__ __align__(8) uint64_t bar_wempty[WSMAX];
+    __shared__ __align__(8) uint64_t bar_acc_full[2];
+    __shared__ __align__(8) uint64_t bar_acc_empty[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    __shared__ double stat_sh[PXM ? 4 * NCH * 32 * 2 : 1];
+    __shared__ float stat_tile[PXM ? 4 : 1][PXM ? 32 : 1][PXM ? 33 : 1];   // per epilogue warp: 32 pixels x 32 channels, transposed to sum over pixels
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t halo_base = (smem_u32(dyn_smem) + 1023u) & ~1023u;
+    const uint32_t w_base = halo_base + 2u * (uint32_t)p.halo_stride;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < 2; s++) {
+            mbar_init(smem_u32(&bar_hfull[s]), 1);
+            mbar_init(smem_u32(&bar_hempty[s]), NISS);     // one arrival per MMA-issuing warp
+            mbar_init(smem_u32(&bar_acc_full[s]), NISS);
+            mbar_init(smem_u32(&bar_acc_empty[s]), 128);
+        }
+        for (int s = 0; s < WS; s++) {
+            mbar_init(smem_u32(&bar_wfull[s]), 1);
+            mbar_init(smem_u32(&bar_wempty[s]), NISS);
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    volatile int* abortp = &abort_flag;
+    const int total_tiles = p.tiles_px * p.tiles_m;  // t -> (pixel tile fastest, then channel tile)
+    const int ntaps = p.kH * p.kW;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------- producer: halo boxes (one chunk ahead) and weight tiles ----------------
+            int ht = blockIdx.x, hcc = 0;   // cursor of the next halo to request
+            uint32_t hcount = 0;
+            bool ok = true;
+            auto issue_halo = [&]() {
+                if (ht >= total_tiles || !ok) return;
+                const uint32_t slot = hcount & 1u;
+                if (!mbar_wait(smem_u32(&bar_hempty[slot]), ((hcount >> 1) & 1u) ^ 1u, p.err, 0x600u + slot, abortp)) { ok = false; return; }
+                const int pt = ht % p.tiles_px;
+                const int tw = pt % p.tiles_w, tt = pt / p.tiles_w;
+                const int th = tt % p.tiles_h, n = tt / p.tiles_h;
+                const uint32_t full = smem_u32(&bar_hfull[slot]);
+                mbar_expect_tx(full, (uint32_t)p.halo_bytes);
+                tma_4d(halo_base + slot * (uint32_t)p.halo_stride, &tmX, hcc * 32, tw * kTW - p.pad, th * kTH - p.pad, n, full);
+                hcount++;
+                if (++hcc == p.cchunks) { hcc = 0; ht += gridDim.x; }
+            };
+            int s = 0;
+            uint32_t ph = 0;
+            issue_halo();
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int m0 = (t / p.tiles_px) * (PXM ? NCH * 32 : kBM);
+                for (int cc = 0; cc < p.cchunks && ok; cc++) {
+                    int wrow = m0;
+                    for (int kh = 0; kh < p.kH; kh++) {
+                        if (kh == (p.kH > 1 ? 1 : 0)) issue_halo();   // the next chunk's halo, once this chunk is under way
+                        if (!ok) break;
+                        if (!mbar_wait(smem_u32(&bar_wempty[s]), ph ^ 1u, p.err, 0x100u + s, abortp)) { ok = false; break; }
+                        const uint32_t full = smem_u32(&bar_wfull[s]);
+                        mbar_expect_tx(full, (uint32_t)(p.kW * p.wbox_bytes));
+                        for (int kw = 0; kw < p.kW; kw++, wrow += p.wrows)
+                            tma_2d(w_base + (uint32_t)(s * p.wslot_bytes + kw * p.wbox_bytes), &tmW, cc * 32, wrow, full);
+                        if (++s == WS) { s = 0; ph ^= 1u; }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1 || warp >= 6) {
+        // ---------------- MMA issuers.  MMAs into one accumulator must come from one thread to stay ordered, and one
+        // thread issues an MMA with fresh descriptors only every hundred-odd cycles; with the pixels on M the two
+        // 8 x 16 pixel blocks of a tile have their own accumulators, so warp 1 issues the upper block and warp 6 the
+        // lower one.  With the channels on M there is one accumulator and warp 1 issues alone.  The whole warp runs
+        // the loop, lane 0 issues.
+        const int issuer = warp == 1 ? 0 : warp - 5;   // 0..3
+        const int iss = issuer & 1, khalf = issuer >> 1;  // pixel block, half of the k-steps
+        if (issuer < NISS) {
+            const uint32_t leader = lane == 0 ? 1u : 0u;
+            const uint64_t dw0 = smem_desc(w_base, 16u, 1024u, 2u);                      // weight tile: K-major, dense 8-row groups
+            const uint64_t dh0 = smem_desc(halo_base, 16u, (uint32_t)p.pitch * 128u, 2u);  // halo: 8-row groups one halo line apart
+            const uint32_t idesc_px = idesc_tf32(128u, (uint32_t)(NCH * 32), false, false);
+            const uint64_t sub_off = (uint64_t)(((uint32_t)(16 * iss * p.pitch) * 128u) >> 4);  // this issuer's 8 x 16 pixel block
+            int s = 0;
+            uint32_t ph = 0, tile_iter = 0, hcount = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, tile_iter++) {
+                const uint32_t ab = tile_iter & 1u;
+                const int th = ((t % p.tiles_px) / p.tiles_w) % p.tiles_h;
+                const int rows = (p.Ho - th * kTH) < kTH ? (p.Ho - th * kTH) : kTH;
+                const uint32_t idesc_ch = idesc_tf32(128u, (uint32_t)(8 * ((rows + 1) & ~1)), false, false);
+                const bool active = !PXM || rows > 16 * iss;   // a short tile has no lower block: that issuer only keeps the barriers moving
+                ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_acc_empty[ab]), ((tile_iter >> 1) & 1u) ^ 1u, p.err, 0x500u + ab, abortp));
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc = tmem_base + ab * 256u + (uint32_t)(PXM ? khalf * 128 + iss * NCH * 32 : 0);
+                for (int cc = 0; cc < p.cchunks && ok; cc++, hcount++) {
+                    const uint32_t slot = hcount & 1u;
+                    ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_hfull[slot]), (hcount >> 1) & 1u, p.err, 0x700u + slot, abortp));
+                    if (!ok) break;
+                    const uint64_t dhs = dh0 + sub_off + (uint64_t)((slot * (uint32_t)p.halo_stride) >> 4);
+                    for (int kh = 0; kh < p.kH; kh++) {
+                        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_wfull[s]), ph, p.err, 0x200u + s, abortp));
+                        if (!ok) break;
+                        tc_fence_after();
+                        uint64_t dw = dw0 + (uint64_t)(((uint32_t)s * (uint32_t)p.wslot_bytes) >> 4);
+                        uint64_t dh = dhs + (uint64_t)(((uint32_t)(kh * p.pitch) * 128u) >> 4);
+                        if (active) {
+                            for (int kw = 0; kw < p.kW; kw++, dw += (uint64_t)((uint32_t)p.wbox_bytes >> 4), dh += 8u) {
+#pragma unroll
+                                for (int k2 = 0; k2 < 4 / KSPLIT; k2++) {
+                                    const int ks = khalf * (4 / KSPLIT) + k2;
+                                    const uint32_t accum = (uint32_t)((cc | kh | kw | k2) != 0);
+                                    if (PXM) umma_tf32_w(acc, dh + (uint64_t)(ks * 2), dw + (uint64_t)(ks * 2), idesc_px, accum, leader);
+                                    else umma_tf32_w(acc, dw + (uint64_t)(ks * 2), dh + (uint64_t)(ks * 2), idesc_ch, accum, leader);
+                                }
+                            }
+                        }
+                        umma_commit_w(smem_u32(&bar_wempty[s]), leader);
+                        if (++s == WS) { s = 0; ph ^= 1u; }
+                    }
+                    if (ok) umma_commit_w(smem_u32(&bar_hempty[slot]), leader);
+                }
+                if (ok) umma_commit_w(smem_u32(&bar_acc_full[ab]), leader);
+            }
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        const int q = warp & 3;
+        const int r = q * 32 + lane;
+        uint32_t tile_iter = 0;
+        bool ok = true;
+        if (!PXM) {
+            // lane = output channel, column = pixel.  Output statistics: a thread owns channel m0 + r of every tile it
+            // sees, so it keeps one running pair per channel tile and writes it once (slab = this CTA):
+            // stat[blockIdx.x][M][2].  Slots of channel tiles this CTA never visits must read zero.
+            double ssum = 0.0, ssq = 0.0;
+            int stat_m0 = -1;
+            if (p.stat)
+                for (int mt = 0; mt < p.tiles_m; mt++)
+                    if (mt * kBM + r < p.M) {
+                        double* sd = p.stat + ((size_t)blockIdx.x * p.M + mt * kBM + r) * 2;
+                        sd[0] = 0.0; sd[1] = 0.0;
+                    }
+            for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, tile_iter++) {
+                const int pt = t % p.tiles_px, m0 = (t / p.tiles_px) * kBM;
+                if (p.stat && m0 != stat_m0) {
+                    if (stat_m0 >= 0 && stat_m0 + r < p.M) {
+                        double* sd = p.stat + ((size_t)blockIdx.x * p.M + stat_m0 + r) * 2;
+                        sd[0] = ssum; sd[1] = ssq;
+                    }
+                    ssum = 0.0; ssq = 0.0; stat_m0 = m0;
+                }
+                const int tw = pt % p.tiles_w, tt = pt / p.tiles_w;
+                const int th = tt % p.tiles_h, n = tt / p.tiles_h;
+                const int rows = (p.Ho - th * kTH) < kTH ? (p.Ho - th * kTH) : kTH;   // image rows this tile holds
+                const int wlim = p.Wo - tw * kTW;                                     // columns j < wlim are inside the image
+                const int last_c0 = ((8 * rows + 31) / 32 - 1) * 32;
+                const uint32_t ab = tile_iter & 1u;
+                ok = mbar_wait(smem_u32(&bar_acc_full[ab]), (tile_iter >> 1) & 1u, p.err, 0x400u + ab, abortp);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc = tmem_base + ab * 256u + ((uint32_t)(q * 32) << 16);
+                const int co = m0 + r;
+                const bool co_ok = co < p.M;
+                const float bv = (co_ok && p.bias) ? p.bias[co] : 0.f;
+                // first pixel of the tile; a column chunk of 32 = 4 image rows x 8 pixels
+                float* tile_dst = p.D + (((long long)n * p.Ho + th * kTH) * p.Wo + tw * kTW) * p.ldd + co;
+                const int line = p.Wo * p.ldd;  // elements between image rows (< 2^31 checked by the host)
+#pragma unroll 1
+                for (int c0 = 0; c0 <= last_c0; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(acc + (uint32_t)c0, v);
+                    tmem_ld_wait();
+                    if (c0 == last_c0) {
+                        tc_fence_before();
+                        mbar_arrive(smem_u32(&bar_acc_empty[ab]));
+                    }
+                    if (!co_ok) continue;
+                    const int h4 = c0 >> 3;
+                    float* dst = tile_dst + (long long)h4 * line;
+                    float fs = 0.f, fq = 0.f;
+                    if (wlim >= 8 && h4 + 4 <= rows) {
+#pragma unroll
+                        for (int hh = 0; hh < 4; hh++) {
+#pragma unroll
+                            for (int j = 0; j < 8; j++) {
+                                const float o = __uint_as_float(v[hh * 8 + j]) + bv;
+                                dst[j * p.ldd] = o;
+                                fs += o;
+                                fq = fmaf(o, o, fq);
+                            }
+                            dst += line;
+                        }
+                    } else {
+#pragma unroll
+                        for (int hh = 0; hh < 4; hh++) {
+                            if (h4 + hh < rows) {
+#pragma unroll
+                                for (int j = 0; j < 8; j++)
+                                    if (j < wlim) {
+                                        const float o = __uint_as_float(v[hh * 8 + j]) + bv;
+                                        dst[j * p.ldd] = o;
+                                        fs += o;
+                                        fq = fmaf(o, o, fq);
+                                    }
+                            }
+                            dst += line;
+                        }
+                    }
+                    ssum += (double)fs;
+                    ssq += (double)fq;
+                }
+            }
+            if (p.stat && stat_m0 >= 0 && stat_m0 + r < p.M) {
+                double* sd = p.stat + ((size_t)blockIdx.x * p.M + stat_m0 + r) * 2;
+                sd[0] = ssum; sd[1] = ssq;
+            }
+        } else {
+            // lane = pixel (8 wide x 16 high block, two blocks per tile), column = output channel: a thread stores runs
+            // of 32 consecutive channels of its pixel.  Output statistics: each warp transposes its 32 pixel x 32 channel
+            // block through shared memory so that lane c sums channel c over the 32 pixels, keeps running sums per
+            // channel chunk over all tiles of the CTA, and the four warps are combined once at the end.
+            constexpr int NCHS = NCH > 0 ? NCH : 1;
+            double fs[NCHS], fq[NCHS];
+#pragma unroll
+            for (int c = 0; c < NCHS; c++) { fs[c] = 0.0; fq[c] = 0.0; }
+            const bool want_stat = p.stat != nullptr;
+            const int wq = warp - 2;   // 0..3: this warp's tile in shared memory
+            int stat_m0 = -1;
+            auto flush_stats = [&](int m0) {
+                // the four warps through shared memory, in a fixed order
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+                for (int ch = 0; ch < NCH; ch++) {
+                    stat_sh[((wq * NCHS + ch) * 32 + lane) * 2] = fs[ch];
+                    stat_sh[((wq * NCHS + ch) * 32 + lane) * 2 + 1] = fq[ch];
+                    fs[ch] = 0.0; fq[ch] = 0.0;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                for (int c = threadIdx.x - 64; c < NCH * 32; c += 128) {
+                    double a = 0.0, b = 0.0;
+                    for (int k = 0; k < 4; k++) { a += stat_sh[((k * NCHS + c / 32) * 32 + (c & 31)) * 2]; b += stat_sh[((k * NCHS + c / 32) * 32 + (c & 31)) * 2 + 1]; }
+                    double* sd = p.stat + ((size_t)blockIdx.x * p.M + m0 + c) * 2;
+                    sd[0] = a; sd[1] = b;
+                }
+            };
+            if (want_stat)   // slots of channel tiles this CTA never visits must read zero
+                for (int c = threadIdx.x - 64; c < p.M; c += 128) {
+                    double* sd = p.stat + ((size_t)blockIdx.x * p.M + c) * 2;
+                    sd[0] = 0.0; sd[1] = 0.0;
+                }
+            for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, tile_iter++) {
+                const int pt = t % p.tiles_px, m0 = (t / p.tiles_px) * (NCH * 32);
+                if (want_stat && m0 != stat_m0) {   // the tile walk visits the channel tiles one after the other
+                    if (stat_m0 >= 0) flush_stats(stat_m0);
+                    stat_m0 = m0;
+                }
+                const int tw = pt % p.tiles_w, tt = pt / p.tiles_w;
+                const int th = tt % p.tiles_h, n = tt / p.tiles_h;
+                const int rows = (p.Ho - th * kTH) < kTH ? (p.Ho - th * kTH) : kTH;
+                const int nsub = rows > 16 ? 2 : 1;
+                const uint32_t ab = tile_iter & 1u;
+                ok = mbar_wait(smem_u32(&bar_acc_full[ab]), (tile_iter >> 1) & 1u, p.err, 0x400u + ab, abortp);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc = tmem_base + ab * 256u + ((uint32_t)(q * 32) << 16);
+                const int w = tw * kTW + (r & 7);
+#pragma unroll 1
+                for (int sub = 0; sub < nsub; sub++) {
+                    const int h = th * kTH + sub * 16 + (r >> 3);
+                    const bool px_ok = (w < p.Wo) && (h < p.Ho);
+                    float* dst = p.D + (((long long)n * p.Ho + h) * p.Wo + w) * p.ldd + m0;
+#pragma unroll
+                    for (int ch = 0; ch < NCH; ch++) {
+                        uint32_t v[32];
+                        tmem_ld32(acc + (uint32_t)(sub * NCH * 32 + ch * 32), v);
+                        tmem_ld_wait();
+                        if (KSPLIT == 2) {
+                            uint32_t u[32];
+                            tmem_ld32(acc + (uint32_t)(128 + sub * NCH * 32 + ch * 32), u);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(u[j]));
+                        }
+                        if (sub == nsub - 1 && ch == NCH - 1) {
+                            tc_fence_before();
+                            mbar_arrive(smem_u32(&bar_acc_empty[ab]));
+                        }
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 o;
+                            o.x = __uint_as_float(v[j]);     o.y = __uint_as_float(v[j + 1]);
+                            o.z = __uint_as_float(v[j + 2]); o.w = __uint_as_float(v[j + 3]);
+                            if (p.bias) {
+                                const float4 b4 = *reinterpret_cast<const float4*>(p.bias + m0 + ch * 32 + j);
+                                o.x += b4.x; o.y += b4.y; o.z += b4.z; o.w += b4.w;
+                            }
+                            if (px_ok) *reinterpret_cast<float4*>(dst + ch * 32 + j) = o;
+                            if (want_stat) {
+                                stat_tile[wq][lane][j] = px_ok ? o.x : 0.f;
+                                stat_tile[wq][lane][j + 1] = px_ok ? o.y : 0.f;
+                                stat_tile[wq][lane][j + 2] = px_ok ? o.z : 0.f;
+                                stat_tile[wq][lane][j + 3] = px_ok ? o.w : 0.f;
+                            }
+                        }
+                        if (want_stat) {
+                            __syncwarp();
+                            float a = 0.f, b = 0.f;
+#pragma unroll
+                            for (int k = 0; k < 32; k++) {
+                                const float o = stat_tile[wq][k][lane];
+                                a += o;
+                                b = fmaf(o, o, b);
+                            }
+                            fs[ch] += (double)a;
+                            fq[ch] += (double)b;
+                            __syncwarp();
+                        }
+                    }
+                }
+            }
+            if (want_stat && stat_m0 >= 0) flush_stats(stat_m0);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        // A wait expired somewhere: give copies still in flight time to land before the shared memory is released.
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) { }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// dwh_kernel
+// ------------------------------------------------------------------------------------------
+struct DwhParams {
+    float* partial;        // [splits][Cout][kH * kW * Cin]
+    int Cout, Cin, kH, kW, pad;
+    int TW, R, PW;         // pixel tile: TW pixels x R image rows per stage; x halo line pitch PW = TW + kW - 1
+    int tiles_w, hblocks;  // pixel tiles per image row, row blocks per image
+    int units_total;       // images * hblocks * tiles_w
+    int units_per_split, splits;
+    int items;             // work items per split
+    int cigs;              // groups of input-channel chunks (item dimension)
+    int G;                 // SHIFT: 32-channel chunks of x per item (1 or 2)
+    int ncol;              // MMA N
+    int a_stride, b_stride;  // bytes between the chunk copies of an operand inside a stage (multiples of 1024)
+    int a_bytes, b_bytes;    // bytes one chunk copy delivers
+    int stage_bytes, stages;
+    int nissue;            // MMA-issuing warps: one per accumulator column block (kW of them, or kH when SHIFT)
+    unsigned int* err;
+};
+
+constexpr int kDwhMaxStages = 8;
+
+// SHIFT = false: A = dY (128 output channels), B = x halo (128 input channels), work item = (channel tile, input
+//                channel group, filter row kh), accumulator kw at column kw * 128.
+// SHIFT = true:  A = x halo chunk with LBO = one pixel row (M = 4 shifts x 32 channels), B = dY (ncol output channels),
+//                work item = (output channel tile, group of G input chunks), accumulator (g, kh) at column (g * kH + kh) * ncol.
+template <bool SHIFT>
+__global__ void __launch_bounds__(256, 1)
+dwh_kernel(const __grid_constant__ CUtensorMap tmDy, const __grid_constant__ CUtensorMap tmX, const DwhParams p) {
+    extern __shared__ uint8_t dyn_smem[];
+    __shared__ __align__(8) uint64_t bar_full[kDwhMaxStages];
+    __shared__ __align__(8) uint64_t bar_empty[kDwhMaxStages];
+    __shared__ __align__(8) uint64_t bar_acc_full;
+    __shared__ __align__(8) uint64_t bar_acc_empty;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t tiles_base = (smem_u32(dyn_smem) + 1023u) & ~1023u;
+    const int STAGES = p.stages;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), (uint32_t)p.nissue);
+        }
+        mbar_init(smem_u32(&bar_acc_full), (uint32_t)p.nissue);
+        mbar_init(smem_u32(&bar_acc_empty), 128);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    volatile int* abortp = &abort_flag;
+    const int total_work = p.items * p.splits;   // w -> (item fastest, then split): CTAs that run together share pixels
+    const int ksteps_w = p.TW >> 3;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------- producer ----------------
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+                const int item = w % p.items, z = w / p.items;
+                int co0, ci0, kh0, nA, nB;
+                if (!SHIFT) {
+                    kh0 = item % p.kH;
+                    const int t2 = item / p.kH;
+                    ci0 = (t2 % p.cigs) * 128;
+                    co0 = (t2 / p.cigs) * 128;
+                    nA = (p.Cout - co0) >= 128 ? 4 : (p.Cout - co0) / 32;
+                    nB = 4;
+                } else {
+                    kh0 = 0;
+                    const int cig = item % p.cigs;
+                    ci0 = cig * p.G * 32;
+                    co0 = (item / p.cigs) * p.ncol;
+                    nA = (p.Cin / 32 - cig * p.G) < p.G ? (p.Cin / 32 - cig * p.G) : p.G;
+                    nB = p.ncol / 32;
+                }
+                const uint32_t bytes = (uint32_t)(nA * p.a_bytes + nB * p.b_bytes);
+                const int u0 = z * p.units_per_split;
+                const int u1 = (u0 + p.units_per_split) < p.units_total ? (u0 + p.units_per_split) : p.units_total;
+                int tw = u0 % p.tiles_w, t3 = u0 / p.tiles_w;
+                int hb = t3 % p.hblocks, n = t3 / p.hblocks;
+                for (int u = u0; u < u1; u++) {
+                    if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, p.err, 0x900u + s, abortp)) { ok = false; break; }
+                    const uint32_t full = smem_u32(&bar_full[s]);
+                    mbar_expect_tx(full, bytes);
+                    const uint32_t a_dst = tiles_base + (uint32_t)s * (uint32_t)p.stage_bytes;
+                    const uint32_t b_dst = a_dst + (uint32_t)(SHIFT ? p.G : 4) * (uint32_t)p.a_stride;
+                    const int w0 = tw * p.TW, h0 = hb * p.R;
+                    if (!SHIFT) {
+                        for (int c = 0; c < nA; c++) tma_4d(a_dst + (uint32_t)(c * p.a_stride), &tmDy, co0 + 32 * c, w0, h0, n, full);
+                        for (int c = 0; c < nB; c++) tma_4d(b_dst + (uint32_t)(c * p.b_stride), &tmX, ci0 + 32 * c, w0 - p.pad, h0 + kh0 - p.pad, n, full);
+                    } else {
+                        for (int c = 0; c < nA; c++) tma_4d(a_dst + (uint32_t)(c * p.a_stride), &tmX, ci0 + 32 * c, w0 - p.pad, h0 - p.pad, n, full);
+                        for (int c = 0; c < nB; c++) tma_4d(b_dst + (uint32_t)(c * p.b_stride), &tmDy, co0 + 32 * c, w0, h0, n, full);
+                    }
+                    if (++tw == p.tiles_w) { tw = 0; if (++hb == p.hblocks) { hb = 0; n++; } }
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1 || warp >= 6) {
+        // ---------------- MMA issuers: warps 1, 6, 7; each owns one accumulator block (a filter column kw, or a filter
+        // row kh when SHIFT).  MMAs into one accumulator must come from one thread to stay ordered; different
+        // accumulators may be issued in parallel, which is what keeps the tensor pipe fed: one thread issues an MMA
+        // with fresh descriptors only every hundred-odd cycles, more than an N <= 128 MMA takes.  The whole warp runs
+        // the loop, lane 0 issues.
+        const int iss = warp == 1 ? 0 : warp - 5;
+        if (iss < p.nissue) {
+            const uint32_t leader = lane == 0 ? 1u : 0u;
+            // MN-major operands: rows are reduction indices (pixels), 128 B = 32 channels each; 4-row swizzle atoms 512 B
+            // apart along the reduction (SBO), 32-channel chunks LBO apart; a k-step is 8 consecutive pixel rows.
+            const uint32_t idesc = idesc_tf32(128u, (uint32_t)p.ncol, true, true);
+            // Every value below is derived from kernel parameters, the block index and warp-wide votes only, and every
+            // branch condition is the same in all lanes: the loop is provably warp-uniform.
+            const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+            const uint64_t dA0 = smem_desc(tiles_base, SHIFT ? 128u : (uint32_t)p.a_stride, 512u, 1u);
+            const uint64_t dB0 = smem_desc(tiles_base + (uint32_t)(SHIFT ? p.G : 4) * (uint32_t)p.a_stride, (uint32_t)p.b_stride, 512u, 1u);
+            const uint32_t a_hi = (uint32_t)(dA0 >> 32), b_hi = (uint32_t)(dB0 >> 32);
+            const uint32_t a_lo0 = (uint32_t)dA0, b_lo0 = (uint32_t)dB0;
+            const uint32_t stage_units = (uint32_t)p.stage_bytes >> 4;   // descriptor start addresses count 16-byte units
+            const uint32_t a_row = SHIFT ? (uint32_t)p.PW * 8u : (uint32_t)p.TW * 8u;   // one image row of the A tile
+            const uint32_t b_row = SHIFT ? (uint32_t)p.TW * 8u : (uint32_t)p.PW * 8u;
+            int s = 0;
+            uint32_t ph = 0, work_iter = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, work_iter++) {
+                const int item = w % p.items, z = w / p.items;
+                int nA = 1;
+                if (SHIFT) {
+                    const int cig = item % p.cigs;
+                    nA = (p.Cin / 32 - cig * p.G) < p.G ? (p.Cin / 32 - cig * p.G) : p.G;
+                }
+                const int u0 = z * p.units_per_split;
+                const int u1 = (u0 + p.units_per_split) < p.units_total ? (u0 + p.units_per_split) : p.units_total;
+                ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_acc_empty), (work_iter & 1u) ^ 1u, p.err, 0xA00u, abortp));
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t accum = 0u;
+                for (int u = u0; u < u1; u++) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_full[s]), ph, p.err, 0xB00u + s, abortp));
+                    if (!ok) break;
+                    tc_fence_after();
+                    uint32_t a_r = a_lo0 + (uint32_t)s * stage_units, b_r = b_lo0 + (uint32_t)s * stage_units;
+                    for (int r = 0; r < p.R; r++, a_r += a_row, b_r += b_row) {
+                        uint32_t a_k = a_r, b_k = b_r;
+                        for (int wk = 0; wk < ksteps_w; wk++, a_k += 64u, b_k += 64u) {   // 8 pixel rows of 128 B
+                            if (!SHIFT) {
+                                // this issuer's filter column: B start moved by `iss` pixel rows, accumulator block `iss`
+                                umma_tf32_w(tmem_u + (uint32_t)(iss * 128), ((uint64_t)a_hi << 32) | a_k,
+                                            ((uint64_t)b_hi << 32) | (b_k + (uint32_t)(iss * 8)), idesc, accum, leader);
+                            } else {
+                                // this issuer's filter row: A start moved by `iss` halo lines, accumulators (g, iss)
+                                const uint64_t db = ((uint64_t)b_hi << 32) | b_k;
+                                uint32_t a_g = a_k + (uint32_t)iss * a_row, acc = tmem_u + (uint32_t)(iss * p.ncol);
+                                for (int g = 0; g < nA; g++, a_g += (uint32_t)p.a_stride >> 4, acc += (uint32_t)(p.kH * p.ncol))
+                                    umma_tf32_w(acc, ((uint64_t)a_hi << 32) | a_g, db, idesc, accum, leader);
+                            }
+                            accum = 1u;
+                        }
+                    }
+                    umma_commit_w(smem_u32(&bar_empty[s]), leader);
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+                if (ok) umma_commit_w(smem_u32(&bar_acc_full), leader);
+            }
+        }
+    } else {
+        // ---------------- epilogue: accumulators -> partial[z] ----------------
+        const int q = warp & 3;
+        const int r = q * 32 + lane;
+        const int ntaps = p.kH * p.kW;
+        const size_t row_len = (size_t)ntaps * p.Cin;
+        uint32_t work_iter = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < total_work; w += gridDim.x, work_iter++) {
+            const int item = w % p.items, z = w / p.items;
+            ok = mbar_wait(smem_u32(&bar_acc_full), work_iter & 1u, p.err, 0xC00u, abortp);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16);
+            float* pz = p.partial + (size_t)z * p.Cout * row_len;
+            if (!SHIFT) {
+                const int kh0 = item % p.kH;
+                const int t2 = item / p.kH;
+                const int ci0 = (t2 % p.cigs) * 128, co = (t2 / p.cigs) * 128 + r;
+                const bool co_ok = co < p.Cout;
+                for (int kw = 0; kw < p.kW; kw++) {
+                    float* dst = pz + (size_t)co * row_len + (size_t)(kh0 * p.kW + kw) * p.Cin + ci0;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < 128; c0 += 32) {
+                        uint32_t v[32];
+                        tmem_ld32(acc + (uint32_t)(kw * 128 + c0), v);
+                        tmem_ld_wait();
+                        if (co_ok) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<float4*>(dst + c0 + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                                       __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                        }
+                    }
+                }
+            } else {
+                // lane r = (pixel shift kw = q, input channel lane); columns = output channels
+                const int cig = item % p.cigs;
+                const int co0 = (item / p.cigs) * p.ncol;
+                const int nA = (p.Cin / 32 - cig * p.G) < p.G ? (p.Cin / 32 - cig * p.G) : p.G;
+                if (q < p.kW) {
+                    for (int g = 0; g < nA; g++) {
+                        const int ci = (cig * p.G + g) * 32 + lane;
+                        for (int kh = 0; kh < p.kH; kh++) {
+                            float* dst = pz + (size_t)co0 * row_len + (size_t)(kh * p.kW + q) * p.Cin + ci;
+#pragma unroll 1
+                            for (int c0 = 0; c0 < p.ncol; c0 += 32) {
+                                uint32_t v[32];
+                                tmem_ld32(acc + (uint32_t)((g * p.kH + kh) * p.ncol + c0), v);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int j = 0; j < 32; j++) dst[(size_t)(c0 + j) * row_len] = __uint_as_float(v[j]);
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(smem_u32(&bar_acc_empty));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) { }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------
+template <bool PXM, int NCH>
+static int convh_launch(const CUtensorMap& tw, const CUtensorMap& tx, ConvhParams& p, int smem, double flops, cudaStream_t st) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        NCC_TRY(cudaFuncSetAttribute(convh_kernel<PXM, NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     2 * 44 * 1024 + 6 * kWTileBytes + 1024));
+        attr_set = true;
+    }
+    const long long total = (long long)p.tiles_px * p.tiles_m;
+    const int sms = ncc::sm_count();
+    const unsigned grid = (unsigned)(total < sms ? total : sms);
+    if (ncc::conv_stats_wanted()) p.stat = ncc::conv_stats_buffer(grid, p.M, st);
+    {
+        ncc::ProfScope prof(ncc::prof_role(), flops, st, true);
+        convh_kernel<PXM, NCH><<<grid, PXM ? (NCH <= 2 ? 288 : 224) : 192, smem, st>>>(tw, tx, p);
+    }
+    NCC_COUNT_LAUNCH();
+    if (p.stat) ncc::conv_stats_publish(p.D, p.M, (long long)(p.tiles_px / (p.tiles_w * p.tiles_h)) * p.Ho * p.Wo, (int)grid, p.stat);
+    return ncc::launch_status("convh_kernel");
+}
+
+int conv_halo_nhwc(float* y, const float* x, const float* wpacked, const float* bias, int N, int H, int W, int Cin, int Cout,
+                   int kH, int kW, int pad, int mode, cudaStream_t st) {
+    const int Ho = H + 2 * pad - kH + 1, Wo = W + 2 * pad - kW + 1;
+    if (mode != NC_CUDA_MATH_TF32) return NC_CUDA_ERR_UNSUPPORTED;   // no operand-conversion stage in this kernel
+    if (kH < 1 || kW < 1 || kH > 3 || kW > 3 || Ho <= 0 || Wo <= 0) return NC_CUDA_ERR_UNSUPPORTED;
+    if ((Cin % 32) || (Cout % 4) || Cout < 16) return NC_CUDA_ERR_UNSUPPORTED;
+    if ((long long)N * Ho * Wo * Cout >= 0x7fffffffLL) return NC_CUDA_ERR_UNSUPPORTED;
+    // Tiles are 8 pixels wide and up to 32 high.  With the channels on M one thread issues all MMAs of a tile, which
+    // only keeps the tensor pipe busy with N = 8 * rows = 256; images lower than 24 rows (16 x 16: N = 128) run faster
+    // on the per-tap kernel, whose 256-pixel boxes span several images.
+    if (Ho < 24) return NC_CUDA_ERR_UNSUPPORTED;
+    // Pixels on M for up to 96 output channels (measured on the 64-channel 64 x 64 layer at batch 256: 447 against 344
+    // TFLOP/s with the channels on M); from 128 channels on, channels on M with N = 256 pixels is the faster shape
+    // (698 against 636 TFLOP/s on the 128-channel 32 x 32 layer).
+    const int ncol = Cout;
+    const bool pxm = (Cout % 32 == 0) && Cout <= 96 && (bias == nullptr || (reinterpret_cast<uintptr_t>(bias) & 15u) == 0) &&
+                     (reinterpret_cast<uintptr_t>(y) & 15u) == 0;
+    CUtensorMap tw, tx;
+    unsigned long long wd[2] = {(unsigned long long)Cin, (unsigned long long)kH * kW * Cout};
+    unsigned long long ws[1] = {(unsigned long long)Cin};
+    unsigned wb[2] = {32, (unsigned)(pxm ? ncol : 128)};
+    if (!make_map(&tw, wpacked, 2, wd, ws, wb, false)) return NC_CUDA_ERR_UNSUPPORTED;
+    unsigned long long dims[4] = {(unsigned long long)Cin, (unsigned long long)W, (unsigned long long)H, (unsigned long long)N};
+    unsigned long long str[3] = {(unsigned long long)Cin, (unsigned long long)W * Cin, (unsigned long long)H * W * Cin};
+    unsigned box[4] = {32, (unsigned)(kTW + kW - 1), (unsigned)(kTH + kH - 1), 1};
+    if (!make_map(&tx, x, 4, dims, str, box, false)) return NC_CUDA_ERR_UNSUPPORTED;
+    ConvhParams p = {};
+    p.D = y; p.ldd = Cout; p.bias = bias; p.M = Cout;
+    p.Ho = Ho; p.Wo = Wo;
+    p.tiles_w = (Wo + kTW - 1) / kTW; p.tiles_h = (Ho + kTH - 1) / kTH;
+    p.tiles_px = N * p.tiles_w * p.tiles_h;
+    p.tiles_m = pxm ? Cout / ncol : (Cout + kBM - 1) / kBM;
+    p.kH = kH; p.kW = kW; p.pad = pad;
+    p.cchunks = Cin / 32;
+    p.wrows = Cout;
+    p.wbox_bytes = (pxm ? ncol : 128) * 128;
+    p.wslot_bytes = (kW * p.wbox_bytes + 1023) & ~1023;
+    p.wstages = 6 * kWTileBytes / p.wslot_bytes;
+    if (p.wstages > kConvhWStages) p.wstages = kConvhWStages;
+    p.pitch = kTW + kW - 1;
+    p.halo_bytes = p.pitch * (kTH + kH - 1) * 128;
+    p.halo_stride = (p.halo_bytes + 1023) & ~1023;
+    p.err = ncc::device_error_word();
+    const int smem = 2 * p.halo_stride + 6 * kWTileBytes + 1024;
+    const double flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
+    if (pxm) {
+        switch (ncol / 32) {
+            case 1: return convh_launch<true, 1>(tw, tx, p, smem, flops, st);
+            case 2: return convh_launch<true, 2>(tw, tx, p, smem, flops, st);
+            case 3: return convh_launch<true, 3>(tw, tx, p, smem, flops, st);
+        }
+    }
+    return convh_launch<false, 0>(tw, tx, p, smem, flops, st);
+}
+
+// Pixel tile of the weight-gradient kernels: TW pixels (a multiple of 8, at most 64) by R image rows per stage, chosen
+// to waste the fewest tensor-core cycles on pixels beyond the image edge while at least `min_stages` stages fit.
+static bool pick_dw_tile(int Wo, int Ho, int kW, int halo_rows, int nchunk_dy, int nchunk_x, int* TW, int* R, int* stage_bytes,
+                         int* a_stride_dy, int* b_stride_x) {
+    double best = -1.0;
+    for (int tw = 8; tw <= 64; tw += 8) {
+        const int tiles_w = (Wo + tw - 1) / tw;
+        for (int r = 1; r <= 8; r *= 2) {
+            if (tw * r > 256 || (r > 1 && r > Ho)) continue;
+            const int dy_stride = ((tw * r * 128) + 1023) & ~1023;
+            const int x_stride = (((tw + kW - 1) * (r + halo_rows) * 128 + 256) + 1023) & ~1023;   // + two rows: the unused shifts read past the last line
+            const int sb = nchunk_dy * dy_stride + nchunk_x * x_stride;
+            if (sb * 3 > kMaxDynSmem - 1024) continue;
+            const int hblocks = (Ho + r - 1) / r;
+            const double useful = (double)Wo * Ho / ((double)tiles_w * tw * hblocks * r);
+            // prefer useful pixels, then less halo re-read, then larger stages (fewer barrier round trips)
+            const double score = useful * 1000.0 - (double)(r + halo_rows) / r * 10.0 + (tw * r >= 64 ? 1.0 : 0.0) + tw * r * 1e-3;
+            if (score > best) { best = score; *TW = tw; *R = r; *stage_bytes = sb; *a_stride_dy = dy_stride; *b_stride_x = x_stride; }
+        }
+    }
+    return best >= 0.0;
+}
+
+int conv_dw_halo_nhwc(float* dW, const float* dy, const float* x, int N, int H, int W, int Cin, int Cout, int kH, int kW, int pad,
+                      int mode, cudaStream_t st) {
+    const int Ho = H + 2 * pad - kH + 1, Wo = W + 2 * pad - kW + 1;
+    if (mode != NC_CUDA_MATH_TF32) return NC_CUDA_ERR_UNSUPPORTED;
+    if (kH < 1 || kW < 2 || kH > 3 || kW > 3 || Ho <= 0 || Wo <= 0) return NC_CUDA_ERR_UNSUPPORTED;
+    if ((Cin % 32) || (Cout % 32)) return NC_CUDA_ERR_UNSUPPORTED;
+    if ((long long)N * Ho * Wo < 4096) return NC_CUDA_ERR_UNSUPPORTED;   // too few pixels to split over the GPU
+    const bool shift = (Cin % 128) != 0;
+    DwhParams p = {};
+    p.Cout = Cout; p.Cin = Cin; p.kH = kH; p.kW = kW; p.pad = pad;
+    int dy_stride = 0, x_stride = 0;
+    if (!shift) {
+        p.ncol = 128; p.G = 4;
+        p.cigs = Cin / 128;
+        p.items = ((Cout + 127) / 128) * p.cigs * kH;
+        if (!pick_dw_tile(Wo, Ho, kW, 0, 4, 4, &p.TW, &p.R, &p.stage_bytes, &dy_stride, &x_stride)) return NC_CUDA_ERR_UNSUPPORTED;
+        p.a_stride = dy_stride; p.b_stride = x_stride;
+    } else {
+        // one accumulator per (input chunk, filter row): kH * G * ncol <= 512 columns
+        p.ncol = Cout >= 128 ? 128 : Cout;            // Cout % 32 == 0: 32, 64, 96 or 128
+        if (Cout > 128 && Cout % 128) return NC_CUDA_ERR_UNSUPPORTED;
+        p.G = (kH * 2 * p.ncol <= 512 && Cin >= 64) ? 2 : 1;
+        p.cigs = (Cin / 32 + p.G - 1) / p.G;
+        p.items = (Cout / p.ncol) * p.cigs;
+        if (!pick_dw_tile(Wo, Ho, kW, kH - 1, p.ncol / 32, p.G, &p.TW, &p.R, &p.stage_bytes, &dy_stride, &x_stride)) return NC_CUDA_ERR_UNSUPPORTED;
+        p.a_stride = x_stride; p.b_stride = dy_stride;
+    }
+    p.PW = p.TW + kW - 1;
+    p.nissue = shift ? kH : kW;
+    p.tiles_w = (Wo + p.TW - 1) / p.TW;
+    p.hblocks = (Ho + p.R - 1) / p.R;
+    p.units_total = N * p.hblocks * p.tiles_w;
+    const int dy_bytes = p.TW * p.R * 128, x_bytes = p.PW * (p.R + (shift ? kH - 1 : 0)) * 128;
+    p.a_bytes = shift ? x_bytes : dy_bytes;
+    p.b_bytes = shift ? dy_bytes : x_bytes;
+    p.stages = (kMaxDynSmem - 1024) / p.stage_bytes;
+    if (p.stages > kDwhMaxStages) p.stages = kDwhMaxStages;
+    if (p.stages < 2) return NC_CUDA_ERR_UNSUPPORTED;
+    const int sms = ncc::sm_count();
+    int splits = sms / p.items;
+    if (splits < 1) splits = 1;
+    if (splits > p.units_total / 4) splits = p.units_total / 4 > 0 ? p.units_total / 4 : 1;
+    p.units_per_split = (p.units_total + splits - 1) / splits;
+    p.splits = (p.units_total + p.units_per_split - 1) / p.units_per_split;
+    const size_t partial_bytes = sizeof(float) * (size_t)p.splits * Cout * kH * kW * Cin;
+    if (partial_bytes > (size_t)512 << 20) return NC_CUDA_ERR_UNSUPPORTED;
+    p.partial = (float*)ncc::scratch(2, partial_bytes, st);
+    if (!p.partial) return NC_CUDA_ERR_RUNTIME;
+    p.err = ncc::device_error_word();
+    CUtensorMap tdy, tx;
+    {
+        unsigned long long dims[4] = {(unsigned long long)Cout, (unsigned long long)Wo, (unsigned long long)Ho, (unsigned long long)N};
+        unsigned long long str[3] = {(unsigned long long)Cout, (unsigned long long)Wo * Cout, (unsigned long long)Ho * Wo * Cout};
+        unsigned box[4] = {32, (unsigned)p.TW, (unsigned)p.R, 1};
+        if (!make_map(&tdy, dy, 4, dims, str, box, true)) return NC_CUDA_ERR_UNSUPPORTED;
+        unsigned long long xd[4] = {(unsigned long long)Cin, (unsigned long long)W, (unsigned long long)H, (unsigned long long)N};
+        unsigned long long xs[3] = {(unsigned long long)Cin, (unsigned long long)W * Cin, (unsigned long long)H * W * Cin};
+        unsigned xbox[4] = {32, (unsigned)p.PW, (unsigned)(p.R + (shift ? kH - 1 : 0)), 1};
+        if (!make_map(&tx, x, 4, xd, xs, xbox, true)) return NC_CUDA_ERR_UNSUPPORTED;
+    }
+    const int smem = p.stages * p.stage_bytes + 1024;
+    const long long total = (long long)p.items * p.splits;
+    const unsigned grid = (unsigned)(total < sms ? total : sms);
+    const double flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
+    static bool attr_set[2] = {false, false};
+    if (!attr_set[shift ? 1 : 0]) {
+        if (shift) NCC_TRY(cudaFuncSetAttribute(dwh_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
+        else NCC_TRY(cudaFuncSetAttribute(dwh_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
+        attr_set[shift ? 1 : 0] = true;
+    }
+    {
+        ncc::ProfScope prof(ncc::prof_role(), flops, st, true);
+        if (shift) dwh_kernel<true><<<grid, 256, smem, st>>>(tdy, tx, p);
+        else dwh_kernel<false><<<grid, 256, smem, st>>>(tdy, tx, p);
+    }
+    NCC_COUNT_LAUNCH();
+    const int rc = ncc::launch_status("dwh_kernel");
+    if (rc) return rc;
+    return dw_reduce(dW, p.partial, p.splits, Cout, Cin, kH, kW, st);
+}
+
+}  // namespace tc

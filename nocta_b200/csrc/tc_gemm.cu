@@ -1,6 +1,6 @@
 // Tensor-core contractions for sm_100a: TMA-fed, tcgen05.mma (kind::tf32) with the accumulator in
-// tensor memory, written with inline PTX.  tc_kernel serves four problem kinds; convh_kernel (further down) is the
-// halo-resident convolution used for forward / input gradient wherever whole 8 x 32 pixel tiles fit.
+// tensor memory, written with inline PTX.  tc_kernel serves four problem kinds; the halo-resident convolution and
+// weight-gradient kernels, which take the stride-1 filters up to 3 x 3 in plain TF32 mode, live in tc_conv.cu.
 //
 //   GEMM   D(M,N) = A * B^T        either operand K-major or MN-major in memory
 //   CONV   channels-last implicit GEMM, stride 1: rows = 128 output pixels (a w x h x n box),
@@ -25,6 +25,7 @@
 //
 // No cluster launch and no multicast anywhere: each CTA loads its own tiles.
 #include "tc_gemm.cuh"
+#include "tc_ptx.cuh"
 #include "../../include/nocta_cuda.h"
 
 namespace tc {
@@ -49,123 +50,13 @@ struct TcParams {
     int cchunks;           // CONV: 32-channel chunks of the reduction channels
     int wrows;             // CONV: rows per (kh,kw) block of the packed weights (= output channels)
     int Cin;               // DW: input channels (column index -> (shift, ci))
-    int desc_variant;
     int lbw, lbh;                  // CONVT: log2 of the pixel box width / height
     int tiles_m, tiles_n, splits;  // persistent tile walk
     int stages;                    // operand ring depth
     double* stat;                  // CONVT, non-null: per CTA and channel (sum, sum of squares) of the output it wrote, [gridDim.x][M][2]
     unsigned int* err;
+    double flops;                  // host only: algorithmic FLOPs of the launch, for the profiling scope
 };
-
-// Experiment switch (nc_cuda_debug_desc_variant), 0 in production.  1..6: cap the operand ring of tc_kernel at that
-// many stages; 7: network-input convolutions (<= 8 channels) on the halo-resident kernel instead of the CUDA-core
-// first-layer kernel; 8: allow 16 x 16 halo tiles; 9: never use the halo-resident kernel.
-static int g_desc_variant = 0;
-void set_desc_variant(int v) { g_desc_variant = v; }
-
-// ------------------------------------------------------------------------------------------
-// PTX wrappers
-// ------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-// Bounded wait (about half a second).  Returns false and records `code` when it gives up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int* err, unsigned int code,
-                                          volatile int* abort_flag) {
-    if (mbar_test(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
-    unsigned int spins = 0;
-    while (true) {
-        if (mbar_test(bar, parity)) return true;
-        if ((++spins & 255u) == 0) {
-            if (*abort_flag) return false;
-            if (global_ns() - t0 > 500000000ull) {
-                *abort_flag = 1;
-                if (err) atomicCAS(err, 0u, code);
-                return false;
-            }
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap* tm, int c0, int c1, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(c0), "r"(c1), "r"(bar)
-        : "memory");
-}
-__device__ __forceinline__ void tma_4d(uint32_t dst, const CUtensorMap* tm, int c0, int c1, int c2, int c3, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
-        : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, Blackwell descriptor version 1.  Start address, leading byte
-// offset and stride byte offset are encoded in 16-byte units.  layout: 2 = 128-byte swizzle on
-// 16-byte units (K-major operands), 1 = 128-byte swizzle on 32-byte units, the only swizzled
-// layout the tensor core accepts for MN-major 32-bit operands.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr >> 4) & 0x3FFFu);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-    d |= (uint64_t)1 << 46;  // descriptor version
-    d |= (uint64_t)layout << 61;
-    return d;
-}
 
 // ------------------------------------------------------------------------------------------
 // The kernel
@@ -724,276 +615,6 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
 }
 
 // ------------------------------------------------------------------------------------------
-// CONVH: stride-1 convolution (filters up to 3 x 3) with the activation halo resident in shared memory
-// ------------------------------------------------------------------------------------------
-// The operand traffic from L2 into shared memory, not the tensor pipe, bounds the kernel above for
-// convolutions: every filter tap re-reads the same pixels.  Here a CTA owns a 16 x 16 pixel tile of one
-// image and up to 128 output channels.  Per 32-channel chunk it loads the (16+kH-1) x (16+kW-1) halo
-// ONCE (one 4-D TMA box, zero fill = padding) and issues the MMAs of all kH*kW taps against it: the B
-// operand of tap (kh, kw) is the same shared-memory buffer with the descriptor start moved by
-// (kh * pitch + kw) pixel rows of 128 bytes (the 128-byte swizzle is a function of the absolute shared
-// address, so a start that is not 1024-byte aligned needs no correction), 8-row groups one halo line
-// (pitch rows) apart.  The 16 x 16 tile is two MMAs of N = 128 (left and right 8 columns).  Only the
-// 16 KB weight tile of a tap streams per 512 MMA cycles: about 40 bytes per cycle instead of 96.
-constexpr int kConvhWStages = 6;
-struct ConvhParams {
-    float* D;
-    int ldd;
-    const float* bias;
-    int M;                 // output channels
-    int Ho, Wo;
-    int tiles_w, tiles_h;  // pixel tiles per image
-    int tiles_px;          // pixel tiles in total (images * tiles_h * tiles_w)
-    int tiles_m;           // 128-channel tiles
-    int kH, kW, pad;
-    int cchunks;           // 32-channel chunks of the input channels
-    int wrows;             // rows per tap in the packed weights
-    int pitch;             // halo line pitch in pixels
-    int halo_bytes, halo_stride;
-    double* stat;          // non-null: per CTA and channel (sum, sum of squares) of the output it wrote, [gridDim.x][M][2]
-    int ksteps;            // MMA k-steps (of 8 channels) per chunk: 4, or fewer when the real channel count is small
-    int wtap_bytes;        // > 0: the weights of ALL taps stay resident in shared memory, this many bytes per tap
-                           //      (wrows rows of 128 B; one chunk only), loaded once per CTA instead of streaming
-    unsigned int* err;
-};
-
-// FEW: the few-channel variant (weights of all taps resident, p.ksteps MMAs per tap) is a separate instantiation so
-// that the single-thread issue loops of the production kernel carry none of its branches.
-template <int TW, int TH, bool FEW = false>  // pixel tile: 16 x 16 (two MMAs of N = 128 per k-step) or 8 x 32 (one MMA of N = 256)
-__global__ void __launch_bounds__(192, 1)
-convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const ConvhParams p) {
-    static_assert(TW * TH == 256 && TW % 8 == 0, "256 pixels per tile");
-    constexpr int WS = kConvhWStages;
-    constexpr int NSUB = TW / 8, NMMA = 8 * TH;  // MMAs per k-step and their N
-    extern __shared__ uint8_t dyn_smem[];
-    __shared__ __align__(8) uint64_t bar_hfull[2];
-    __shared__ __align__(8) uint64_t bar_hempty[2];
-    __shared__ __align__(8) uint64_t bar_wfull[WS];
-    __shared__ __align__(8) uint64_t bar_wempty[WS];
-    __shared__ __align__(8) uint64_t bar_acc_full[2];
-    __shared__ __align__(8) uint64_t bar_acc_empty[2];
-    __shared__ uint32_t tmem_slot;
-    __shared__ int abort_flag;
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t halo_base = (smem_u32(dyn_smem) + 1023u) & ~1023u;
-    const uint32_t w_base = halo_base + 2u * (uint32_t)p.halo_stride;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < 2; s++) {
-            mbar_init(smem_u32(&bar_hfull[s]), 1);
-            mbar_init(smem_u32(&bar_hempty[s]), 1);
-            mbar_init(smem_u32(&bar_acc_full[s]), 1);
-            mbar_init(smem_u32(&bar_acc_empty[s]), 128);
-        }
-        for (int s = 0; s < WS; s++) {
-            mbar_init(smem_u32(&bar_wfull[s]), 1);
-            mbar_init(smem_u32(&bar_wempty[s]), 1);
-        }
-        abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(512u)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = tmem_slot;
-    volatile int* abortp = &abort_flag;
-    const int total_tiles = p.tiles_px * p.tiles_m;  // t -> (pixel tile fastest, then channel tile)
-    const int ntaps = p.kH * p.kW;
-
-    if (warp == 0) {
-        if (lane == 0) {
-            // ---------------- producer: halo boxes (one chunk ahead) and weight tiles ----------------
-            int ht = blockIdx.x, hcc = 0;   // cursor of the next halo to request
-            uint32_t hcount = 0;
-            bool ok = true;
-            auto issue_halo = [&]() {
-                if (ht >= total_tiles || !ok) return;
-                const uint32_t slot = hcount & 1u;
-                if (!mbar_wait(smem_u32(&bar_hempty[slot]), ((hcount >> 1) & 1u) ^ 1u, p.err, 0x600u + slot, abortp)) { ok = false; return; }
-                const int pt = ht % p.tiles_px;
-                const int tw = pt % p.tiles_w, tt = pt / p.tiles_w;
-                const int th = tt % p.tiles_h, n = tt / p.tiles_h;
-                const uint32_t full = smem_u32(&bar_hfull[slot]);
-                mbar_expect_tx(full, (uint32_t)p.halo_bytes);
-                tma_4d(halo_base + slot * (uint32_t)p.halo_stride, &tmX, hcc * 32, tw * TW - p.pad, th * TH - p.pad, n, full);
-                hcount++;
-                if (++hcc == p.cchunks) { hcc = 0; ht += gridDim.x; }
-            };
-            int lead = WS < ntaps - 1 ? WS : ntaps - 1;  // weight tap after which the next halo is requested
-            if (lead < 0) lead = 0;
-            int s = 0;
-            uint32_t ph = 0;
-            if (FEW) {
-                // all taps once, then only halos: one per tile, requested one tile ahead
-                const uint32_t full = smem_u32(&bar_wfull[0]);
-                mbar_expect_tx(full, (uint32_t)(ntaps * p.wtap_bytes));
-                for (int tap = 0; tap < ntaps; tap++) tma_2d(w_base + (uint32_t)(tap * p.wtap_bytes), &tmW, 0, tap * p.wrows, full);
-                issue_halo();
-                for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) issue_halo();
-            } else {
-            issue_halo();
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const int m0 = (t / p.tiles_px) * BM;
-                for (int cc = 0; cc < p.cchunks && ok; cc++) {
-                    int wrow = m0;
-                    for (int tap = 0; tap < ntaps; tap++, wrow += p.wrows) {
-                        if (tap == lead) issue_halo();
-                        if (!ok) break;
-                        if (!mbar_wait(smem_u32(&bar_wempty[s]), ph ^ 1u, p.err, 0x100u + s, abortp)) { ok = false; break; }
-                        const uint32_t full = smem_u32(&bar_wfull[s]);
-                        mbar_expect_tx(full, (uint32_t)A_BYTES);
-                        tma_2d(w_base + (uint32_t)s * A_BYTES, &tmW, cc * 32, wrow, full);
-                        if (++s == WS) { s = 0; ph ^= 1u; }
-                    }
-                }
-            }
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0) {
-            // ---------------- MMA issuer ----------------
-            // D = f32, A = B = tf32, both K-major, M = 128
-            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(NMMA >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-            const uint64_t da0 = smem_desc(w_base, 16u, 1024u, 2u);
-            const uint64_t db0 = smem_desc(halo_base, 16u, (uint32_t)p.pitch * 128u, 2u);
-            int s = 0;
-            uint32_t ph = 0, tile_iter = 0, hcount = 0;
-            bool ok = true;
-            constexpr bool resident = FEW;
-            if (resident && total_tiles > (int)blockIdx.x)
-                ok = mbar_wait(smem_u32(&bar_wfull[0]), 0u, p.err, 0x200u, abortp);
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, tile_iter++) {
-                const uint32_t ab = tile_iter & 1u;
-                if (!mbar_wait(smem_u32(&bar_acc_empty[ab]), ((tile_iter >> 1) & 1u) ^ 1u, p.err, 0x500u + ab, abortp)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t acc = tmem_base + ab * 256u;
-                for (int cc = 0; cc < p.cchunks && ok; cc++, hcount++) {
-                    const uint32_t slot = hcount & 1u;
-                    if (!mbar_wait(smem_u32(&bar_hfull[slot]), (hcount >> 1) & 1u, p.err, 0x700u + slot, abortp)) { ok = false; break; }
-                    const uint64_t dbs = db0 + (uint64_t)((slot * (uint32_t)p.halo_stride) >> 4);
-                    int kh = 0, kw = 0;
-                    for (int tap = 0; tap < ntaps; tap++) {
-                        if (!resident && !mbar_wait(smem_u32(&bar_wfull[s]), ph, p.err, 0x200u + s, abortp)) { ok = false; break; }
-                        tc_fence_after();
-                        const uint64_t da = da0 + (uint64_t)((resident ? (uint32_t)(tap * p.wtap_bytes) : (uint32_t)s * (uint32_t)A_BYTES) >> 4);
-                        const uint64_t db = dbs + (uint64_t)(((uint32_t)(kh * p.pitch + kw) * 128u) >> 4);
-#pragma unroll
-                        for (int ks = 0; ks < BK / 8; ks++) {
-                            if (FEW && ks >= p.ksteps) break;
-                            const uint32_t accum = (uint32_t)((cc | tap | ks) != 0);
-#pragma unroll
-                            for (int sub = 0; sub < NSUB; sub++)  // sub-tile of 8 columns: + 8 pixel rows in the halo
-                                umma_tf32(acc + (uint32_t)(sub * NMMA), da + (uint64_t)(ks * 2), db + (uint64_t)(ks * 2 + sub * 64), idesc, accum);
-                        }
-                        if (!resident) {
-                            umma_commit(smem_u32(&bar_wempty[s]));
-                            if (++s == WS) { s = 0; ph ^= 1u; }
-                        }
-                        if (++kw == p.kW) { kw = 0; kh++; }
-                    }
-                    if (ok) umma_commit(smem_u32(&bar_hempty[slot]));
-                }
-                if (ok) umma_commit(smem_u32(&bar_acc_full[ab]));
-            }
-        }
-    } else {
-        // ---------------- epilogue warps: lane = output channel, column = pixel ----------------
-        const int q = warp & 3;
-        const int r = q * 32 + lane;
-        uint32_t tile_iter = 0;
-        bool ok = true;
-        // Output statistics: a thread owns channel m0 + r of every tile it sees, so it keeps one running pair per
-        // channel tile and writes it once (slab = this CTA): stat[blockIdx.x][M][2].  Slots of channel tiles this
-        // CTA never visits must read zero, so the thread clears all of its slots first.
-        double ssum = 0.0, ssq = 0.0;
-        int stat_m0 = -1;
-        if (p.stat)
-            for (int mt = 0; mt < p.tiles_m; mt++)
-                if (mt * BM + r < p.M) {
-                    double* sd = p.stat + ((size_t)blockIdx.x * p.M + mt * BM + r) * 2;
-                    sd[0] = 0.0; sd[1] = 0.0;
-                }
-        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, tile_iter++) {
-            const int pt = t % p.tiles_px, m0 = (t / p.tiles_px) * BM;
-            if (p.stat && m0 != stat_m0) {
-                if (stat_m0 >= 0 && stat_m0 + r < p.M) {
-                    double* sd = p.stat + ((size_t)blockIdx.x * p.M + stat_m0 + r) * 2;
-                    sd[0] = ssum; sd[1] = ssq;
-                }
-                ssum = 0.0; ssq = 0.0; stat_m0 = m0;
-            }
-            const int tw = pt % p.tiles_w, tt = pt / p.tiles_w;
-            const int th = tt % p.tiles_h, n = tt / p.tiles_h;
-            const uint32_t ab = tile_iter & 1u;
-            ok = mbar_wait(smem_u32(&bar_acc_full[ab]), (tile_iter >> 1) & 1u, p.err, 0x400u + ab, abortp);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t acc = tmem_base + ab * 256u + ((uint32_t)(q * 32) << 16);
-            const int co = m0 + r;
-            const bool co_ok = co < p.M;
-            const float bv = (co_ok && p.bias) ? p.bias[co] : 0.f;
-            // first pixel of the tile; a column chunk of 32 = 4 lines x 8 pixels of one 8-column sub-tile
-            float* tile_dst = p.D + (((long long)n * p.Ho + th * TH) * p.Wo + tw * TW) * p.ldd + co;
-            const int line = p.Wo * p.ldd;  // elements between image rows (< 2^31 checked by the host)
-#pragma unroll 1
-            for (int c0 = 0; c0 < 256; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(acc + (uint32_t)c0, v);
-                tmem_ld_wait();
-                if (c0 == 224) {
-                    tc_fence_before();
-                    mbar_arrive(smem_u32(&bar_acc_empty[ab]));
-                }
-                if (!co_ok) continue;
-                const int sub = c0 / NMMA, h4 = (c0 % NMMA) >> 3;
-                float* dst = tile_dst + (long long)h4 * line + sub * 8 * p.ldd;
-#pragma unroll
-                for (int hh = 0; hh < 4; hh++) {
-#pragma unroll
-                    for (int j = 0; j < 8; j++) dst[j * p.ldd] = __uint_as_float(v[hh * 8 + j]) + bv;
-                    dst += line;
-                }
-                if (p.stat) {  // uniform over the CTA
-                    float fs = 0.f, fq = 0.f;
-#pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const float o = __uint_as_float(v[j]) + bv;
-                        fs += o;
-                        fq = fmaf(o, o, fq);
-                    }
-                    ssum += (double)fs;
-                    ssq += (double)fq;
-                }
-            }
-        }
-        if (p.stat && stat_m0 >= 0 && stat_m0 + r < p.M) {
-            double* sd = p.stat + ((size_t)blockIdx.x * p.M + stat_m0 + r) * 2;
-            sd[0] = ssum; sd[1] = ssq;
-        }
-    }
-
-    tc_fence_before();
-    __syncthreads();
-    if (abort_flag) {
-        const unsigned long long t0 = global_ns();
-        while (global_ns() - t0 < 2000000ull) { }
-        __syncthreads();
-    }
-    if (warp == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
-    }
-}
-
-// ------------------------------------------------------------------------------------------
 // Second stages and weight packing
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(float* __restrict__ D, long long ldd, const float* __restrict__ partial,
@@ -1050,68 +671,12 @@ __global__ void __launch_bounds__(256) pack_weights_kernel(float* __restrict__ w
 // ------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)sym;
-    }
-    return fn;
-}
-
-// rank-2..4 f32 tensor map with 128-byte swizzle; dims/box innermost first, strides in elements for dims 1..
-static bool make_map(CUtensorMap* tm, const float* base, int rank, const unsigned long long* dims,
-                     const unsigned long long* strides_elems, const unsigned* box, bool mn_major) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    if (reinterpret_cast<uintptr_t>(base) & 15u) return false;
-    cuuint64_t gdim[4], gstr[3];
-    cuuint32_t bdim[4], estr[4];
-    for (int i = 0; i < rank; i++) {
-        gdim[i] = dims[i];
-        bdim[i] = box[i];
-        estr[i] = 1;
-        if (dims[i] == 0 || box[i] == 0 || box[i] > 256) return false;
-    }
-    for (int i = 0; i + 1 < rank; i++) {
-        gstr[i] = strides_elems[i] * 4ull;
-        if (gstr[i] % 16 != 0) return false;
-    }
-    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<float*>(base), gdim, gstr, bdim, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
-}
-
-// Optional per-launch timing of the tensor-core kernel (CUDA events on the launching stream), used by
-// the benchmark to report achieved TFLOP/s of this kernel inside a real training step.
-struct ProfState {
-    bool on = false;
-    int n = 0, cap = 0;
-    cudaEvent_t* start = nullptr;
-    cudaEvent_t* stop = nullptr;
-    double flops = 0.0;
-    double next_flops = 0.0;  // algorithmic FLOPs of the launch about to be made
-};
-static ProfState g_prof;
-
 template <int BN, bool A_MN, bool B_MN, int MODE>
 static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const TcParams& p_in, dim3 tiles, cudaStream_t st) {
     using Cfg = TileCfg<BN, MODE>;
     TcParams p = p_in;
     p.tiles_n = (int)tiles.x; p.tiles_m = (int)tiles.y; p.splits = (int)tiles.z;
     p.stages = Cfg::STAGES;
-    if (g_desc_variant > 0 && g_desc_variant < p.stages) p.stages = g_desc_variant;  // experiment: shallower ring
     const long long total = (long long)tiles.x * tiles.y * tiles.z;
     const int sms = ncc::sm_count();
     dim3 grid((unsigned)(total < sms ? total : sms), 1, 1);
@@ -1121,13 +686,9 @@ static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const TcPara
         NCC_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         attr_set = true;
     }
-    const bool prof = g_prof.on && g_prof.n < g_prof.cap;
-    if (prof) cudaEventRecord(g_prof.start[g_prof.n], st);
-    kern<<<grid, ProdCfg<A_MN, B_MN, BN>::THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, p);
-    if (prof) {
-        cudaEventRecord(g_prof.stop[g_prof.n], st);
-        g_prof.n++;
-        g_prof.flops += g_prof.next_flops;
+    {
+        ncc::ProfScope prof(ncc::prof_role(), p.flops, st, true);
+        kern<<<grid, ProdCfg<A_MN, B_MN, BN>::THREADS, Cfg::SMEM_BYTES, st>>>(ta, tb, p);
     }
     NCC_COUNT_LAUNCH();
     return ncc::launch_status("tc_kernel");
@@ -1192,7 +753,6 @@ int gemm(float* D, int ldd, const float* A, int lda, bool a_mn, const float* B, 
     p.M = M; p.N = N;
     p.num_k_tiles = (K + BK - 1) / BK;
     p.D = D; p.ldd = ldd; p.bias = bias; p.alpha = alpha; p.beta = beta;
-    p.desc_variant = g_desc_variant;
     p.err = ncc::device_error_word();
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + bn - 1) / bn;
     int splits, kps;
@@ -1203,7 +763,7 @@ int gemm(float* D, int ldd, const float* A, int lda, bool a_mn, const float* B, 
         if (!p.partial) return NC_CUDA_ERR_RUNTIME;
     }
     dim3 grid(tiles_n, tiles_m, splits);
-    g_prof.next_flops = 2.0 * M * (double)N * K;
+    p.flops = 2.0 * M * (double)N * K;
     int rc;
     if (!a_mn && !b_mn) rc = launch_bn<false, false>(bn, mode, ta, tb, p, grid, st);
     else if (!a_mn && b_mn) rc = launch_bn<false, true>(bn, mode, ta, tb, p, grid, st);
@@ -1233,198 +793,14 @@ static void pick_box(int pixels, int Wd, int Hd, int Nd, int* bw, int* bh, int* 
         }
 }
 
-// Halo-resident convolution (convh_kernel): whole 8 x 32 or 16 x 16 pixel tiles, filters up to 3 x 3, plain TF32 mode.
-static bool convh_ok(int N, int H, int W, int Cin, int Cout, int kH, int kW, int pad, int mode) {
-    const int Ho = H + 2 * pad - kH + 1, Wo = W + 2 * pad - kW + 1;
-    if (g_desc_variant == 9) return false;  // experiment switch: use the per-tap kernel
-    if (mode != NC_CUDA_MATH_TF32) return false;
-    if (kH < 1 || kW < 1 || kH > 3 || kW > 3) return false;
-    if (Ho <= 0 || Wo <= 0) return false;
-    // 8 x 32 tiles (one N = 256 MMA per k-step) beat the per-tap kernel; 16 x 16 tiles (two N = 128 MMAs,
-    // which read the A tile twice) do not, so images that only fit those stay on the per-tap kernel
-    // unless the experiment switch asks for them
-    if (!((Ho % 32 == 0 && Wo % 8 == 0) || (g_desc_variant == 8 && Ho % 16 == 0 && Wo % 16 == 0))) return false;
-    if ((Cin % 32) || (Cout % 4) || Cout < 16) return false;
-    if ((long long)N * Ho * Wo * Cout >= 0x7fffffffLL) return false;
-    return true;
-}
-
-template <int TW, int TH>
-static int conv_halo_launch(float* y, const float* x, const float* wpacked, const float* bias, int N, int H, int W, int Cin,
-                            int Cout, int kH, int kW, int pad, cudaStream_t st) {
-    const int Ho = H + 2 * pad - kH + 1, Wo = W + 2 * pad - kW + 1;
-    CUtensorMap tw, tx;
-    unsigned long long wd[2] = {(unsigned long long)Cin, (unsigned long long)kH * kW * Cout};
-    unsigned long long ws[1] = {(unsigned long long)Cin};
-    unsigned wb[2] = {32, 128};
-    if (!make_map(&tw, wpacked, 2, wd, ws, wb, false)) return NC_CUDA_ERR_UNSUPPORTED;
-    unsigned long long dims[4] = {(unsigned long long)Cin, (unsigned long long)W, (unsigned long long)H, (unsigned long long)N};
-    unsigned long long str[3] = {(unsigned long long)Cin, (unsigned long long)W * Cin, (unsigned long long)H * W * Cin};
-    unsigned box[4] = {32, (unsigned)(TW + kW - 1), (unsigned)(TH + kH - 1), 1};
-    if (!make_map(&tx, x, 4, dims, str, box, false)) return NC_CUDA_ERR_UNSUPPORTED;
-    ConvhParams p = {};
-    p.D = y; p.ldd = Cout; p.bias = bias; p.M = Cout;
-    p.Ho = Ho; p.Wo = Wo;
-    p.tiles_w = Wo / TW; p.tiles_h = Ho / TH;
-    p.tiles_px = N * p.tiles_w * p.tiles_h;
-    p.tiles_m = (Cout + BM - 1) / BM;
-    p.kH = kH; p.kW = kW; p.pad = pad;
-    p.cchunks = Cin / 32;
-    p.wrows = Cout;
-    p.pitch = TW + kW - 1;
-    p.halo_bytes = p.pitch * (TH + kH - 1) * 128;
-    p.halo_stride = (p.halo_bytes + 1023) & ~1023;
-    p.ksteps = BK / 8;
-    p.err = ncc::device_error_word();
-    const long long total = (long long)p.tiles_px * p.tiles_m;
-    const int sms = ncc::sm_count();
-    const unsigned grid = (unsigned)(total < sms ? total : sms);
-    if (ncc::conv_stats_wanted()) p.stat = ncc::conv_stats_buffer(grid, Cout, st);
-    const int smem = 2 * p.halo_stride + kConvhWStages * A_BYTES + 1024;
-    static bool attr_set = false;
-    if (!attr_set) {
-        NCC_TRY(cudaFuncSetAttribute(convh_kernel<TW, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     2 * 44 * 1024 + kConvhWStages * A_BYTES + 1024));
-        attr_set = true;
-    }
-    g_prof.next_flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
-    const bool prof = g_prof.on && g_prof.n < g_prof.cap;
-    if (prof) cudaEventRecord(g_prof.start[g_prof.n], st);
-    convh_kernel<TW, TH><<<grid, 192, smem, st>>>(tw, tx, p);
-    if (prof) {
-        cudaEventRecord(g_prof.stop[g_prof.n], st);
-        g_prof.n++;
-        g_prof.flops += g_prof.next_flops;
-    }
-    NCC_COUNT_LAUNCH();
-    if (p.stat) ncc::conv_stats_publish(y, Cout, (long long)N * Ho * Wo, (int)grid, p.stat);
-    return ncc::launch_status("convh_kernel");
-}
-
-static int conv_halo_nhwc(float* y, const float* x, const float* wpacked, const float* bias, int N, int H, int W, int Cin,
-                          int Cout, int kH, int kW, int pad, cudaStream_t st) {
-    const int Ho = H + 2 * pad - kH + 1, Wo = W + 2 * pad - kW + 1;
-    const bool tall = (Ho % 32 == 0 && Wo % 8 == 0), square = (Ho % 16 == 0 && Wo % 16 == 0);
-    if (tall && !(square && g_desc_variant == 8)) return conv_halo_launch<8, 32>(y, x, wpacked, bias, N, H, W, Cin, Cout, kH, kW, pad, st);
-    return conv_halo_launch<16, 16>(y, x, wpacked, bias, N, H, W, Cin, Cout, kH, kW, pad, st);
-}
-
-// ---- few-channel first layer on the halo-resident kernel ----
-// The network input (3 channels) is copied once per call into a channels-last buffer of 128-byte pixel records of
-// which only the first 8 channels are written (channels 3..7 zero; the rest of a record is never read by an MMA:
-// a halo row is an ordinary 128-byte K-major row and only its first k-step, one MMA per tap, is issued).  Letting
-// TMA zero-fill the missing channels of an 8-channel tensor instead was slower than moving whole records.  The weights of all taps (Cout rows of 128 bytes each, 3 real values per row) stay resident in shared
-// memory, so per tile only the halo moves.  Measured on the 256 x 3 x 64 x 64 -> 64 channel layer: 114 us in
-// isolation (copy + pack + kernel) against 127 us for the CUDA-core kernel, but slower than it inside a training
-// step, so the path stays behind the experiment switch.
-__global__ void __launch_bounds__(256) few_channels_to_cl8_kernel(float4* __restrict__ out, const float* __restrict__ in, size_t pixels_per_image,
-                                                                  size_t total_pixels, int W, long long sn, long long sc, long long sh,
-                                                                  long long sw, int C, int round) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t p = (size_t)blockIdx.x * blockDim.x + threadIdx.x; p < total_pixels; p += stride) {
-        const size_t n = p / pixels_per_image, r = p % pixels_per_image;
-        const size_t h = r / (size_t)W, w = r % (size_t)W;
-        const float* src = in + (long long)n * sn + (long long)h * sh + (long long)w * sw;
-        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int c = 0; c < C; c++) { const float t = src[(long long)c * sc]; v[c] = round ? ncc::round_tf32(t) : t; }
-        out[8 * p] = make_float4(v[0], v[1], v[2], v[3]);      // a pixel record is 128 bytes; only its first 32 are ever used
-        out[8 * p + 1] = make_float4(v[4], v[5], v[6], v[7]);
-    }
-}
-// wp[(kh*kW + kw)][co][32]: channels ci < Cin from w (Cout, Cin, kH, kW), the rest zero
-__global__ void __launch_bounds__(256) pack_few_channel_weights_kernel(float* __restrict__ wp, const float* __restrict__ w, int Cout, int Cin,
-                                                                       int kH, int kW, int round) {
-    const int total = kH * kW * Cout * 32;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-        const int ci = i & 31, co = (i >> 5) % Cout, tap = (i >> 5) / Cout;
-        float v = 0.f;
-        if (ci < Cin) {
-            v = w[((size_t)(co * Cin + ci) * kH + tap / kW) * kW + tap % kW];
-            if (round) v = ncc::round_tf32(v);
-        }
-        wp[i] = v;
-    }
-}
-
-bool conv_few_channels_ok(int Cin, int Cout, int kH, int kW, int Ho, int Wo, int mode) {
-    // off unless asked for (experiment switch 7): the CUDA-core first-layer kernel is the default path
-    return g_desc_variant == 7 && mode == NC_CUDA_MATH_TF32 && Cin >= 1 && Cin <= 8 && kH >= 1 && kW >= 1 && kH <= 3 && kW <= 3 &&
-           (Cout == 16 || Cout == 32 || Cout == 64) && Ho > 0 && Wo > 0 && (Ho % 32 == 0) && (Wo % 8 == 0);
-}
-
-// x: (N, Cin, H, W) with arbitrary element strides xs; y channels-last (N, Ho, Wo, Cout); w in the reference layout
-int conv_few_channels(float* y, const float* x, const long long xs[4], const float* w, const float* bias, int N, int H, int W, int Cin,
-                      int Cout, int kH, int kW, int pad, bool round, cudaStream_t st) {
-    constexpr int TW = 8, TH = 32;
-    const int Ho = H + 2 * pad - kH + 1, Wo = W + 2 * pad - kW + 1, ntaps = kH * kW;
-    if ((long long)N * Ho * Wo * Cout >= 0x7fffffffLL) return NC_CUDA_ERR_UNSUPPORTED;
-    const size_t pixels = (size_t)N * H * W;
-    float* x8 = (float*)ncc::scratch(4, sizeof(float) * 32 * pixels, st);
-    float* wp = (float*)ncc::scratch(3, sizeof(float) * 32 * (size_t)ntaps * Cout, st);
-    if (!x8 || !wp) return NC_CUDA_ERR_RUNTIME;
-    few_channels_to_cl8_kernel<<<ncc::grid_for((long long)pixels, 256), 256, 0, st>>>((float4*)x8, x, (size_t)H * W, pixels, W, xs[0], xs[1], xs[2],
-                                                                                    xs[3], Cin, round ? 1 : 0);
-    NCC_COUNT_LAUNCH();
-    pack_few_channel_weights_kernel<<<ncc::grid_for((long long)ntaps * Cout * 32, 256), 256, 0, st>>>(wp, w, Cout, Cin, kH, kW, round ? 1 : 0);
-    NCC_COUNT_LAUNCH();
-    CUtensorMap tw, tx;
-    unsigned long long wd[2] = {32, (unsigned long long)ntaps * Cout};
-    unsigned long long ws[1] = {32};
-    unsigned wb[2] = {32, (unsigned)Cout};
-    if (!make_map(&tw, wp, 2, wd, ws, wb, false)) return NC_CUDA_ERR_UNSUPPORTED;
-    unsigned long long dims[4] = {32, (unsigned long long)W, (unsigned long long)H, (unsigned long long)N};
-    unsigned long long str[3] = {32, (unsigned long long)W * 32, (unsigned long long)H * W * 32};
-    unsigned box[4] = {32, (unsigned)(TW + kW - 1), (unsigned)(TH + kH - 1), 1};
-    if (!make_map(&tx, x8, 4, dims, str, box, false)) return NC_CUDA_ERR_UNSUPPORTED;
-    ConvhParams p = {};
-    p.D = y; p.ldd = Cout; p.bias = bias; p.M = Cout;
-    p.Ho = Ho; p.Wo = Wo;
-    p.tiles_w = Wo / TW; p.tiles_h = Ho / TH;
-    p.tiles_px = N * p.tiles_w * p.tiles_h;
-    p.tiles_m = 1;
-    p.kH = kH; p.kW = kW; p.pad = pad;
-    p.cchunks = 1;
-    p.wrows = Cout;
-    p.pitch = TW + kW - 1;
-    p.halo_bytes = p.pitch * (TH + kH - 1) * 128;
-    p.halo_stride = (p.halo_bytes + 1023) & ~1023;
-    p.ksteps = 1;
-    p.wtap_bytes = Cout * 128;
-    p.err = ncc::device_error_word();
-    const int sms = ncc::sm_count();
-    const unsigned grid = (unsigned)(p.tiles_px < sms ? p.tiles_px : sms);
-    if (ncc::conv_stats_wanted()) p.stat = ncc::conv_stats_buffer(grid, Cout, st);
-    // resident weights: ntaps * Cout rows, plus the rows an M = 128 descriptor of the last tap reaches beyond them
-    const int smem = 2 * p.halo_stride + (ntaps * Cout + (BM - Cout)) * 128 + 1024;
-    if (smem > 2 * 44 * 1024 + kConvhWStages * A_BYTES + 1024) return NC_CUDA_ERR_UNSUPPORTED;
-    static bool attr_set = false;
-    if (!attr_set) {
-        NCC_TRY(cudaFuncSetAttribute(convh_kernel<TW, TH, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     2 * 44 * 1024 + kConvhWStages * A_BYTES + 1024));
-        attr_set = true;
-    }
-    g_prof.next_flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
-    const bool prof = g_prof.on && g_prof.n < g_prof.cap;
-    if (prof) cudaEventRecord(g_prof.start[g_prof.n], st);
-    convh_kernel<TW, TH, true><<<grid, 192, smem, st>>>(tw, tx, p);
-    if (prof) {
-        cudaEventRecord(g_prof.stop[g_prof.n], st);
-        g_prof.n++;
-        g_prof.flops += g_prof.next_flops;
-    }
-    NCC_COUNT_LAUNCH();
-    if (p.stat) ncc::conv_stats_publish(y, Cout, (long long)N * Ho * Wo, (int)grid, p.stat);
-    return ncc::launch_status("convh_kernel(few channels)");
-}
-
 int conv_nhwc(float* y, const float* x, const float* wpacked, const float* bias, int N, int H, int W, int Cin, int Cout,
               int kH, int kW, int pad, int mode, cudaStream_t st) {
     const int Ho = H + 2 * pad - kH + 1, Wo = W + 2 * pad - kW + 1;
     if (Ho <= 0 || Wo <= 0) return NC_CUDA_ERR_UNSUPPORTED;
     if ((Cin & 3) || (Cout & 3) || Cin < 16 || Cout < 16) return NC_CUDA_ERR_UNSUPPORTED;
     if ((long long)N * Ho * Wo < 128) return NC_CUDA_ERR_UNSUPPORTED;
-    if (convh_ok(N, H, W, Cin, Cout, kH, kW, pad, mode)) {
-        const int rc = conv_halo_nhwc(y, x, wpacked, bias, N, H, W, Cin, Cout, kH, kW, pad, st);
+    {
+        const int rc = conv_halo_nhwc(y, x, wpacked, bias, N, H, W, Cin, Cout, kH, kW, pad, mode, st);
         if (rc != NC_CUDA_ERR_UNSUPPORTED) return rc;
     }
     if ((long long)N * Ho * Wo >= 1024 && kH * kW * Cout >= 128) {
@@ -1457,7 +833,7 @@ int conv_nhwc(float* y, const float* x, const float* wpacked, const float* bias,
         const long long tiles_px = (long long)p.tiles_w * p.tiles_h * ((N + bnn - 1) / bnn);
         p.N = (int)(tiles_px * 256 < 0x7fffffffLL ? tiles_px * 256 : 0x7fffffff);
         dim3 tiles((unsigned)tiles_px, (unsigned)((Cout + BM - 1) / BM), 1);
-        g_prof.next_flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
+        p.flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
         // launch_one uses min(tiles, SMs) persistent CTAs: one statistics slab per CTA
         const long long total_tiles = (long long)tiles.x * tiles.y;
         const int n_ctas = (int)(total_tiles < ncc::sm_count() ? total_tiles : ncc::sm_count());
@@ -1491,11 +867,10 @@ int conv_nhwc(float* y, const float* x, const float* wpacked, const float* bias,
     p.tiles_w = (Wo + bw - 1) / bw; p.tiles_h = (Ho + bh - 1) / bh;
     p.Ho = Ho; p.Wo = Wo; p.Nimg = N;
     p.kW = kW; p.pad = pad; p.wrows = Cout;
-    p.desc_variant = g_desc_variant;
     p.err = ncc::device_error_word();
     const long long tiles_m = (long long)p.tiles_w * p.tiles_h * ((N + bnn - 1) / bnn);
     dim3 grid((Cout + bn_cols - 1) / bn_cols, (unsigned)tiles_m, 1);
-    g_prof.next_flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
+    p.flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
     return launch_bn<false, false>(bn_cols, mode, ta, tb, p, grid, st);
 }
 
@@ -1504,6 +879,10 @@ int conv_dw_nhwc(float* dW, const float* dy, const float* x, int N, int H, int W
     const int Ho = H + 2 * pad - kH + 1, Wo = W + 2 * pad - kW + 1;
     if (Ho <= 0 || Wo <= 0) return NC_CUDA_ERR_UNSUPPORTED;
     if ((Cin & 31) || (Cout & 3) || Cout < 32) return NC_CUDA_ERR_UNSUPPORTED;
+    {
+        const int rc = conv_dw_halo_nhwc(dW, dy, x, N, H, W, Cin, Cout, kH, kW, pad, mode, st);
+        if (rc != NC_CUDA_ERR_UNSUPPORTED) return rc;
+    }
     const int Ncols = kH * kW * Cin;
     // column tile: whole filter rows when they fit in 256 columns, else 256 / 128 / 64
     int bn_cols;
@@ -1530,7 +909,6 @@ int conv_dw_nhwc(float* dW, const float* dy, const float* x, int N, int H, int W
     p.kW = kW; p.pad = pad; p.Cin = Cin;
     p.num_k_tiles = p.tiles_w * p.tiles_h * ((N + bnn - 1) / bnn);
     p.alpha = 1.f;
-    p.desc_variant = g_desc_variant;
     p.err = ncc::device_error_word();
     const int tiles_m = (Cout + BM - 1) / BM, tiles_n = (Ncols + bn_cols - 1) / bn_cols;
     int splits, kps;
@@ -1539,12 +917,16 @@ int conv_dw_nhwc(float* dW, const float* dy, const float* x, int N, int H, int W
     p.partial = (float*)ncc::scratch(2, sizeof(float) * (size_t)splits * Cout * Ncols, st);
     if (!p.partial) return NC_CUDA_ERR_RUNTIME;
     dim3 grid(tiles_n, tiles_m, splits);
-    g_prof.next_flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
+    p.flops = 2.0 * N * Ho * Wo * (double)Cout * Cin * kH * kW;
     int rc;
     if (bn_cols == 192) rc = launch_mode<192, true, true>(mode, ta, tb, p, grid, st);
     else rc = launch_bn<true, true>(bn_cols, mode, ta, tb, p, grid, st);
     if (rc) return rc;
-    dw_reduce_kernel<<<ncc::grid_for((long long)Cout * Ncols, 256), 256, 0, st>>>(dW, p.partial, splits, Cout, Cin, kH, kW);
+    return dw_reduce(dW, p.partial, splits, Cout, Cin, kH, kW, st);
+}
+
+int dw_reduce(float* dW, const float* partial, int splits, int Cout, int Cin, int kH, int kW, cudaStream_t st) {
+    dw_reduce_kernel<<<ncc::grid_for((long long)Cout * Cin * kH * kW, 256), 256, 0, st>>>(dW, partial, splits, Cout, Cin, kH, kW);
     NCC_COUNT_LAUNCH();
     return ncc::launch_status("dw_reduce");
 }
@@ -1561,41 +943,3 @@ int pack_weights_dx(float* wp, const float* w, int Cout, int Cin, int kH, int kW
 }
 
 }  // namespace tc
-
-extern "C" int nc_cuda_tc_profile_begin(void) {
-    using tc::g_prof;
-    if (!g_prof.start) {
-        g_prof.cap = 16384;
-        g_prof.start = new cudaEvent_t[g_prof.cap];
-        g_prof.stop = new cudaEvent_t[g_prof.cap];
-        for (int i = 0; i < g_prof.cap; i++) {
-            if (cudaEventCreate(&g_prof.start[i]) != cudaSuccess || cudaEventCreate(&g_prof.stop[i]) != cudaSuccess)
-                return ncc::set_status(NC_CUDA_ERR_RUNTIME, "tc profile: cudaEventCreate failed");
-        }
-    }
-    g_prof.n = 0;
-    g_prof.flops = 0.0;
-    g_prof.on = true;
-    return NC_CUDA_OK;
-}
-extern "C" int nc_cuda_tc_profile_end(double* total_ms, unsigned long long* launches, double* flops) {
-    using tc::g_prof;
-    g_prof.on = false;
-    double ms = 0.0;
-    if (g_prof.n > 0) {
-        if (cudaEventSynchronize(g_prof.stop[g_prof.n - 1]) != cudaSuccess)
-            return ncc::set_status(NC_CUDA_ERR_RUNTIME, "tc profile: cudaEventSynchronize failed");
-        for (int i = 0; i < g_prof.n; i++) {
-            float t = 0.f;
-            if (cudaEventElapsedTime(&t, g_prof.start[i], g_prof.stop[i]) == cudaSuccess) ms += t;
-        }
-    }
-    if (total_ms) *total_ms = ms;
-    if (launches) *launches = (unsigned long long)g_prof.n;
-    if (flops) *flops = g_prof.flops;
-    return NC_CUDA_OK;
-}
-
-// Bring-up knob (not part of the public header): selects an alternative shared-memory descriptor
-// encoding for MN-major operands so both can be checked against a known answer on hardware.
-extern "C" void nc_cuda_debug_desc_variant(int v) { tc::set_desc_variant(v); }

@@ -25,16 +25,18 @@ int conv_nhwc(float* y, const float* x, const float* wpacked, const float* bias,
 int conv_dw_nhwc(float* dW, const float* dy, const float* x, int N, int H, int W, int Cin, int Cout, int kH, int kW,
                  int pad, int mode, cudaStream_t st);
 
+// Halo-resident kernels (tc_conv.cu), plain TF32 mode, stride 1, filters up to 3 x 3; NC_CUDA_ERR_UNSUPPORTED otherwise.
+//   conv_halo_nhwc:    forward / input gradient with the activation halo of a pixel tile resident in shared memory
+//   conv_dw_halo_nhwc: weight gradient with one dY tile and one x halo tile serving all filter taps of a row
+int conv_halo_nhwc(float* y, const float* x, const float* wpacked, const float* bias, int N, int H, int W, int Cin, int Cout,
+                   int kH, int kW, int pad, int mode, cudaStream_t st);
+int conv_dw_halo_nhwc(float* dW, const float* dy, const float* x, int N, int H, int W, int Cin, int Cout, int kH, int kW,
+                      int pad, int mode, cudaStream_t st);
+// partial[z][co][(kh*kW+kw)*Cin + ci] summed over z in order -> dW (Cout, Cin, kH, kW)
+int dw_reduce(float* dW, const float* partial, int splits, int Cout, int Cin, int kH, int kW, cudaStream_t st);
+
 // (Cout,Cin,kH,kW) -> (kH,kW,Cout,Cin) for the forward; -> flipped (kH,kW,Cin,Cout) for dX.
-// Few-channel (network input) convolution on the halo-resident tensor-core kernel: x (N, Cin <= 8, H, W) with element
-// strides xs, y channels-last, w in the reference layout; plain TF32 mode, Cout in {16, 32, 64}, Ho % 32 == 0, Wo % 8 == 0.
-bool conv_few_channels_ok(int Cin, int Cout, int kH, int kW, int Ho, int Wo, int mode);
-int conv_few_channels(float* y, const float* x, const long long xs[4], const float* w, const float* bias, int N, int H, int W, int Cin,
-                      int Cout, int kH, int kW, int pad, bool round, cudaStream_t st);
 int pack_weights_fwd(float* wp, const float* w, int Cout, int Cin, int kH, int kW, bool round, cudaStream_t st);
 int pack_weights_dx(float* wp, const float* w, int Cout, int Cin, int kH, int kW, bool round, cudaStream_t st);
-
-// Experiment knob for bring-up: alternative shared-memory descriptor encodings (0 = default).
-void set_desc_variant(int v);
 
 }  // namespace tc

@@ -51,6 +51,8 @@ SIGNATURES = {
     "nc_cuda_event_record": (_i, [_p, _p]),
     "nc_cuda_stream_wait_event": (_i, [_p, _p]),
     "nc_cuda_event_synchronize": (_i, [_p]),
+    "nc_cuda_event_create_timed": (_p, []),
+    "nc_cuda_event_elapsed_ms": (_i, [_p, _p, C.POINTER(_f)]),
     "nc_cuda_last_status": (_i, []),
     "nc_cuda_last_message": (C.c_char_p, []),
     "nc_cuda_clear_status": (None, []),
@@ -61,8 +63,11 @@ SIGNATURES = {
     "nc_cuda_device_error_word": (C.c_uint, []),
     "nc_cuda_launch_count": (C.c_ulonglong, []),
     "nc_cuda_reset_launch_count": (None, []),
-    "nc_cuda_tc_profile_begin": (_i, []),
-    "nc_cuda_tc_profile_end": (_i, [C.POINTER(_d), C.POINTER(C.c_ulonglong), C.POINTER(_d)]),
+    "nc_cuda_profile_begin": (_i, []),
+    "nc_cuda_profile_end": (_i, []),
+    "nc_cuda_profile_categories": (_i, []),
+    "nc_cuda_profile_category_name": (C.c_char_p, [_i]),
+    "nc_cuda_profile_read": (_i, [_i, C.POINTER(_d), C.POINTER(C.c_ulonglong), C.POINTER(_d)]),
     # elementwise
     "nc_cuda_fill_f32": (None, [_p, _f, _z]),
     "nc_cuda_copy_f32": (None, [_p, _p, _z]),

@@ -177,9 +177,15 @@ static void accumulate_leaf(nc_tensor* leaf, nc_tensor* g) {
     if (g_ready_fn) g_ready_fn(leaf, g_ready_ctx);
 }
 
+/* The seed nc_backward itself filled with ones: a loss node that receives it knows the upstream value on the host
+ * and does not have to read a device scalar back (which would drain the whole forward pass before backward starts). */
+static const nc_tensor* g_unit_seed = NULL;
+bool nci_is_unit_seed(const nc_tensor* g) { return g && g == g_unit_seed; }
+
 nc_error nc_backward(nc_tensor* t, nc_tensor* grad_output) {
     if (!t) return NC_ERR_NULL_PTR;
     nc_tensor* seed = NULL;
+    g_unit_seed = NULL;
     if (grad_output) {
         if (grad_output->numel != t->numel) { NC_SET_ERROR(NC_ERR_SHAPE_MISMATCH, "backward: gradient has %zu elements, output %zu", grad_output->numel, t->numel); return NC_ERR_SHAPE_MISMATCH; }
         seed = nci_alias(grad_output);
@@ -187,18 +193,20 @@ nc_error nc_backward(nc_tensor* t, nc_tensor* grad_output) {
         if (t->numel != 1) { NC_SET_ERROR(NC_ERR_SHAPE_MISMATCH, "backward: output must be scalar, got %zu elements", t->numel); return NC_ERR_SHAPE_MISMATCH; }
         seed = nci_empty_on(t->shape, t->ndim, t->dtype, t->storage->device);
         if (seed) nc_tensor_fill_(seed, 1.0);
+        g_unit_seed = seed;
     }
     if (!seed) return NC_ERR_ALLOC;
     if (!t->grad_fn) {
         if (t->requires_grad) accumulate_leaf(t, seed);
+        g_unit_seed = NULL;
         nc_tensor_free(seed);
         return NC_OK;
     }
     size_t n = 0;
     nc_node** topo = nc_build_topo(t, &n);
-    if (!topo || !n) { nc_tensor_free(seed); nc_free(topo); return NC_OK; }
+    if (!topo || !n) { g_unit_seed = NULL; nc_tensor_free(seed); nc_free(topo); return NC_OK; }
     nc_tensor** pending = nc_calloc(n, sizeof(*pending));
-    if (!pending) { nc_tensor_free(seed); nc_free(topo); return NC_ERR_ALLOC; }
+    if (!pending) { g_unit_seed = NULL; nc_tensor_free(seed); nc_free(topo); return NC_ERR_ALLOC; }
     pending[n - 1] = seed;
     const int prev = g_grad_enabled;
     g_grad_enabled = 0;
@@ -234,9 +242,11 @@ nc_error nc_backward(nc_tensor* t, nc_tensor* grad_output) {
             if (!adopted && ig != g) nc_tensor_free(ig);
         }
         nc_free(in_grads);
+        if (g == g_unit_seed) g_unit_seed = NULL;   /* only the root node ever sees it */
         nc_tensor_free(g);
         pending[i] = NULL;
     }
+    g_unit_seed = NULL;
     g_grad_enabled = prev;
     for (size_t i = 0; i < n; i++) if (pending[i]) nc_tensor_free(pending[i]);
     for (size_t i = 0; i < n; i++) topo[i]->ref_count = 0;

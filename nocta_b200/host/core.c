@@ -216,6 +216,7 @@ nc_storage* nc_storage_retain(nc_storage* s) { if (s) s->refcount++; return s; }
 void nc_storage_release(nc_storage* s) {
     if (!s) return;
     if (--s->refcount > 0) return;
+    nci_forget_grad_arena(s);
     if (s->data) nc_free(s->data);
     if (s->cuda_data) nci_dev_free(s->cuda_data, s->size);
     nc_free(s);

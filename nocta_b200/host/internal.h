@@ -30,6 +30,7 @@ bool nci_on_cuda(const nc_tensor* t);
 nc_tensor* nci_param_grad_out(size_t input_index, const nc_tensor* like);
 /* the storage is a flattened-gradient arena of some optimizer (optim.c) */
 bool nci_is_grad_arena(const nc_storage* st);
+void nci_forget_grad_arena(const nc_storage* st);
 /* device pointer to element 0 (honours offset) */
 void* nci_dptr(const nc_tensor* t);
 #define nci_fptr(t) ((float*)nci_dptr(t))
@@ -49,6 +50,8 @@ void nci_round_outputs(bool activation_op);
 bool nci_tf32_mode(void);
 /* record a failed kernel call */
 bool nci_ok(int status, const char* op);
+/* g is the all-ones seed nc_backward created itself for a scalar loss (its value is known without a device read) */
+bool nci_is_unit_seed(const nc_tensor* g);
 /* autograd wiring for an op output */
 nc_node* nci_attach(nc_tensor* out, const char* name, nc_backward_fn fn);
 void nci_strides4(const nc_tensor* t, size_t s[4]);

@@ -333,7 +333,7 @@ static nc_tensor** bwd_sum_all(nc_tensor* g, nc_tensor** saved, size_t n) {
     nc_tensor** out = grad_array(1);
     if (!out) return NULL;
     nc_tensor* x = saved[0];
-    double scale = nc_tensor_get_flat(saved[1], 0) * nc_tensor_get_flat(g, 0);
+    double scale = nc_tensor_get_flat(saved[1], 0) * (nci_is_unit_seed(g) ? 1.0 : nc_tensor_get_flat(g, 0));
     out[0] = nci_empty_like(x);
     if (out[0]) nci_ok(nc_cuda_fill_f32_ex(nci_fptr(out[0]), (float)scale, x->numel, nci_stream()), "sum backward");
     return out;
@@ -384,7 +384,7 @@ nc_tensor* nc_argmax(nc_tensor* x, int axis, bool keepdim) {
 static nc_tensor** bwd_saved_grad(nc_tensor* g, nc_tensor** saved, size_t n) {
     nc_tensor** out = grad_array(2);
     if (!out) return NULL;
-    double up = nc_tensor_get_flat(g, 0);
+    double up = nci_is_unit_seed(g) ? 1.0 : nc_tensor_get_flat(g, 0);
     nc_tensor* gi = saved[n - 1];
     out[0] = (up == 1.0) ? nci_alias(gi) : nc_mul_scalar(gi, up);
     return out;
@@ -393,7 +393,7 @@ static nc_tensor** bwd_mse(nc_tensor* g, nc_tensor** saved, size_t n) {
     (void)n;
     nc_tensor** out = grad_array(2);
     if (!out) return NULL;
-    double up = nc_tensor_get_flat(g, 0);
+    double up = nci_is_unit_seed(g) ? 1.0 : nc_tensor_get_flat(g, 0);
     nc_tensor* pred = saved[0];
     nc_tensor* target = saved[1];
     nc_tensor* gp = saved[2];

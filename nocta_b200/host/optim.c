@@ -51,10 +51,14 @@ void nc_optimizer_set_grad_scale(nc_optimizer* opt, double scale) { if (opt && o
 /* storages that hold flattened gradients: views into them are written in place although they share storage */
 #define NCI_MAX_ARENAS 16
 static const nc_storage* g_arenas[NCI_MAX_ARENAS];
-static int g_n_arenas = 0;
 bool nci_is_grad_arena(const nc_storage* st) {
-    for (int i = 0; i < g_n_arenas; i++) if (g_arenas[i] == st) return true;
+    if (!st) return false;
+    for (int i = 0; i < NCI_MAX_ARENAS; i++) if (g_arenas[i] == st) return true;
     return false;
+}
+/* called by nc_storage_release when a storage dies: a later storage at the same address must not pass for an arena */
+void nci_forget_grad_arena(const nc_storage* st) {
+    for (int i = 0; i < NCI_MAX_ARENAS; i++) if (g_arenas[i] == st) g_arenas[i] = NULL;
 }
 void* nc_optimizer_flatten_grads(nc_optimizer* opt, size_t* n_floats) {
     if (!opt || !n_floats) return NULL;
@@ -65,11 +69,13 @@ void* nc_optimizer_flatten_grads(nc_optimizer* opt, size_t* n_floats) {
         total += (p->numel + 63) & ~(size_t)63;
     }
     if (!total) return NULL;
+    int slot = -1;
+    for (int i = 0; i < NCI_MAX_ARENAS && slot < 0; i++) if (!g_arenas[i]) slot = i;
+    if (slot < 0) { NC_SET_ERROR(NC_ERR_ALLOC, "flatten_grads: %d gradient arenas are alive already", NCI_MAX_ARENAS); return NULL; }
     nc_storage* arena = nc_storage_create_on(total * sizeof(float), NC_DEVICE_CUDA);
     if (!arena) return NULL;
     nc_cuda_memset_async(arena->cuda_data, 0, total * sizeof(float), nci_stream());
-    g_arenas[g_n_arenas % NCI_MAX_ARENAS] = arena; /* a reused slot only costs a copy, never correctness */
-    if (g_n_arenas < NCI_MAX_ARENAS) g_n_arenas++;
+    g_arenas[slot] = arena;
     size_t off = 0;
     for (size_t i = 0; i < opt->n_params; i++) {
         nc_tensor* p = opt->params[i];
@@ -84,7 +90,7 @@ void* nc_optimizer_flatten_grads(nc_optimizer* opt, size_t* n_floats) {
         g->dtype = NC_F32;
         g->is_leaf = true;
         g->is_contiguous = true;
-        if (p->grad) { nc_tensor_copy_(g, p->grad); nc_tensor_free(p->grad); }
+        if (p->grad) { nc_tensor_copy_(g, p->grad); g->is_reachable = true; /* holds values: accumulate, do not take over */ nc_tensor_free(p->grad); }
         p->grad = g;
         p->requires_grad = true;
         off += (p->numel + 63) & ~(size_t)63;

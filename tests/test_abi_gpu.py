@@ -385,6 +385,14 @@ CONV_CASES = [
     (16, 32, 12, 12, 64, 5, 1, 2),
     (4, 3, 16, 16, 64, 3, 1, 1),    # first-layer kernels (3 input channels)
     (3, 3, 9, 11, 32, 3, 1, 0),
+    # shapes the halo-resident tensor-core kernels take in plain TF32 mode: whole 8-wide pixel tiles, >= 32 channels
+    (2, 32, 32, 8, 32, 3, 1, 1),
+    (3, 64, 32, 16, 128, 3, 1, 1),
+    (2, 32, 64, 24, 48, 3, 1, 1),   # two tiles in h, three in w, Cout not a power of two
+    (2, 64, 32, 8, 64, 1, 1, 0),    # 1 x 1 filter
+    (2, 64, 56, 56, 64, 3, 1, 1),   # the isolated-backward benchmark's layer at a small batch (ragged in h: 56 = 32 + 24)
+    (3, 128, 16, 16, 128, 3, 1, 1), # half-height tile
+    (2, 64, 20, 12, 32, 3, 1, 1),   # ragged in both directions
 ]
 
 
@@ -579,31 +587,3 @@ def test_multi_tensor_optimizer_updates_equal_the_single_tensor_kernels(abi):
     ok(abi, abi.nc_cuda_adam_update_multi_f32_ex(len(sizes), tab(pb), tab(mb), tab(sb), None, tab(g0), numel, 1e-3, 0.9, 0.999, 1e-8, 0.01, 0.1, 0.001, 1.0, None))
     for a_, b_ in zip(pa + ma + sa, pb + mb + sb):
         assert torch.equal(a_, b_)
-
-
-@pytest.mark.parametrize("shape", [(2, 3, 32, 8, 16, 1), (3, 3, 64, 64, 64, 1), (2, 3, 34, 10, 32, 0), (2, 1, 32, 16, 64, 1), (1, 8, 32, 24, 64, 1)])
-def test_few_channel_convolution_on_tensor_cores(abi, shape):
-    """Network-input convolutions (<= 8 channels) in plain TF32 mode run on the halo-resident tensor-core kernel
-    (8-channel padded copy of the input, weights of all taps resident): against the oracle at the TF32 bar, with
-    NCHW input strides as the first layer sees them."""
-    from nocta_b200 import cuda_abi
-    N, Cin, H, W, Cout, pad = shape
-    Ho, Wo = H + 2 * pad - 2, W + 2 * pad - 2
-    rng = np.random.default_rng(H * W + Cout)
-    x = rng.standard_normal((N, Cin, H, W)).astype(np.float32)
-    w = (rng.standard_normal((Cout, Cin, 3, 3)) / 3).astype(np.float32)
-    b = rng.standard_normal(Cout).astype(np.float32)
-    y = torch.empty(N, Ho, Wo, Cout, device="cuda")
-    xs = cuda_abi.size4([Cin * H * W, H * W, W, 1])                 # dense NCHW input
-    ys = cuda_abi.size4([Ho * Wo * Cout, 1, Wo * Cout, Cout])       # channels-last output
-    abi.nc_cuda_set_math_mode(MODE_TF32)
-    abi.lib.nc_cuda_debug_desc_variant.argtypes = [C.c_int]
-    abi.lib.nc_cuda_debug_desc_variant(7)                           # this path is selected by the experiment switch
-    try:
-        before = abi.nc_cuda_launch_count()
-        ok(abi, abi.nc_cuda_conv2d_forward_f32_ex(P(y), ys, P(dev(x)), xs, P(dev(w)), P(dev(b)), N, Cin, H, W, Cout, 3, 3, 1, pad, None))
-        assert abi.nc_cuda_launch_count() - before == 3             # input copy, weight pack, convolution
-    finally:
-        abi.lib.nc_cuda_debug_desc_variant(0)
-    ref = O.conv2d_forward(x, w, b, 1, pad).transpose(0, 2, 3, 1)
-    close(host(y), ref, TOL_TF32)

@@ -10,10 +10,11 @@ Tolerances (max-abs error over max-abs reference, and relative L2; both must hol
                            whole forward+backward chain (north-star bar: 1e-3 per contraction, met in
                            test_abi_gpu.py).  The convolutional networks contain ReLU masks and max-pool
                            argmax selections: a forward value perturbed by 1e-3 flips a few of those decisions
-                           and re-routes whole gradient entries, so on these small test shapes (as few as 128
-                           samples per weight) whole-step gradients agree to 5-20 percent only; bound 0.3
-                           (a wrong kernel gives errors of order 1).
-                           The same networks agree to 4e-6 in 3xTF32 mode, which shows the kernels are right.
+                           and re-routes whole gradient entries, so a free-running comparison of their gradients
+                           measures the flips, not the kernels.  Here only their losses are held (1e-3) and the
+                           gradient error is printed; the gradients themselves are held to 1e-3 layer by layer on
+                           the reference's own activations, and the flipped fraction is bounded, in
+                           test_teacher_forced_gpu.py.
 Integer bookkeeping (optimizer step counter) is compared with ==.
 
 Updated parameters under Adam/AdamW: the update lr * m_hat / (sqrt(v_hat) + eps) is close to lr * sign(g)
@@ -32,7 +33,6 @@ pytestmark = pytest.mark.gpu
 
 MODE_TF32, MODE_RNA, MODE_3X, MODE_SIMT = 0, 1, 2, 3
 TOL = {MODE_SIMT: 2e-5, MODE_3X: 2e-5, MODE_TF32: 2e-3}
-TOL_TF32_CONV = 0.3
 TOL_PARAM_ADAM_L2 = 1e-3
 
 
@@ -69,6 +69,7 @@ def run(r, builder, steps, **kw):
 
 
 def compare(a, b, tol, adam_slack=0.0, loss_tol=None):
+    """tol None: gradients and parameters are only measured (worst error returned), the losses still held to loss_tol."""
     worst = ("", 0.0)
     loss_tol = tol if loss_tol is None else loss_tol
     for k in b["grads"]:
@@ -77,11 +78,13 @@ def compare(a, b, tol, adam_slack=0.0, loss_tol=None):
         e = max(O.rel_errors(a["grads"][k], b["grads"][k]))
         if e > worst[1]:
             worst = ("grad " + k, e)
-        assert e <= tol, ("grad", k, e, tol)
+        assert tol is None or e <= tol, ("grad", k, e, tol)
     for k in b["params"]:
         emax, el2 = O.rel_errors(a["params"][k], b["params"][k])
         if max(emax, el2) > worst[1]:
             worst = ("param " + k, max(emax, el2))
+        if tol is None:
+            continue
         slack = adam_slack / max(float(np.abs(b["params"][k]).max()), 1e-30)
         l2_tol = max(tol, TOL_PARAM_ADAM_L2) if adam_slack else tol
         assert el2 <= l2_tol and emax <= tol + slack, ("param", k, emax, el2, tol, slack)
@@ -112,7 +115,7 @@ def test_training_step_matches_reference(ours, theirs, name, kw, steps, mode):
         ours.api.lib.nc_cuda_set_math_mode(MODE_TF32)
     tol, loss_tol = TOL[mode], None
     if mode == MODE_TF32 and name in ("lenet", "convbn", "vgg"):
-        tol, loss_tol = TOL_TF32_CONV, 1e-3
+        tol, loss_tol = None, 1e-3   # free-running TF32 gradients of a ReLU / max-pool network: reported, not bounded (see above)
     elif mode == MODE_TF32:
         loss_tol = 1e-3
     worst = compare(got, expected, tol, adam_slack=2 * ADAM_LR.get(name, 0.0) * steps, loss_tol=loss_tol)

@@ -82,7 +82,7 @@ def test_rejects_more_rows_than_the_fixed_scratch_holds(abi):
     loss = torch.full((1,), -1.0, device="cuda")
     rc = abi.nc_cuda_cross_entropy_fused_static_f32_ex(P(loss), None, P(logits), P(labels), n, c, 1.0, None)
     torch.cuda.synchronize()
-    assert rc != 0
+    assert rc == 5   # "request exceeds a stated fixed capacity"
     abi.lib.nc_cuda_last_message.restype = C.c_char_p
     assert b"at most 4096 rows" in abi.lib.nc_cuda_last_message()
     assert float(loss.cpu()[0]) == -1.0  # nothing was launched
@@ -90,3 +90,28 @@ def test_rejects_more_rows_than_the_fixed_scratch_holds(abi):
     rc = abi.nc_cuda_cross_entropy_fused_static_f32_ex(P(loss), None, P(logits[:8]), P(labels[:8]), 8, c, 1.0, None)
     torch.cuda.synchronize()
     assert rc == 0 and abs(float(loss.cpu()[0]) - np.log(4.0)) < 1e-6
+
+
+def test_static_entry_point_leaves_device_memory_untouched(abi):
+    """The property the entry point exists for: once its inputs and outputs exist, calling it allocates nothing on the
+    device.  After one call (which resolves the scratch address on this device) the free-memory figure of cudaMemGetInfo
+    must stay exactly where it was across calls of every size up to the limit, new streams included."""
+    sizes = [(1, 3), (300, 100), (2048, 10), (MAX_ROWS, 64)]
+    g = torch.Generator().manual_seed(9)
+    cases = []
+    for n, c in sizes:   # every buffer the calls will touch is created first (and kept alive)
+        cases.append((torch.randn(n, c, generator=g).cuda(), torch.randint(0, c, (n,), generator=g, dtype=torch.int64).cuda(),
+                      torch.zeros(1, device="cuda"), torch.zeros(n, c, device="cuda"), n, c))
+    side = torch.cuda.Stream()
+    logits, labels, loss, grad, n, c = cases[0]
+    assert abi.nc_cuda_cross_entropy_fused_static_f32_ex(P(loss), P(grad), P(logits), P(labels), n, c, 1.0, None) == 0
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        for logits, labels, loss, grad, n, c in cases:
+            assert abi.nc_cuda_cross_entropy_fused_static_f32_ex(P(loss), P(grad), P(logits), P(labels), n, c, 1.0, None) == 0
+            torch.cuda.synchronize()
+            assert abi.nc_cuda_cross_entropy_fused_static_f32_ex(P(loss), None, P(logits), P(labels), n, c, 1.0, C.c_void_p(side.cuda_stream)) == 0
+            torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, (free_before, free_after)
