@@ -530,9 +530,38 @@ void nc_tensor_free(nc_tensor* t) {
 }
 
 /* ------------------------------------------------------------------ element access */
+/* A raw host pointer to the elements, as the reference returns it (src/core/tensor.c).  A caller that asks for it means
+ * to read or write the data behind the library's back (the script VM's optimizer natives do: src/lang/vm.c:1090-1112), so
+ * a device-resident storage is moved to the host first, all its views with it (blocking copy); the next operator that
+ * uses the tensor moves it back (nci_need_cuda_f32).  Correct, and slow by design: code on the hot path uses the
+ * device-side optimizers instead. */
 void* nc_tensor_data(const nc_tensor* t) {
-    if (!t || !t->storage || !t->storage->data) return NULL;
+    if (!t || !t->storage) return NULL;
+    if (t->storage->device == NC_DEVICE_CUDA) nc_storage_to_device(t->storage, NC_DEVICE_CPU);
+    if (!t->storage->data) return NULL;
     return (char*)t->storage->data + t->offset * nc_dtype_sizeof(t->dtype);
+}
+
+/* Mark bits for a caller's garbage collector (the script VM, src/lang/vm.c; reference: src/core/tensor.c:763-806): mark
+ * walks the tensor, the inputs and saved tensors of its graph node and marks them; reset clears the same set.  The flag
+ * of a GRADIENT tensor is left alone: this library uses it to remember whether a gradient still holds the zeros it was
+ * cleared to (autograd.c), and gradients belong to their tensor, never to a collector. */
+void nc_tensor_mark_reachable(nc_tensor* t) {
+    if (!t || t->is_reachable) return;
+    t->is_reachable = true;
+    nc_node* nd = t->grad_fn;
+    if (!nd) return;
+    for (size_t i = 0; i < nd->n_inputs; i++) if (nd->inputs[i]) nc_tensor_mark_reachable(nd->inputs[i]);
+    for (size_t i = 0; i < nd->n_saved; i++) if (nd->saved_tensors[i]) nc_tensor_mark_reachable(nd->saved_tensors[i]);
+}
+bool nc_tensor_is_reachable(const nc_tensor* t) { return t ? t->is_reachable : false; }
+void nc_tensor_reset_reachable(nc_tensor* t) {
+    if (!t || !t->is_reachable) return;
+    t->is_reachable = false;
+    nc_node* nd = t->grad_fn;
+    if (!nd) return;
+    for (size_t i = 0; i < nd->n_inputs; i++) if (nd->inputs[i]) nc_tensor_reset_reachable(nd->inputs[i]);
+    for (size_t i = 0; i < nd->n_saved; i++) if (nd->saved_tensors[i]) nc_tensor_reset_reachable(nd->saved_tensors[i]);
 }
 static size_t flat_to_offset(const nc_tensor* t, size_t idx) {
     if (t->is_contiguous) return t->offset + idx;

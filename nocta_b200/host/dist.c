@@ -280,6 +280,7 @@ double nc_dist_exposed_ms(nc_dist* d) {
     if (!d) return -1.0;
     double worst = 0.0;
     const size_t nb = nc_bucket_plan_count(d->plan);
+    if (nc_cuda_event_synchronize(d->bwd_end_ev)) return -1.0;
     for (size_t b = 0; b < nb; b++) {
         float ms = 0.f;
         if (nc_cuda_event_synchronize(d->done_ev[b])) return -1.0;

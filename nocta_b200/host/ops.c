@@ -404,11 +404,32 @@ static nc_tensor** bwd_mse(nc_tensor* g, nc_tensor** saved, size_t n) {
 
 nc_tensor* nc_cross_entropy_loss_ex(nc_tensor* logits, nc_tensor* targets, nc_reduction reduction) {
     if (!nci_need_cuda_f32(logits, "cross_entropy")) return NULL;
-    if (!targets || targets->dtype != NC_I64 || !nci_on_cuda(targets)) {
-        NC_SET_ERROR(NC_ERR_INVALID_DTYPE, "cross_entropy: targets must be an int64 tensor on the CUDA device");
-        return NULL;
-    }
+    if (!targets) { NC_SET_ERROR(NC_ERR_NULL_PTR, "cross_entropy: null targets"); return NULL; }
     if (logits->ndim != 2 || targets->numel != logits->shape[0]) { NC_SET_ERROR(NC_ERR_SHAPE_MISMATCH, "cross_entropy: logits (N,C), targets (N)"); return NULL; }
+    nc_tensor* converted = NULL;
+    if (targets->dtype != NC_I64 || !nci_on_cuda(targets)) {
+        /* The reference reads class indices from a tensor of any dtype (src/ops/loss.c:218-232); its script VM passes
+         * float32.  The kernel wants int64 on the device: convert through the host (N values, off the hot path). */
+        const size_t n = targets->numel;
+        int64_t* idx = nc_alloc(sizeof(int64_t) * (n ? n : 1));
+        if (!idx) return NULL;
+        nc_tensor* th = nc_tensor_clone(targets);
+        if (th && nci_on_cuda(th)) nc_tensor_to_device(th, NC_DEVICE_CPU);
+        if (!th) { nc_free(idx); return NULL; }
+        for (size_t i = 0; i < n; i++) idx[i] = (int64_t)nc_tensor_get_flat(th, i);
+        nc_tensor_free(th);
+        size_t shp = n;
+        converted = nc_tensor_from_data(idx, &shp, 1, NC_I64);
+        nc_free(idx);
+        if (converted && !nci_on_cuda(converted)) nc_tensor_to_device(converted, NC_DEVICE_CUDA);
+        if (!converted || !nci_on_cuda(converted)) { nc_tensor_free(converted); NC_SET_ERROR(NC_ERR_DEVICE, "cross_entropy: cannot stage the targets on the device"); return NULL; }
+        nc_tensor* out = nc_cross_entropy_loss_ex(logits, converted, reduction);
+        /* the node keeps the converted targets alive through its input list only while it owns them: it does not, so
+         * detach them from the graph before they go (targets never receive a gradient) */
+        if (out && out->grad_fn) for (size_t i = 0; i < out->grad_fn->n_inputs; i++) if (out->grad_fn->inputs[i] == converted) out->grad_fn->inputs[i] = NULL;
+        nc_tensor_free(converted);
+        return out;
+    }
     if (reduction == NC_REDUCTION_NONE) { NC_SET_ERROR(NC_ERR_UNKNOWN, "cross_entropy: per-sample losses are not available on the device"); return NULL; }
     nc_tensor* lc = nc_tensor_contiguous(logits);
     nc_tensor* tc = nc_tensor_contiguous(targets);

@@ -258,3 +258,36 @@ def test_xor_trajectory_matches_reference(both):
         assert np.abs(ours - theirs).max() <= 1e-2 * max(theirs.max(), 1e-3), (seed, ours[-1], theirs[-1])
         if seed == 7:
             assert abs(ours[-1] - 0.25) < 1e-3 and abs(theirs[-1] - 0.25) < 1e-3
+
+
+def _vm_lines(binary, script, env_extra):
+    env = dict(os.environ, **env_extra)
+    out = subprocess.run([str(binary), str(script)], capture_output=True, text=True, timeout=300, env=env)
+    assert out.returncode == 0, out.stderr[-2000:]
+    return [l for l in out.stdout.splitlines() if l.startswith("step ") or l.startswith("w0 ")], out.stderr
+
+
+@pytest.mark.parametrize("mode,tol", [("2", 2e-4), ("0", 2e-2)])
+def test_script_interpreter_trains_on_the_cuda_library(mode, tol):
+    """The reference's script interpreter (src/lang/*.c + src/main.c), compiled UNMODIFIED against this repository's
+    headers and libraries (oracle/Makefile, target `vm`), runs a four-step training script (tests/golden/vm/train_cnn.noc:
+    conv2d, batch_norm2d, relu, max_pool2d, reshape, matmul + bias, cross_entropy, backward, apply_sgd_momentum — the
+    natives of src/lang/vm.c:924-1112) and prints the same losses and final weights as the same interpreter linked against
+    the compiled reference.  apply_sgd_momentum updates the parameters through raw nc_tensor_data pointers
+    (vm.c:1090-1112): the library hands out host memory for that and moves the tensors back on their next use.
+    Printed numbers carry six digits; 3xTF32 mode is held to 2e-4 over the four steps, plain TF32 to 2e-2."""
+    vm, vm_ref = APPS / "noc_vm", APPS / "noc_vm_ref"
+    if not vm.exists() or not vm_ref.exists():
+        pytest.skip("oracle/_ref/apps/noc_vm(_ref) not built (reference sources were absent at build time)")
+    script = ROOT / "tests" / "golden" / "vm" / "train_cnn.noc"
+    want, _ = _vm_lines(vm_ref, script, {"OMP_NUM_THREADS": "1"})
+    got, err = _vm_lines(vm, script, {"NOCTA_CUDA_MATH_MODE": mode})
+    assert len(want) == 5 and len(got) == 5, (want, got, err[-1000:])
+    import re
+    num = re.compile(r"-?\d+\.?\d*(?:e-?\d+)?")
+    for lw, lg in zip(want, got):
+        vw, vg = [float(v) for v in num.findall(lw)], [float(v) for v in num.findall(lg)]
+        assert len(vw) == len(vg)
+        for a, b in zip(vw, vg):
+            assert abs(a - b) <= tol * max(abs(a), 1e-2), (lw, lg)
+    assert "not on the training path" not in err
