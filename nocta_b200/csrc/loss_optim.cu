@@ -447,8 +447,9 @@ int nc_cuda_adam_update_multi_f32_ex(int count, float* const* params, float* con
     AdamArgs a{lr, beta1, beta2, eps, weight_decay, 1.0 / bias_corr1, 1.0 / bias_corr2, grad_scale};
     cudaStream_t st = (cudaStream_t)stream;
     double total = 0.0;
-    for (int i = 0; i < count; i++) total += (double)numel[i];
-    ProfScope prof(PROF_ADAM, (v_max ? 36.0 : 28.0) * total, st);
+    bool amsgrad = false;
+    for (int i = 0; i < count; i++) { total += (double)numel[i]; amsgrad = amsgrad || (v_max && v_max[i]); }
+    ProfScope prof(PROF_ADAM, (amsgrad ? 36.0 : 28.0) * total, st);
     return multi_launch(count, params, m, v, v_max, grads, numel, "adam_multi",
                         [&](const MultiTable& t, unsigned int blocks) { adam_multi_kernel<<<blocks, kThreads, 0, st>>>(t, a); });
 }

@@ -347,6 +347,11 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
             int s = 0;
             uint32_t ph = 0, tile_iter = 0;
             bool ok = true;
+            // A barrier test takes this thread well over a hundred cycles before its result can be used, about as long as
+            // issuing two MMAs.  The state of the NEXT stage's barrier is therefore requested before this stage's MMAs
+            // are issued and only looked at afterwards: with the producers ahead it is already set, and the wait at
+            // the top of the next round is skipped.
+            bool known_ready = false;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, tile_iter++) {
                 const int z = (t / p.tiles_n) / p.tiles_m;
                 const int kt_begin = z * p.k_tiles_per_split;
@@ -360,8 +365,13 @@ tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                 const uint32_t acc_base = tmem_base + ab * (uint32_t)(Cfg::NACC * Cfg::ACC_COLS);
                 for (int i = 0; i < nk; i++) {
                     const uint32_t ready = MODE == 0 ? smem_u32(&bar_full[s]) : smem_u32(&bar_conv[s]);
-                    if (!mbar_wait(ready, ph, p.err, 0x200u + s, abortp)) { ok = false; break; }
+                    if (!known_ready && !mbar_wait(ready, ph, p.err, 0x200u + s, abortp)) { ok = false; break; }
                     tc_fence_after();
+                    {
+                        const int s1 = (s + 1 == STAGES) ? 0 : s + 1;
+                        const uint32_t ph1 = (s + 1 == STAGES) ? (ph ^ 1u) : ph;
+                        known_ready = mbar_test(MODE == 0 ? smem_u32(&bar_full[s1]) : smem_u32(&bar_conv[s1]), ph1);
+                    }
                     const uint64_t soff = (uint64_t)(((uint32_t)s * (uint32_t)Cfg::STAGE_BYTES) >> 4);
 #pragma unroll
                     for (int ks = 0; ks < BK / 8; ks++) {
@@ -622,11 +632,11 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(float* __restrict__ 
                                                             float alpha, float beta) {
     const size_t total = (size_t)M * N, stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        float acc = 0.f;
-        for (int z = 0; z < splits; z++) acc += partial[(size_t)z * total + i];
+        double acc = 0.0;   // the splits are combined in double, in order: no rounding that grows with their number
+        for (int z = 0; z < splits; z++) acc += (double)partial[(size_t)z * total + i];
         const int m = (int)(i / N), n = (int)(i % N);
         float* d = D + (size_t)m * ldd + n;
-        float o = alpha * acc;
+        float o = alpha * (float)acc;
         if (beta != 0.f) o += beta * *d;
         if (bias) o += bias[n];
         *d = o;
@@ -644,9 +654,9 @@ __global__ void __launch_bounds__(256) dw_reduce_kernel(float* __restrict__ dW, 
         const int ci = r % Cin;
         const int co = (int)(r / Cin);
         const size_t src = (size_t)co * (kH * kW * Cin) + (size_t)(kh * kW + kw) * Cin + ci;
-        float acc = 0.f;
-        for (int z = 0; z < splits; z++) acc += partial[(size_t)z * total + src];
-        dW[i] = acc;
+        double acc = 0.0;
+        for (int z = 0; z < splits; z++) acc += (double)partial[(size_t)z * total + src];
+        dW[i] = (float)acc;
     }
 }
 
