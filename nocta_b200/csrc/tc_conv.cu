@@ -1,27 +1,36 @@
 // Halo-resident tensor-core kernels for stride-1 convolutions with filters up to 3 x 3 (plain TF32 mode), sm_100a:
 // TMA-fed tcgen05.mma (kind::tf32), accumulators in tensor memory, inline PTX.
 //
-// The operand traffic from L2 into shared memory, not the tensor pipe, bounds an implicit-GEMM convolution that streams
-// one operand tile per filter tap: every tap re-reads the same pixels.  The kernels here load a pixel tile WITH its halo
-// once and address every tap inside it by moving the start address of the shared-memory matrix descriptor: the swizzle
-// of a TMA-written tile is a function of the absolute shared-memory address, so a descriptor may start at any 128-byte
-// pixel row and use any stride between its 8-row groups.
+// An implicit-GEMM convolution that streams one operand tile per filter tap re-reads the same pixels for every tap.  The
+// kernels here load a pixel tile WITH its halo once and address every tap inside it by moving the start address of the
+// shared-memory matrix descriptor: the swizzle of a TMA-written tile is a function of the absolute shared-memory
+// address, so a descriptor may start at any 128-byte pixel row and use any stride between its 8-row groups (K-major
+// operands) or 4-row atoms (MN-major operands, 32-byte swizzle atoms).
 //
-//   convh_kernel<false>  forward / input gradient, output channels on M (weights = A, streamed per tap), 8 x <=32 pixels
-//                        of one image on N (halo = B).  One MMA of N = 8 * rows per k-step.
+// What bounds these kernels is not operand delivery but MMA ISSUE: measured on B200, one thread issues a tcgen05.mma with
+// fresh descriptors every 65 - 80 cycles at best, a barrier test costs it another ~180 cycles, while the tensor pipe needs
+// 128 cycles for M = 128, N = 256, 64 for N = 128 and 48 for N = 64 (K = 8).  MMAs into ONE accumulator must come from one
+// thread to stay ordered, but different accumulators can be issued by different warps.  So: one barrier round trip covers
+// a whole filter row of taps (12 MMAs), and wherever a tile has several accumulators they get an issuing warp each.
+//
+//   convh_kernel<false>  forward / input gradient, output channels on M (weights = A, streamed one filter row per
+//                        stage), 8 x <=32 pixels of one image on N (halo = B).  One MMA of N = 8 * rows per k-step, one
+//                        issuing warp.  Used from 128 output channels on.
 //   convh_kernel<true>   the same convolution with the roles swapped for layers with at most 96 output channels: 8 x 16
 //                        pixels on M (halo = A), all output channels on N (weights = B).  An MMA costs
 //                        max(N / 2, operand bytes / 128, ~46) cycles whatever M is, so 64 channels on M run at half
-//                        rate while 128 pixels on M with N = 64 run at two thirds.
+//                        rate while 128 pixels on M with N = 64 run at two thirds.  The two 8 x 16 blocks of a tile have
+//                        their own accumulators and issuing warps; up to 64 channels a second pair of warps takes
+//                        k-steps 2 and 3 into accumulators of its own, which the epilogue adds.
 //   dwh_kernel<false>    weight gradient for Cin % 128 == 0: A = dY tile (128 output channels, MN-major), B = x halo
 //                        tile (128 input channels, MN-major); one filter row per work item, the kW taps of the row are kW
 //                        MMAs per 8-pixel k-step against the same two tiles (B start moved by kw pixel rows) into kW
-//                        accumulators.  dY and x cross from L2 to shared memory kH times instead of kH * kW times, as a
-//                        few large copies per stage instead of twelve 4 KB ones.
+//                        accumulators, each with its own issuing warp.  dY and x cross from L2 to shared memory kH times
+//                        instead of kH * kW times, as a few large copies per stage.
 //   dwh_kernel<true>     weight gradient for narrower inputs: A = ONE 32-channel x halo chunk addressed with a leading
 //                        byte offset of one pixel row, so the four 32-row chunks of M are the same channels shifted by
 //                        0..3 pixels = the kW taps of a filter row (kW = 3: three quarters of M useful); B = dY tile;
-//                        one accumulator per filter row, all kH * kW taps per work item.
+//                        one accumulator and one issuing warp per filter row, all kH * kW taps per work item.
 //
 // Pixel tiles may hang over the image edge: TMA zero-fills what it loads there (which is also the padding) and the
 // epilogues mask what they store.  No cluster launch and no multicast: each CTA loads its own tiles.  Every mbarrier

@@ -8,6 +8,7 @@ themselves are only needed where the library is built.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import subprocess
 from pathlib import Path
 
@@ -16,7 +17,8 @@ from nocta_b200.capi import NoctaAPI, TensorP
 HERE = Path(__file__).resolve().parent
 REF_SO = HERE / "_ref" / "libnocta_ref.so"
 REF_FAST_SO = HERE / "_ref" / "libnocta_ref_fast.so"
-REFERENCE_ROOT = Path("/root/reference")
+# where the reference sources lie when they are available (same variable as oracle/Makefile: make REF=...)
+REFERENCE_ROOT = Path(os.environ.get("REF", "/root/reference"))
 
 
 def build(reference_root: Path = REFERENCE_ROOT) -> bool:
