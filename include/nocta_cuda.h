@@ -95,7 +95,9 @@ int   nc_cuda_set_round_outputs(int on);
 /* new: while on, nc_cuda_conv2d_forward_f32_ex (channels-last output, tensor-core or first-layer kernels)
  * also sums its output per channel, and a training-mode BatchNorm forward that is the library's very next
  * kernel-launching call on exactly that output takes those sums instead of reading the tensor again.  Any other
- * launch of the library in between cancels the offer; switching off afterwards does not.  Off by default.
+ * launch, copy or memset of the library in between cancels the offer; switching off afterwards does not.  The library
+ * only sees its own calls: a caller that lets ANYTHING ELSE write that tensor between the two calls (its own kernel,
+ * another library, a peer copy, a collective) must leave the switch off, or stale sums are used.  Off by default.
  * Returns the previous setting. */
 int   nc_cuda_set_conv_stats(int on);
 /* new: reads and clears the device-side error word set when a bounded in-kernel wait expires */
