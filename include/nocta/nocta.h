@@ -108,6 +108,10 @@ typedef struct {
 } nc_device_pool_stats;
 nc_device_pool_stats nc_device_pool_get_stats(void);
 void nc_device_pool_release(void); /* return cached blocks to the driver */
+/* new: cap on the bytes the pool may hold from the driver (0 = no cap, the default).  An allocation that would exceed it
+ * first returns the cached blocks, then fails like a refused driver allocation: NULL + NC_ERR_ALLOC, nothing leaked. */
+void nc_device_pool_set_limit(size_t bytes);
+size_t nc_device_pool_get_limit(void);
 
 typedef struct {
     void* data;      /* CPU pointer (NULL while the bytes live on the device only) */

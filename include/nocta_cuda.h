@@ -100,6 +100,21 @@ int   nc_cuda_set_round_outputs(int on);
  * another library, a peer copy, a collective) must leave the switch off, or stale sums are used.  Off by default.
  * Returns the previous setting. */
 int   nc_cuda_set_conv_stats(int on);
+/* new: the backward counterpart of the above.  Announces that the gradient the NEXT nc_cuda_conv2d_backward_input_f32_ex call
+ * writes is the upstream gradient of a training-mode BatchNorm with fused ReLU whose input is x (channels-last, C channels,
+ * rows = N*H*W pixels; batch mean / biased variance as saved by the forward pass; gamma / beta may be NULL).  That call
+ * consumes the announcement; if its kernel can (the halo-resident tensor-core kernel with the channels on M: TF32 mode, 3x3
+ * stride 1, images of 24 rows or more, more than 96 channels, dense channels-last gradient of the same shape), it also sums per channel g and g * xhat with g zeroed where gamma * xhat + beta <= 0, and a
+ * nc_cuda_batchnorm_backward_f32_ex(relu_recompute = 1) that is the library's very next launching call on exactly that
+ * gradient and that x takes the sums instead of reading both tensors again.  Same hazard as above: nothing outside the
+ * library may write the gradient between the two calls.  Results are the same sums in another order of addition. */
+int   nc_cuda_offer_batchnorm_backward_sums_f32(const float* x, const float* mean, const float* var, const float* gamma,
+                                                const float* beta, double eps, int C, long long rows);
+/* new: while off, announcements are ignored (every BatchNorm backward does its own reduction).  On by default.
+ * Returns the previous setting. */
+int   nc_cuda_set_batchnorm_backward_fold(int on);
+/* new: how many BatchNorm backward calls have taken folded sums so far (bookkeeping for tests and benches) */
+unsigned long long nc_cuda_batchnorm_backward_fold_count(void);
 /* new: reads and clears the device-side error word set when a bounded in-kernel wait expires */
 unsigned int nc_cuda_device_error_word(void);
 /* new: number of kernels this library has launched since the last reset (bookkeeping for benches) */

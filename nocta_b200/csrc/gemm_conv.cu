@@ -338,6 +338,8 @@ int nc_cuda_conv2d_forward_f32_ex(float* y, const size_t ys[4], const float* x, 
 int nc_cuda_conv2d_backward_input_f32_ex(float* dx, const size_t xs[4], const float* dy, const size_t ys[4], const float* w,
                                          int N, int Cin, int H, int W, int Cout, int kH, int kW, int stride, int pad,
                                          void* stream) {
+    // an announced BatchNorm backward (nc_cuda_offer_batchnorm_backward_sums_f32) is served by this call or dropped
+    struct FoldScope { FoldScope() { bn_fold_enter(); } ~FoldScope() { bn_fold_leave(); } } fold_scope;
     NCC_REQUIRE(dx && dy && w && ys && xs, "conv2d_backward_input: null pointer");
     cudaStream_t st = (cudaStream_t)stream;
     ConvGeo g;

@@ -38,6 +38,31 @@ double* conv_stats_buffer(size_t slabs, int C, cudaStream_t st);
 void conv_stats_publish(const float* y, int C, long long rows, int slabs, double* partial);
 bool conv_stats_take(const float* x, int C, long long rows, double** partial, int* slabs);
 
+// Backward counterpart: the input-gradient convolution whose output is the upstream gradient of a BatchNorm(+ReLU)
+// can sum, per channel, what that BatchNorm's backward pass needs (sum of g and of g * xhat, g zeroed where the ReLU
+// was inactive) while it stores the gradient, so the BatchNorm backward does not read both tensors once more.
+// The caller announces the BatchNorm (nc_cuda_offer_batchnorm_backward_sums_f32); the next input-gradient call consumes
+// the announcement, and if its kernel could honour it publishes partial[slab][C][2]; a BatchNorm backward that is the
+// very next launching call on exactly that gradient takes them.
+struct BnFold {
+    const float* x;      // the BatchNorm's input (channels-last, same shape as the gradient)
+    const float* mean;   // batch mean and (biased) variance per channel
+    const float* var;
+    const float* gamma;  // may be null (1)
+    const float* beta;   // may be null (0)
+    float eps;
+    int C;
+    long long rows;      // N * H * W
+};
+void bn_fold_announce(const BnFold& f);
+void bn_fold_enter();                 // input-gradient entry point: takes the pending announcement (if any) for this call
+void bn_fold_leave();
+const BnFold* bn_fold_active();       // non-null inside that entry point while an announcement is being served
+double* bn_fold_buffer(size_t slabs, int C, cudaStream_t st);
+void bn_fold_publish(const float* dy, int slabs, double* partial);
+bool bn_fold_take(const float* dy, const BnFold& want, double** partial, int* slabs);
+extern unsigned long long g_bn_fold_hits;
+
 // Device-resident error word the tensor-core kernels set when a bounded wait expires.
 unsigned int* device_error_word();
 

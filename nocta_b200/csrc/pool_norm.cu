@@ -1013,13 +1013,18 @@ int nc_cuda_batchnorm_backward_f32_ex(float* dx, float* dgamma, float* dbeta, co
     double* partial = nullptr;
     int slabs = 0;
     // sums pass reads dy and x (and the saved ReLU output when there is one), apply pass reads them again and writes dx
-    ProfScope prof(PROF_BATCHNORM, (relu_out ? 28.0 : 20.0) * (double)total, st);
+    // ... unless the convolution that wrote dy summed on its way out (nc_cuda_offer_batchnorm_backward_sums_f32)
+    const bool folded = layout == 1 && relu_recompute && !relu_out &&
+                        bn_fold_take(dy, BnFold{x, save_mean, save_var, gamma, relu_beta, fe, C, (long long)N * spatial}, &partial, &slabs);
+    ProfScope prof(PROF_BATCHNORM, (folded ? 12.0 : (relu_out ? 28.0 : 20.0)) * (double)total, st);
     const ReluMask mask{relu_out, gamma, relu_beta, relu_out ? 0 : (relu_recompute ? 1 : 0)};
-    int rc = channel_reduce(&partial, &slabs, N, C, spatial, layout,
-                            BnBwdSum{dy, x, mask, save_mean, save_var, fe, C},
-                            BnBwdSumFlat{dy, x, mask, save_mean, save_var, fe},
-                            al16(dy) && al16(x) && al16(relu_out) && al16(save_mean) && al16(save_var), st);
-    if (rc) return rc;
+    if (!folded) {
+        int rc = channel_reduce(&partial, &slabs, N, C, spatial, layout,
+                                BnBwdSum{dy, x, mask, save_mean, save_var, fe, C},
+                                BnBwdSumFlat{dy, x, mask, save_mean, save_var, fe},
+                                al16(dy) && al16(x) && al16(relu_out) && al16(save_mean) && al16(save_var), st);
+        if (rc) return rc;
+    }
     float* sums = (float*)scratch(6, sizeof(float) * 2 * (size_t)C, st);
     if (!sums) return NC_CUDA_ERR_RUNTIME;
     bn_bwd_finalize_kernel<<<fin_grid(C), kFinCols * kFinLanes, 0, st>>>(partial, slabs, C, dgamma, dbeta, sums);

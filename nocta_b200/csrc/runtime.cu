@@ -23,7 +23,7 @@ static int g_math_mode = initial_math_mode();
 unsigned long long g_launches = 0;
 unsigned long long g_epoch = 0;
 
-static const int kScratchSlots = 9;
+static const int kScratchSlots = 10;
 static void* g_scratch[kScratchSlots] = {nullptr};
 static size_t g_scratch_bytes[kScratchSlots] = {0};
 static unsigned int* g_err_word = nullptr;
@@ -97,6 +97,32 @@ bool conv_stats_take(const float* x, int C, long long rows, double** partial, in
     const bool hit = g_offer.valid && g_offer.y == x && g_offer.C == C && g_offer.rows == rows && g_offer.stamp == g_epoch;
     g_offer.valid = false;
     if (hit) { *partial = g_offer.partial; *slabs = g_offer.slabs; }
+    return hit;
+}
+
+// BatchNorm-backward sums folded into the input-gradient convolution that produces the upstream gradient.
+static BnFold g_fold_pending = {}, g_fold_now = {};
+static bool g_fold_pending_valid = false, g_fold_now_valid = false;
+static struct { const float* dy; BnFold f; int slabs; double* partial; unsigned long long stamp; bool valid; } g_fold_offer = {};
+unsigned long long g_bn_fold_hits = 0;
+static int initial_bn_fold() { const char* e = getenv("NOCTA_BN_FOLD"); return (e && e[0] == '0') ? 0 : 1; }   // NOCTA_BN_FOLD=0: off at start
+static int g_bn_fold_on = initial_bn_fold();
+void bn_fold_announce(const BnFold& f) { g_fold_pending = f; g_fold_pending_valid = true; }
+void bn_fold_enter() { g_fold_now = g_fold_pending; g_fold_now_valid = g_fold_pending_valid; g_fold_pending_valid = false; g_fold_offer.valid = false; }
+void bn_fold_leave() { g_fold_now_valid = false; }
+const BnFold* bn_fold_active() { return g_fold_now_valid ? &g_fold_now : nullptr; }
+double* bn_fold_buffer(size_t slabs, int C, cudaStream_t st) { return (double*)scratch(9, sizeof(double) * 2 * slabs * (size_t)C, st); }
+void bn_fold_publish(const float* dy, int slabs, double* partial) {
+    g_fold_offer.dy = dy; g_fold_offer.f = g_fold_now; g_fold_offer.slabs = slabs;
+    g_fold_offer.partial = partial; g_fold_offer.stamp = g_epoch; g_fold_offer.valid = true;
+}
+bool bn_fold_take(const float* dy, const BnFold& want, double** partial, int* slabs) {
+    const BnFold& f = g_fold_offer.f;
+    const bool hit = g_fold_offer.valid && g_fold_offer.dy == dy && g_fold_offer.stamp == g_epoch && f.x == want.x && f.mean == want.mean &&
+                     f.var == want.var && f.gamma == want.gamma && f.beta == want.beta && f.eps == want.eps && f.C == want.C &&
+                     f.rows == want.rows;
+    g_fold_offer.valid = false;
+    if (hit) { *partial = g_fold_offer.partial; *slabs = g_fold_offer.slabs; ++g_bn_fold_hits; }
     return hit;
 }
 
@@ -336,6 +362,15 @@ int nc_cuda_set_math_mode(int mode) {
 int nc_cuda_get_math_mode(void) { return g_math_mode; }
 int nc_cuda_set_round_outputs(int on) { return ncc::set_round_outputs(on); }
 int nc_cuda_set_conv_stats(int on) { return set_conv_stats(on); }
+int nc_cuda_offer_batchnorm_backward_sums_f32(const float* x, const float* mean, const float* var, const float* gamma, const float* beta,
+                                              double eps, int C, long long rows) {
+    NCC_REQUIRE(x && mean && var && C > 0 && rows > 0, "offer_batchnorm_backward_sums: null pointer or empty shape");
+    BnFold f = {x, mean, var, gamma, beta, (float)eps, C, rows};
+    if (g_bn_fold_on) bn_fold_announce(f);
+    return NC_CUDA_OK;
+}
+int nc_cuda_set_batchnorm_backward_fold(int on) { int p = g_bn_fold_on; g_bn_fold_on = on ? 1 : 0; return p; }
+unsigned long long nc_cuda_batchnorm_backward_fold_count(void) { return g_bn_fold_hits; }
 unsigned int nc_cuda_device_error_word(void) {
     unsigned int* w = device_error_word();
     unsigned int h = 0;

@@ -75,12 +75,20 @@ struct ConvhParams {
     int pitch;             // halo line pitch in pixels
     int halo_bytes, halo_stride;
     double* stat;          // non-null: per CTA and channel (sum, sum of squares) of the output it wrote, [gridDim.x][M][2]
+    // non-null bnx: the output is the upstream gradient g of a BatchNorm+ReLU with input bnx (same shape and strides as D);
+    // stat then receives (sum of g', sum of g' * xhat), g' = g where gamma * xhat + beta > 0 and 0 elsewhere
+    const float* bnx;
+    const float* bn_mean;
+    const float* bn_var;
+    const float* bn_gamma;
+    const float* bn_beta;
+    float bn_eps;
     unsigned int* err;
 };
 
 // PXM: pixels on M.  NCH: output channels / 32 (PXM only; 0 otherwise).
 template <bool PXM, int NCH>
-__global__ void __launch_bounds__(288, 1)
+__global__ void __launch_bounds__(PXM ? 288 : 320, 1)
 convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const ConvhParams p) {
     constexpr int WSMAX = kConvhWStages;
     // MMA-issuing warps.  Channels on M: one.  Pixels on M: one per 8 x 16 pixel block of the tile, and with at most 64
@@ -110,7 +118,7 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
             mbar_init(smem_u32(&bar_hfull[s]), 1);
             mbar_init(smem_u32(&bar_hempty[s]), NISS);     // one arrival per MMA-issuing warp
             mbar_init(smem_u32(&bar_acc_full[s]), NISS);
-            mbar_init(smem_u32(&bar_acc_empty[s]), 128);
+            mbar_init(smem_u32(&bar_acc_empty[s]), PXM ? 128 : 256);   // channels on M: two epilogue warps per lane quarter
         }
         for (int s = 0; s < WS; s++) {
             mbar_init(smem_u32(&bar_wfull[s]), 1);
@@ -172,7 +180,7 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                 }
             }
         }
-    } else if (warp == 1 || warp >= 6) {
+    } else if (warp == 1 || (PXM && warp >= 6)) {
         // ---------------- MMA issuers.  MMAs into one accumulator must come from one thread to stay ordered, and one
         // thread issues an MMA with fresh descriptors only every hundred-odd cycles; with the pixels on M the two
         // 8 x 16 pixel blocks of a tile have their own accumulators, so warp 1 issues the upper block and warp 6 the
@@ -236,22 +244,41 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
         uint32_t tile_iter = 0;
         bool ok = true;
         if (!PXM) {
+            // Eight warps: two per quarter of the accumulator's lanes, `half` 0 takes the even 32-column chunks of a tile and
+            // `half` 1 the odd ones.  One warp per scheduler executes this dependent code at a few cycles per instruction;
+            // with four warps the epilogue of a tile took longer than its MMAs once anything was added to the plain store.
+            const int half = (warp - 2) >> 2;
             // lane = output channel, column = pixel.  Output statistics: a thread owns channel m0 + r of every tile it
             // sees, so it keeps one running pair per channel tile and writes it once (slab = this CTA):
-            // stat[blockIdx.x][M][2].  Slots of channel tiles this CTA never visits must read zero.
+            // stat[2 * blockIdx.x + half][M][2].  Slots of channel tiles this CTA never visits must read zero.
             double ssum = 0.0, ssq = 0.0;
             int stat_m0 = -1;
+            double* const stat_slab = p.stat ? p.stat + (size_t)(2 * blockIdx.x + half) * p.M * 2 : nullptr;
             if (p.stat)
                 for (int mt = 0; mt < p.tiles_m; mt++)
                     if (mt * kBM + r < p.M) {
-                        double* sd = p.stat + ((size_t)blockIdx.x * p.M + mt * kBM + r) * 2;
+                        double* sd = stat_slab + (size_t)(mt * kBM + r) * 2;
                         sd[0] = 0.0; sd[1] = 0.0;
                     }
+            // 128-byte lines (pixel x 32-channel segment) of a tile's part of the BatchNorm input, spread over the 256 threads
+            auto prefetch_tile = [&](int tn) {
+                const int pt = tn % p.tiles_px, m0 = (tn / p.tiles_px) * kBM;
+                const int tw = pt % p.tiles_w, tt = pt / p.tiles_w;
+                const int th = tt % p.tiles_h, n = tt / p.tiles_h;
+                const int rows = (p.Ho - th * kTH) < kTH ? (p.Ho - th * kTH) : kTH;
+                const int wlim = p.Wo - tw * kTW;
+                const float* tb = p.bnx + (((long long)n * p.Ho + th * kTH) * p.Wo + tw * kTW) * p.ldd + m0;
+                const int segs = (p.M - m0 + 31) / 32 < 4 ? (p.M - m0 + 31) / 32 : 4;
+                for (int L = half * 128 + r; L < rows * 32; L += 256) {
+                    const int seg = L & 3, px = L >> 2, hh = px >> 3, j = px & 7;
+                    if (j < wlim && seg < segs) prefetch_l2(tb + ((long long)hh * p.Wo + j) * p.ldd + seg * 32);
+                }
+            };
             for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, tile_iter++) {
                 const int pt = t % p.tiles_px, m0 = (t / p.tiles_px) * kBM;
                 if (p.stat && m0 != stat_m0) {
                     if (stat_m0 >= 0 && stat_m0 + r < p.M) {
-                        double* sd = p.stat + ((size_t)blockIdx.x * p.M + stat_m0 + r) * 2;
+                        double* sd = stat_slab + (size_t)(stat_m0 + r) * 2;
                         sd[0] = ssum; sd[1] = ssq;
                     }
                     ssum = 0.0; ssq = 0.0; stat_m0 = m0;
@@ -260,21 +287,63 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                 const int th = tt % p.tiles_h, n = tt / p.tiles_h;
                 const int rows = (p.Ho - th * kTH) < kTH ? (p.Ho - th * kTH) : kTH;   // image rows this tile holds
                 const int wlim = p.Wo - tw * kTW;                                     // columns j < wlim are inside the image
-                const int last_c0 = ((8 * rows + 31) / 32 - 1) * 32;
+                const int nchunks = (8 * rows + 31) / 32;                             // 32-column chunks of the tile
+                const int first_c0 = half * 32;                                       // this warp: chunks half, half + 2, ...
+                const int last_c0 = (nchunks - 1 - half) >= 0 ? (half + 2 * ((nchunks - 1 - half) / 2)) * 32 : -1;   // -1: none
                 const uint32_t ab = tile_iter & 1u;
-                ok = mbar_wait(smem_u32(&bar_acc_full[ab]), (tile_iter >> 1) & 1u, p.err, 0x400u + ab, abortp);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t acc = tmem_base + ab * 256u + ((uint32_t)(q * 32) << 16);
                 const int co = m0 + r;
                 const bool co_ok = co < p.M;
                 const float bv = (co_ok && p.bias) ? p.bias[co] : 0.f;
                 // first pixel of the tile; a column chunk of 32 = 4 image rows x 8 pixels
                 float* tile_dst = p.D + (((long long)n * p.Ho + th * kTH) * p.Wo + tw * kTW) * p.ldd + co;
                 const int line = p.Wo * p.ldd;  // elements between image rows (< 2^31 checked by the host)
+                const bool bn = p.bnx != nullptr;
+                const float* tile_bsrc = bn ? p.bnx + (tile_dst - p.D) : nullptr;
+                float mu = 0.f, is = 1.f, ga = 1.f, be = 0.f;
+                // BatchNorm input of one column chunk (4 image rows x 8 pixels of this thread's channel)
+                auto load_bn = [&](int c0, float* xb) {
+                    const int h4 = c0 >> 3;
+                    const float* bsrc = tile_bsrc + (long long)h4 * line;
+                    if (!co_ok) return;
+                    if (wlim >= 8 && h4 + 4 <= rows) {
+#pragma unroll
+                        for (int hh = 0; hh < 4; hh++)
+#pragma unroll
+                            for (int j = 0; j < 8; j++) xb[hh * 8 + j] = __ldg(bsrc + hh * line + j * p.ldd);
+                    } else {
+#pragma unroll
+                        for (int hh = 0; hh < 4; hh++)
+#pragma unroll
+                            for (int j = 0; j < 8; j++)
+                                xb[hh * 8 + j] = (h4 + hh < rows && j < wlim) ? __ldg(bsrc + hh * line + j * p.ldd) : 0.f;
+                    }
+                };
+                float xb[32];
+                if (bn) {
+                    // The BatchNorm input of the NEXT tile of this CTA is requested into L2 now, a whole tile ahead of its use
+                    // (the loads of the epilogue are few per SM: from DRAM their latency would bound the kernel), and the first
+                    // chunk of this tile is loaded while its MMAs still run.
+                    if (t == (int)blockIdx.x) prefetch_tile(t);
+                    if (t + (int)gridDim.x < total_tiles) prefetch_tile(t + (int)gridDim.x);
+                    if (co_ok) {
+                        mu = p.bn_mean[co];
+                        is = rsqrtf(p.bn_var[co] + p.bn_eps);
+                        if (p.bn_gamma) ga = p.bn_gamma[co];
+                        if (p.bn_beta) be = p.bn_beta[co];
+                    }
+                    if (last_c0 >= 0) load_bn(first_c0, xb);
+                }
+                ok = mbar_wait(smem_u32(&bar_acc_full[ab]), (tile_iter >> 1) & 1u, p.err, 0x400u + ab, abortp);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc = tmem_base + ab * 256u + ((uint32_t)(q * 32) << 16);
+                if (last_c0 < 0) {   // a tile of at most four image rows has no odd chunk: only release the accumulator
+                    tc_fence_before();
+                    mbar_arrive(smem_u32(&bar_acc_empty[ab]));
+                }
 #pragma unroll 1
-                for (int c0 = 0; c0 <= last_c0; c0 += 32) {
+                for (int c0 = first_c0; c0 <= last_c0; c0 += 64) {
                     uint32_t v[32];
                     tmem_ld32(acc + (uint32_t)c0, v);
                     tmem_ld_wait();
@@ -286,7 +355,47 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                     const int h4 = c0 >> 3;
                     float* dst = tile_dst + (long long)h4 * line;
                     float fs = 0.f, fq = 0.f;
-                    if (wlim >= 8 && h4 + 4 <= rows) {
+                    if (bn) {
+                        // gradient of a BatchNorm+ReLU output: sums of g' and g' * xhat against the BatchNorm's input, whose
+                        // next chunk is requested before this one is used
+                        const bool full = wlim >= 8 && h4 + 4 <= rows;
+                        float xn[32];
+                        if (c0 < last_c0) load_bn(c0 + 64, xn);
+                        if (full) {
+#pragma unroll
+                            for (int hh = 0; hh < 4; hh++) {
+#pragma unroll
+                                for (int j = 0; j < 8; j++) {
+                                    const float o = __uint_as_float(v[hh * 8 + j]) + bv;
+                                    dst[j * p.ldd] = o;
+                                    const float xh = (xb[hh * 8 + j] - mu) * is;
+                                    const float g = ((ga * xh + be) > 0.f) ? o : 0.f;
+                                    fs += g;
+                                    fq = fmaf(g, xh, fq);
+                                }
+                                dst += line;
+                            }
+                        } else {
+#pragma unroll
+                            for (int hh = 0; hh < 4; hh++) {
+#pragma unroll
+                                for (int j = 0; j < 8; j++)
+                                    if (h4 + hh < rows && j < wlim) {
+                                        const float o = __uint_as_float(v[hh * 8 + j]) + bv;
+                                        dst[j * p.ldd] = o;
+                                        const float xh = (xb[hh * 8 + j] - mu) * is;
+                                        const float g = ((ga * xh + be) > 0.f) ? o : 0.f;
+                                        fs += g;
+                                        fq = fmaf(g, xh, fq);
+                                    }
+                                dst += line;
+                            }
+                        }
+                        if (c0 < last_c0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) xb[j] = xn[j];
+                        }
+                    } else if (wlim >= 8 && h4 + 4 <= rows) {
 #pragma unroll
                         for (int hh = 0; hh < 4; hh++) {
 #pragma unroll
@@ -319,7 +428,7 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                 }
             }
             if (p.stat && stat_m0 >= 0 && stat_m0 + r < p.M) {
-                double* sd = p.stat + ((size_t)blockIdx.x * p.M + stat_m0 + r) * 2;
+                double* sd = stat_slab + (size_t)(stat_m0 + r) * 2;
                 sd[0] = ssum; sd[1] = ssq;
             }
         } else {
@@ -367,12 +476,12 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                 const int rows = (p.Ho - th * kTH) < kTH ? (p.Ho - th * kTH) : kTH;
                 const int nsub = rows > 16 ? 2 : 1;
                 const uint32_t ab = tile_iter & 1u;
+                const int w = tw * kTW + (r & 7);
                 ok = mbar_wait(smem_u32(&bar_acc_full[ab]), (tile_iter >> 1) & 1u, p.err, 0x400u + ab, abortp);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t acc = tmem_base + ab * 256u + ((uint32_t)(q * 32) << 16);
-                const int w = tw * kTW + (r & 7);
 #pragma unroll 1
                 for (int sub = 0; sub < nsub; sub++) {
                     const int h = th * kTH + sub * 16 + (r >> 3);
@@ -715,13 +824,28 @@ static int convh_launch(const CUtensorMap& tw, const CUtensorMap& tx, ConvhParam
     const long long total = (long long)p.tiles_px * p.tiles_m;
     const int sms = ncc::sm_count();
     const unsigned grid = (unsigned)(total < sms ? total : sms);
-    if (ncc::conv_stats_wanted()) p.stat = ncc::conv_stats_buffer(grid, p.M, st);
+    const long long rows = (long long)(p.tiles_px / (p.tiles_w * p.tiles_h)) * p.Ho * p.Wo;
+    // an input-gradient call whose output feeds an announced BatchNorm+ReLU backward sums for it on the way out
+    const ncc::BnFold* fold = ncc::bn_fold_active();
+    const unsigned slabs = PXM ? grid : 2 * grid;   // channels on M: two epilogue warps per channel, each with sums of its own
+    // (channels-on-M kernel only: its eight epilogue warps absorb the extra work; with the pixels on M the four epilogue warps
+    // are the slower side of a tile already and the sums cost more there than the reduction they replace)
+    if (!PXM && fold && fold->C == p.M && fold->rows == rows && p.ldd == p.M && !p.bias) {
+        p.stat = ncc::bn_fold_buffer(slabs, p.M, st);
+        if (p.stat) {
+            p.bnx = fold->x; p.bn_mean = fold->mean; p.bn_var = fold->var; p.bn_gamma = fold->gamma; p.bn_beta = fold->beta;
+            p.bn_eps = fold->eps;
+        }
+    } else if (ncc::conv_stats_wanted()) {
+        p.stat = ncc::conv_stats_buffer(slabs, p.M, st);
+    }
     {
         ncc::ProfScope prof(ncc::prof_role(), flops, st, true);
-        convh_kernel<PXM, NCH><<<grid, PXM ? (NCH <= 2 ? 288 : 224) : 192, smem, st>>>(tw, tx, p);
+        convh_kernel<PXM, NCH><<<grid, PXM ? (NCH <= 2 ? 288 : 224) : 320, smem, st>>>(tw, tx, p);
     }
     NCC_COUNT_LAUNCH();
-    if (p.stat) ncc::conv_stats_publish(p.D, p.M, (long long)(p.tiles_px / (p.tiles_w * p.tiles_h)) * p.Ho * p.Wo, (int)grid, p.stat);
+    if (p.bnx) ncc::bn_fold_publish(p.D, (int)slabs, p.stat);
+    else if (p.stat) ncc::conv_stats_publish(p.D, p.M, rows, (int)slabs, p.stat);
     return ncc::launch_status("convh_kernel");
 }
 

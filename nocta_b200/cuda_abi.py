@@ -60,6 +60,9 @@ SIGNATURES = {
     "nc_cuda_get_math_mode": (_i, []),
     "nc_cuda_set_round_outputs": (_i, [_i]),
     "nc_cuda_set_conv_stats": (_i, [_i]),
+    "nc_cuda_offer_batchnorm_backward_sums_f32": (_i, [_p, _p, _p, _p, _p, _d, _i, C.c_longlong]),
+    "nc_cuda_batchnorm_backward_fold_count": (C.c_ulonglong, []),
+    "nc_cuda_set_batchnorm_backward_fold": (_i, [_i]),
     "nc_cuda_device_error_word": (C.c_uint, []),
     "nc_cuda_launch_count": (C.c_ulonglong, []),
     "nc_cuda_reset_launch_count": (None, []),

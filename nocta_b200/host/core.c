@@ -122,6 +122,9 @@ typedef struct pool_bucket { size_t size; pool_block* free_list; struct pool_buc
 static pool_bucket* g_buckets[POOL_HASH];
 static nc_device_pool_stats g_pool;
 
+static size_t g_pool_limit = 0; /* 0: none */
+void nc_device_pool_set_limit(size_t bytes) { g_pool_limit = bytes; }
+size_t nc_device_pool_get_limit(void) { return g_pool_limit; }
 static size_t pool_round(size_t bytes) { return bytes == 0 ? 512 : (bytes + 511) & ~(size_t)511; }
 static pool_bucket* pool_find(size_t size, bool create) {
     size_t h = (size >> 9) % POOL_HASH;
@@ -147,6 +150,13 @@ void* nci_dev_alloc(size_t bytes) {
         g_pool.bytes_in_use += size;
         if (g_pool.bytes_in_use > g_pool.peak_in_use) g_pool.peak_in_use = g_pool.bytes_in_use;
         return p;
+    }
+    if (g_pool_limit && g_pool.bytes_reserved + size > g_pool_limit) {
+        nc_device_pool_release(); /* cached blocks of other sizes count against the limit: hand them back first */
+        if (g_pool.bytes_reserved + size > g_pool_limit) {
+            NC_SET_ERROR(NC_ERR_ALLOC, "device allocation of %zu bytes refused: %zu reserved, limit %zu", size, g_pool.bytes_reserved, g_pool_limit);
+            return NULL;
+        }
     }
     void* p = nc_cuda_malloc(size);
     if (!p) { /* give cached blocks back and retry once */

@@ -213,6 +213,21 @@ nc_tensor* nc_linear_bias(nc_module* l) { return nc_module_get_param(l, "bias");
 /* ------------------------------------------------------------------ Conv2d */
 typedef struct { size_t cin, cout, k, stride, pad; bool has_bias; } conv_cfg;
 
+static nc_tensor** bwd_batchnorm2d(nc_tensor* g, nc_tensor** saved, size_t n);
+/* If `xin` (the convolution's input, read by the kernels as `x`) was produced by a training-mode BatchNorm2d with fused ReLU
+ * in channels-last layout, tell the kernel library so: see nc_cuda_offer_batchnorm_backward_sums_f32. */
+static void announce_bn_backward(const nc_tensor* xin, const nc_tensor* x) {
+    const nc_node* nd = xin->grad_fn;
+    if (!nd || nd->backward != bwd_batchnorm2d || nd->n_saved <= 6 || x != xin || !nci_is_channels_last(x)) return;
+    nc_tensor** sv = nd->saved_tensors;
+    const nc_tensor* bx = sv[0];
+    if (!bx || !sv[2] || !sv[3] || !sv[4] || (int)nc_tensor_get_flat(sv[4], 1) != 1 || bx->numel != x->numel || !nci_on_cuda(bx)) return;
+    const size_t C = x->shape[1];
+    nc_cuda_offer_batchnorm_backward_sums_f32(nci_fptr(bx), nci_fptr(sv[2]), nci_fptr(sv[3]), sv[1] ? nci_fptr(sv[1]) : NULL,
+                                              sv[6] ? nci_fptr(sv[6]) : NULL, nc_tensor_get_flat(sv[4], 0), (int)C,
+                                              (long long)(x->numel / C));
+}
+
 /* node params: [0] stride, [1] padding, [2] Ho, [3] Wo */
 static nc_tensor** bwd_conv2d(nc_tensor* g, nc_tensor** saved, size_t n) {
     (void)n;
@@ -236,11 +251,6 @@ static nc_tensor** bwd_conv2d(nc_tensor* g, nc_tensor** saved, size_t n) {
     size_t xs[4], ys[4];
     nci_strides4(x, xs);
     nci_strides4(gd, ys);
-    if (xin->requires_grad) {
-        out[0] = nci_empty_like(x);
-        if (out[0]) nci_ok(nc_cuda_conv2d_backward_input_f32_ex(nci_fptr(out[0]), xs, nci_fptr(gd), ys, nci_fptr(W), N, Cin, H, Wd, Cout, kH, kW,
-                                                                stride, pad, nci_stream()), "conv2d backward (input)");
-    }
     const bool need_w = W->requires_grad, need_b = b && b->requires_grad;
     if (need_w) out[1] = nci_param_grad_out(1, W);
     if (need_b) out[2] = nci_param_grad_out(2, b);
@@ -248,6 +258,17 @@ static nc_tensor** bwd_conv2d(nc_tensor* g, nc_tensor** saved, size_t n) {
         nci_ok(nc_cuda_conv2d_backward_weight_f32_ex(out[1] ? nci_fptr(out[1]) : NULL, out[2] ? nci_fptr(out[2]) : NULL, nci_fptr(gd), ys,
                                                      nci_fptr(x), xs, N, Cin, H, Wd, Cout, kH, kW, stride, pad, nci_stream()),
                "conv2d backward (weight)");
+    /* the input gradient goes last: when the input is the output of a BatchNorm with fused ReLU, the kernel that writes the
+     * gradient also sums what that BatchNorm's backward needs, and the offer only holds while nothing else is launched
+     * between this call and that backward (the next node of a chain) */
+    if (xin->requires_grad) {
+        out[0] = nci_empty_like(x);
+        if (out[0]) {
+            announce_bn_backward(xin, x);
+            nci_ok(nc_cuda_conv2d_backward_input_f32_ex(nci_fptr(out[0]), xs, nci_fptr(gd), ys, nci_fptr(W), N, Cin, H, Wd, Cout, kH, kW,
+                                                        stride, pad, nci_stream()), "conv2d backward (input)");
+        }
+    }
     if (gd != g) nc_tensor_free(gd);
     return out;
 }

@@ -573,6 +573,77 @@ def test_batchnorm_takes_statistics_offered_by_the_convolution(abi, shape):
         abi.nc_cuda_set_conv_stats(prev)
 
 
+@pytest.mark.parametrize("shape", [(4, 128, 32, 128), (2, 128, 27, 160), (3, 256, 40, 64), (2, 160, 24, 128), (5, 128, 26, 32)])
+def test_batchnorm_backward_takes_sums_from_the_input_gradient_convolution(abi, shape):
+    """nc_cuda_offer_batchnorm_backward_sums_f32: the input-gradient convolution that writes the upstream gradient of a
+    BatchNorm+ReLU also sums g' and g' * xhat per channel, and the BatchNorm backward called right after it skips its own
+    reduction: dx, dgamma, dbeta equal the plain path (sums in another order: 2e-6 of the largest entry), the gradient the
+    convolution stores is bit-identical, the offer is used once, is tied to the tensors, and any launch in between voids it."""
+    from nocta_b200 import cuda_abi
+    N, C, H, Cout = shape                                # C = channels of the BatchNorm = input channels of the convolution (>= 128:
+                                                         # the channels-on-M kernel, the one that serves announcements)
+    rng = np.random.default_rng(C * 7 + Cout)
+    xbn = dev(rng.standard_normal((N, H, H, C)).astype(np.float32))             # BatchNorm input
+    gamma, beta = dev(rng.standard_normal(C).astype(np.float32)), dev((0.3 * rng.standard_normal(C)).astype(np.float32))
+    mean = dev(xbn.reshape(-1, C).mean(0).cpu().numpy())
+    var = dev(xbn.reshape(-1, C).var(0, unbiased=False).cpu().numpy())
+    w = dev((rng.standard_normal((Cout, C, 3, 3)) / (3 * C ** 0.5)).astype(np.float32))
+    dy = dev(rng.standard_normal((N, H, H, Cout)).astype(np.float32))           # gradient of the convolution's output
+    xs = cuda_abi.size4([H * H * C, 1, H * C, C])
+    ys = cuda_abi.size4([H * H * Cout, 1, H * Cout, Cout])
+    g = torch.empty(N, H, H, C, device="cuda")                                  # gradient of the convolution's input
+
+    def offer(x_=None):
+        ok(abi, abi.nc_cuda_offer_batchnorm_backward_sums_f32(P(xbn if x_ is None else x_), P(mean), P(var), P(gamma), P(beta), 1e-5, C, N * H * H))
+    conv_dx = lambda: ok(abi, abi.nc_cuda_conv2d_backward_input_f32_ex(P(g), xs, P(dy), ys, P(w), N, C, H, H, Cout, 3, 3, 1, 1, None))
+
+    def bn_bwd(grad, x_=None):
+        dx, dg, db = torch.empty_like(xbn), torch.empty(C, device="cuda"), torch.empty(C, device="cuda")
+        ok(abi, abi.nc_cuda_batchnorm_backward_f32_ex(P(dx), P(dg), P(db), P(grad), P(xbn if x_ is None else x_), P(gamma), P(mean), P(var), None, P(beta), 1,
+                                                      N, C, H * H, 1e-5, 1, None))
+        return dx, dg, db
+
+    conv_dx()
+    g_plain = g.clone()
+    ref = bn_bwd(g)
+    hits0 = abi.nc_cuda_batchnorm_backward_fold_count()
+    abi.nc_cuda_reset_launch_count()
+    offer(); conv_dx()
+    assert torch.equal(g, g_plain)                        # the stored gradient does not depend on the extra sums
+    base = abi.nc_cuda_launch_count()
+    got = bn_bwd(g)
+    assert abi.nc_cuda_batchnorm_backward_fold_count() == hits0 + 1
+    assert abi.nc_cuda_launch_count() - base == 2          # finalize + apply, no reduction
+    for a, b in zip(got, ref):
+        close(host(a), host(b), 2e-6)
+    # used once
+    bn_bwd(g)
+    assert abi.nc_cuda_batchnorm_backward_fold_count() == hits0 + 1
+    # an announcement is consumed by the next input-gradient call only
+    offer(); conv_dx(); conv_dx()
+    bn_bwd(g)
+    assert abi.nc_cuda_batchnorm_backward_fold_count() == hits0 + 1
+    # a launch in between voids the offer (here it changes the gradient)
+    offer(); conv_dx()
+    ok(abi, abi.nc_cuda_scalar_f32_ex(2, P(g), P(g), 2.0, g.numel(), None))
+    got2 = bn_bwd(g)
+    assert abi.nc_cuda_batchnorm_backward_fold_count() == hits0 + 1
+    close(host(got2[1]), 2 * host(ref[1]), 2e-6)
+    # tied to the gradient tensor and to the BatchNorm's input
+    offer(); conv_dx()
+    bn_bwd(g.clone())
+    assert abi.nc_cuda_batchnorm_backward_fold_count() == hits0 + 1
+    offer(); conv_dx()
+    bn_bwd(g, xbn.clone())
+    assert abi.nc_cuda_batchnorm_backward_fold_count() == hits0 + 1
+    # a shape the announcement does not fit is ignored by the convolution
+    ok(abi, abi.nc_cuda_offer_batchnorm_backward_sums_f32(P(xbn), P(mean), P(var), P(gamma), P(beta), 1e-5, C, N * H * H + 1))
+    conv_dx()
+    bn_bwd(g)
+    assert abi.nc_cuda_batchnorm_backward_fold_count() == hits0 + 1
+    assert abi.nc_cuda_device_error_word() == 0
+
+
 def test_multi_tensor_optimizer_updates_equal_the_single_tensor_kernels(abi):
     """nc_cuda_sgd_update_multi_f32_ex / nc_cuda_adam_update_multi_f32_ex: bit-equal to one call per tensor, for
     ragged sizes (1 element, not a multiple of the chunk, empty) and more tensors than one launch table holds."""

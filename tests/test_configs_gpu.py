@@ -123,6 +123,41 @@ def test_training_step_matches_reference(ours, theirs, name, kw, steps, mode):
     assert ours.api.lib.nc_cuda_device_error_word() == 0
 
 
+def test_batchnorm_backward_sums_come_from_the_input_gradient_kernel(ours):
+    """In a conv -> BatchNorm+ReLU -> conv chain the second convolution's input-gradient kernel (halo-resident with the channels
+    on M: 128 channels or more, TF32 mode, images of 24 rows or more) also sums what the BatchNorm backward needs: the fold is
+    taken once per such pair and step, and training equals the run with the fold switched off up to the order of the additions."""
+    import ctypes as C
+    from nocta_b200 import configs
+    lib = ours.api.lib
+    lib.nc_cuda_batchnorm_backward_fold_count.restype = C.c_ulonglong
+    lib.nc_cuda_set_batchnorm_backward_fold.argtypes = [C.c_int]
+    kw = dict(batch=4, size=32, widths=(128, 32, 32), classes=10)
+
+    def steps(on):
+        prev = lib.nc_cuda_set_batchnorm_backward_fold(on)
+        try:
+            before = lib.nc_cuda_batchnorm_backward_fold_count()
+            out = run(ours, configs.BUILDERS["vgg"], 3, **kw)
+            return out, lib.nc_cuda_batchnorm_backward_fold_count() - before
+        finally:
+            lib.nc_cuda_set_batchnorm_backward_fold(prev)
+
+    # The offer holds only while nothing else is launched between the two kernels.  In the very first step of a network the
+    # weight gradient of the convolution is ADDED to a zero gradient that already exists (one launch), from the second step
+    # on it is adopted in place of the cleared one: steps 2 and 3 fold bn0 (128 channels at 32 x 32, behind conv1's input
+    # gradient).
+    plain, n_plain = steps(0)
+    folded, n_folded = steps(1)
+    assert n_plain == 0 and n_folded >= 2, (n_plain, n_folded)
+    assert folded["loss"][0] == plain["loss"][0]
+    for la, lb in zip(folded["loss"], plain["loss"]):
+        assert abs(la - lb) <= 1e-5 * abs(lb), (folded["loss"], plain["loss"])
+    for k, w in plain["params"].items():
+        assert max(O.rel_errors(folded["params"][k], w)) <= 1e-5, k
+    assert lib.nc_cuda_device_error_word() == 0
+
+
 @pytest.mark.parametrize("name,kw", [("lenet", dict()), ("convbn", dict(batch=16)), ("vgg", dict(batch=8, size=16, widths=(32, 64, 128), classes=10))])
 def test_eval_mode_predictions_match_reference(ours, theirs, name, kw):
     """Two training steps, then the inference half of the loop on a held-out batch: eval-mode logits at
