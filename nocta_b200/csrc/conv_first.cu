@@ -6,6 +6,8 @@
 // memory (see dw_tile_kernel); per-CTA partial sums are combined in a fixed order.  No input gradient: the network input needs none.
 // Semantics: src/nn/conv.c:269-299 (dW), :381-586 (forward) of the reference.
 #include "nc_common.cuh"
+#include "tc_ptx.cuh"
+#include "../../include/nocta_cuda.h"
 
 namespace convfirst {
 
@@ -334,6 +336,206 @@ __global__ void __launch_bounds__(256) dw_reduce_kernel(float* __restrict__ dW, 
     if (lane == 0) dW[i] = (float)acc;
 }
 
+// ------------------------------------------------------------------------------------------
+// Tensor-core forward (TF32 mode, 64 output channels).  The 27-wide patch of an output pixel, padded to 32 floats, is
+// exactly one 128-byte row of a K-major tcgen05 operand.  Weights (64 rows + 64 zero rows, x 32) are the A operand, a tile
+// of 128 pixels' patches the B operand: four kind::tf32 MMAs (K = 8 each) leave channel co of pixel j in lane co, column j
+// of tensor memory.  No TMA: eight builder warps gather the patches (the input is small and stays in L2) and write the rows
+// with the 128-byte swizzle the MMA expects into a ring of four tiles; warp 16 issues the MMAs into a ring of four
+// accumulators; eight epilogue warps read them (lane = channel), add the bias and store: for one pixel a warp writes 32
+// consecutive floats, i.e. whole 128-byte lines (with the pixels on the lanes every store instruction would touch 32
+// different lines, and the rate of such requests, not the bytes, bounds the kernel).  The rings let each role run ahead of
+// the next by up to four tiles, which hides the load, tensor-memory and store latencies.
+// ------------------------------------------------------------------------------------------
+namespace tcf {
+using namespace tc;
+constexpr int G = 4;                 // ring depth: patch tiles and accumulators in flight per CTA
+constexpr int COUT = 64;
+constexpr int P_BYTES = 128 * 128;   // one patch tile: 128 pixels x 32 floats
+constexpr int W_BYTES = 128 * 128;   // weights padded to 128 rows
+constexpr int SMEM = G * P_BYTES + W_BYTES + 1024;
+
+__device__ __forceinline__ uint32_t idesc_tf32_k(uint32_t M, uint32_t N) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);   // D f32, A = B = tf32, both K-major
+}
+// byte offset of 16-byte chunk c of row r in a K-major tile with 128-byte rows and the 128-byte swizzle
+__device__ __forceinline__ uint32_t sw128(int r, int c) { return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4)); }
+
+__global__ void __launch_bounds__(544, 1) fwd_kernel(float* __restrict__ y, const float* __restrict__ in, const float* __restrict__ w,
+                                                     const float* __restrict__ bias, Geo g, int pixels, int ntiles,
+                                                     double* __restrict__ stat, unsigned int* err) {
+    extern __shared__ uint8_t dyn[];
+    __shared__ __align__(8) uint64_t bar_p_full[G], bar_p_empty[G], bar_acc_full[G], bar_acc_empty[G];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    __shared__ double st_comb[8][32][2];
+    const uint32_t base = (smem_u32(dyn) + 1023u) & ~1023u;
+    uint8_t* gen = dyn + (base - smem_u32(dyn));
+    const uint32_t w_base = base + G * P_BYTES;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* abortp = &abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < G; i++) {
+            mbar_init(smem_u32(&bar_p_full[i]), 128);
+            mbar_init(smem_u32(&bar_p_empty[i]), 1);
+            mbar_init(smem_u32(&bar_acc_full[i]), 1);
+            mbar_init(smem_u32(&bar_acc_empty[i]), 256);
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // weights = the A operand: row co, K index (ci, kh, kw) as the reference stores them, padded with zeros to 32, rounded to
+    // TF32; rows 64..127 are zero (the MMA wants M = 128, those accumulator lanes are never read)
+    for (int i = threadIdx.x; i < 128 * 8; i += blockDim.x) {
+        const int co = i >> 3, c = i & 7;
+        float4 q;
+        float* qf = reinterpret_cast<float*>(&q);
+#pragma unroll
+        for (int e = 0; e < 4; e++) { const int k = c * 4 + e; qf[e] = (co < COUT && k < K) ? ncc::round_tf32(w[co * K + k]) : 0.f; }
+        *reinterpret_cast<float4*>(gen + G * P_BYTES + sw128(co, c)) = q;
+    }
+    if (warp == 16) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the weight tile is read by the tensor core
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    // tiles of this CTA: local index i is tile blockIdx.x + i * gridDim.x, patch buffer and accumulator i % G
+    const int nloc = ((int)blockIdx.x < ntiles) ? (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+
+    if (warp == 16) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = idesc_tf32_k(128u, 128u);
+            const uint64_t dW = smem_desc(w_base, 16u, 1024u, 2u);
+            for (int i = 0; i < nloc; i++) {
+                const int b = i & (G - 1);
+                const uint32_t ph = (uint32_t)((i / G) & 1);
+                if (!mbar_wait(smem_u32(&bar_p_full[b]), ph, err, 0xC00u + b, abortp)) break;
+                if (!mbar_wait(smem_u32(&bar_acc_empty[b]), ph ^ 1u, err, 0xC10u + b, abortp)) break;
+                tc_fence_after();
+                const uint64_t dP = smem_desc(base + (uint32_t)(b * P_BYTES), 16u, 1024u, 2u);
+#pragma unroll
+                for (int ks = 0; ks < 4; ks++) umma_tf32(tmem_base + (uint32_t)(b * 128), dW + (uint64_t)(ks * 2), dP + (uint64_t)(ks * 2), idesc, ks != 0);
+                umma_commit(smem_u32(&bar_p_empty[b]));
+                umma_commit(smem_u32(&bar_acc_full[b]));
+            }
+        }
+    } else if ((warp & 3) >= 2) {
+        // ---------------- builders (warps 2, 3, 6, 7, 10, 11, 14, 15): two sets of four warps, one set per tile; a thread
+        // gathers one pixel's patch and writes its 128-byte row of the B operand ----------------
+        const int bw = (warp >> 2) * 2 + (warp & 1);   // 0..7
+        const int set = bw >> 2, r = (bw & 3) * 32 + lane;
+        for (int i = set; i < nloc; i += 2) {
+            const int b = i & (G - 1);
+            const int p = ((int)blockIdx.x + i * (int)gridDim.x) * 128 + r;
+            float x[K];
+            if (p < pixels) {
+                const int wo = p % g.Wo;
+                const int t = p / g.Wo;
+                load_patch(x, in, g, t / g.Ho, t % g.Ho, wo);
+            } else {
+#pragma unroll
+                for (int k = 0; k < K; k++) x[k] = 0.f;
+            }
+            if (!mbar_wait(smem_u32(&bar_p_empty[b]), (uint32_t)(((i / G) & 1) ^ 1), err, 0xC20u + b, abortp)) break;
+            uint8_t* prow = gen + b * P_BYTES;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                float4 qv;
+                float* qf = reinterpret_cast<float*>(&qv);
+#pragma unroll
+                for (int e = 0; e < 4; e++) qf[e] = (c * 4 + e) < K ? ncc::round_tf32(x[(c * 4 + e) < K ? (c * 4 + e) : 0]) : 0.f;
+                *reinterpret_cast<float4*>(prow + sw128(r, c)) = qv;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(smem_u32(&bar_p_full[b]));
+        }
+    } else {
+        // ---------------- epilogue (warps 0, 1, 4, 5, 8, 9, 12, 13).  The accumulator holds channel co in lane co and pixel j
+        // of the tile in column j; warp % 4 (0 or 1) is the quarter of the lanes a warp may read = its 32 channels, and the
+        // four warps of a quarter take one 32-pixel chunk of every tile each.  For one pixel the 32 lanes store 32
+        // consecutive floats: whole 128-byte lines.  A thread owns one channel, so the sums for the BatchNorm that
+        // follows are plain running sums. ----------------
+        const int q = warp & 1, chunk = warp >> 2, co = q * 32 + lane;
+        const float bv = bias ? bias[co] : 0.f;
+        double ssum = 0.0, ssq = 0.0;
+        for (int i = 0; i < nloc; i++) {
+            const int b = i & (G - 1);
+            const int p0 = ((int)blockIdx.x + i * (int)gridDim.x) * 128 + chunk * 32;
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_acc_full[b]), (uint32_t)((i / G) & 1), err, 0xC30u + b, abortp));
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t v[32];
+            tmem_ld32(tmem_base + (uint32_t)(b * 128 + chunk * 32) + ((uint32_t)(q * 32) << 16), v);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(smem_u32(&bar_acc_empty[b]));
+            float* dst = y + (size_t)p0 * COUT + co;
+            float fs = 0.f, fq = 0.f;
+            if (p0 + 32 <= pixels) {
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    const float o = __uint_as_float(v[j]) + bv;
+                    dst[j * COUT] = o;
+                    fs += o;
+                    fq = fmaf(o, o, fq);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; j++)
+                    if (p0 + j < pixels) {
+                        const float o = __uint_as_float(v[j]) + bv;
+                        dst[j * COUT] = o;
+                        fs += o;
+                        fq = fmaf(o, o, fq);
+                    }
+            }
+            ssum += (double)fs;
+            ssq += (double)fq;
+        }
+        const int ew = (warp >> 2) * 2 + (warp & 1);   // 0..7
+        st_comb[ew][lane][0] = ssum;
+        st_comb[ew][lane][1] = ssq;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (stat && threadIdx.x < COUT) {   // the four warps of a channel's quarter in a fixed order
+        const int q = threadIdx.x >> 5, l = threadIdx.x & 31;
+        double a = 0.0, b = 0.0;
+        for (int c = 0; c < 4; c++) { a += st_comb[c * 2 + q][l][0]; b += st_comb[c * 2 + q][l][1]; }
+        stat[((size_t)blockIdx.x * COUT + threadIdx.x) * 2] = a;
+        stat[((size_t)blockIdx.x * COUT + threadIdx.x) * 2 + 1] = b;
+    }
+    if (warp == 16) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+}  // namespace tcf
+
+static int forward_tc(float* y, const float* x, const float* w, const float* bias, const Geo& g, cudaStream_t st) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        NCC_TRY(cudaFuncSetAttribute(tcf::fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tcf::SMEM));
+        attr_set = true;
+    }
+    const int pixels = g.N * g.Ho * g.Wo;
+    const int ntiles = (pixels + 127) / 128;
+    const int sms = ncc::sm_count();
+    const int grid = ntiles < sms ? ntiles : sms;
+    double* stat = ncc::conv_stats_wanted() ? ncc::conv_stats_buffer((size_t)grid, tcf::COUT, st) : nullptr;
+    tcf::fwd_kernel<<<grid, 544, tcf::SMEM, st>>>(y, x, w, bias, g, pixels, ntiles, stat, ncc::device_error_word());
+    NCC_COUNT_LAUNCH();
+    const int rc = ncc::launch_status("conv_first forward (tensor core)");
+    if (rc == NC_CUDA_OK && stat) ncc::conv_stats_publish(y, tcf::COUT, (long long)pixels, grid, stat);
+    return rc;
+}
+
 // 32-bit index arithmetic is used throughout: everything addressed must stay below 2^31 elements
 static bool fits_int(int N, int H, int W, const long long xs[4], int Ho, int Wo) {
     long long span = 1 + (long long)(N - 1) * xs[0] + 2 * xs[1] + (long long)(H - 1) * xs[2] + (long long)(W - 1) * xs[3];
@@ -352,6 +554,7 @@ int forward(float* y, const float* x, const long long xs[4], const float* w, con
     if ((reinterpret_cast<uintptr_t>(y) & 15u) != 0) return NC_CUDA_ERR_UNSUPPORTED;
     if (!fits_int(N, H, W, xs, g.Ho, g.Wo)) return NC_CUDA_ERR_UNSUPPORTED;
     const int pixels = N * g.Ho * g.Wo;
+    if (Cout == tcf::COUT && ncc::math_mode() == NC_CUDA_MATH_TF32) return forward_tc(y, x, w, bias, g, st);
     if (Cout == 16 || Cout == 32 || Cout == 64 || Cout == 128) {
         double* stat = nullptr;
         int slabs;
