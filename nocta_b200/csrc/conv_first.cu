@@ -536,6 +536,179 @@ static int forward_tc(float* y, const float* x, const float* w, const float* bia
     return rc;
 }
 
+// ------------------------------------------------------------------------------------------
+// Tensor-core weight gradient (TF32 mode, 64 output channels): dW[co][k] = sum over pixels of dY[pixel][co] * patch[pixel][k].
+// The reduction runs over pixels, so both operands are MN-major: a pixel is a reduction row of 128 bytes per 32-value chunk.
+// A stage holds TWO pixel tiles of 128: the A operand is dY of tile 0 (two 32-channel chunks) followed by dY of tile 1 (two
+// more) = 128 "rows", the B operand the patch tile of tile 0 followed by that of tile 1 = 64 "columns".  One MMA
+// (128 x 64 x 8 pixels) then accumulates tile 0's product in lanes 0-63 x columns 0-31 and tile 1's in lanes 64-127 x
+// columns 32-63; the two off-diagonal blocks pair different pixels and are never read.  That gives the full M = 128 MMA
+// shape from a 64-channel gradient without zero padding.  dY arrives by TMA (128-byte swizzle on 32-byte units, the
+// layout MN-major 32-bit operands need), the patch tiles are written by the builder warps with the same swizzle.
+// Every CTA leaves two partial 64 x 32 blocks; dw_reduce_kernel adds all of them in a fixed order.
+// ------------------------------------------------------------------------------------------
+namespace tcw {
+using namespace tc;
+constexpr int COUT = 64;
+constexpr int CHUNK = 128 * 128;               // 128 pixels x 32 floats
+constexpr int STAGE = 6 * CHUNK;               // dY: 4 chunks, patches: 2 chunks
+constexpr int STAGES = 2;
+constexpr int SMEM = STAGES * STAGE + 1024;
+
+__device__ __forceinline__ uint32_t idesc_tf32_mn(uint32_t M, uint32_t N) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | (1u << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);   // both operands MN-major
+}
+// byte offset of 16-byte piece c (0..7) of reduction row r in an MN-major chunk: 128-byte swizzle on 32-byte units
+__device__ __forceinline__ uint32_t sw32(int r, int c) { return (uint32_t)(r * 128 + ((((c >> 1) ^ (r & 3))) << 5) + ((c & 1) << 4)); }
+
+__global__ void __launch_bounds__(320, 1) dw_kernel(const __grid_constant__ CUtensorMap tmDy, float* __restrict__ partial,
+                                                    const float* __restrict__ in, Geo g, int pixels, int npairs, unsigned int* err) {
+    extern __shared__ uint8_t dyn[];
+    __shared__ __align__(8) uint64_t bar_full[STAGES], bar_empty[STAGES], bar_done;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    const uint32_t base = (smem_u32(dyn) + 1023u) & ~1023u;
+    uint8_t* gen = dyn + (base - smem_u32(dyn));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* abortp = &abort_flag;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; i++) { mbar_init(smem_u32(&bar_full[i]), 257); mbar_init(smem_u32(&bar_empty[i]), 1); }
+        mbar_init(smem_u32(&bar_done), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(64u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    // tile pairs of this CTA: local index i is pair blockIdx.x + i * gridDim.x, stage i % 2
+    const int nloc = ((int)blockIdx.x < npairs) ? (npairs - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+
+    if (warp == 8) {
+        // ---------------- dY by TMA: four boxes of 32 channels x 128 pixels (rows past the last pixel arrive as zeros) ----------------
+        if (lane == 0) {
+            for (int i = 0; i < nloc; i++) {
+                const int s = i & 1;
+                if (!mbar_wait(smem_u32(&bar_empty[s]), (uint32_t)(((i >> 1) & 1) ^ 1), err, 0xE00u + s, abortp)) break;
+                const int pix0 = ((int)blockIdx.x + i * (int)gridDim.x) * 256;
+                const uint32_t full = smem_u32(&bar_full[s]);
+                mbar_expect_tx(full, 4u * CHUNK);
+                const uint32_t a = base + (uint32_t)(s * STAGE);
+                tma_2d(a, &tmDy, 0, pix0, full);
+                tma_2d(a + CHUNK, &tmDy, 32, pix0, full);
+                tma_2d(a + 2 * CHUNK, &tmDy, 0, pix0 + 128, full);
+                tma_2d(a + 3 * CHUNK, &tmDy, 32, pix0 + 128, full);
+            }
+        }
+    } else if (warp == 9) {
+        // ---------------- MMA issuer: 16 k-steps of 8 pixels per stage, one accumulator for the whole kernel ----------------
+        if (lane == 0) {
+            const uint32_t idesc = idesc_tf32_mn(128u, 64u);
+            bool ok = true;
+            for (int i = 0; i < nloc && ok; i++) {
+                const int s = i & 1;
+                if (!mbar_wait(smem_u32(&bar_full[s]), (uint32_t)((i >> 1) & 1), err, 0xE10u + s, abortp)) { ok = false; break; }
+                tc_fence_after();
+                const uint64_t dA = smem_desc(base + (uint32_t)(s * STAGE), (uint32_t)CHUNK, 512u, 1u);
+                const uint64_t dB = smem_desc(base + (uint32_t)(s * STAGE + 4 * CHUNK), (uint32_t)CHUNK, 512u, 1u);
+#pragma unroll
+                for (int k = 0; k < 16; k++) umma_tf32(tmem_base, dA + (uint64_t)(k * 64), dB + (uint64_t)(k * 64), idesc, (i | k) != 0);
+                umma_commit(smem_u32(&bar_empty[s]));
+            }
+            if (ok) umma_commit(smem_u32(&bar_done));
+        }
+    } else {
+        // ---------------- builders: warps 0-3 the first tile of a pair, warps 4-7 the second; a thread gathers one pixel's
+        // patch and writes its 128-byte reduction row ----------------
+        const int half = warp >> 2, r = (warp & 3) * 32 + lane;
+        for (int i = 0; i < nloc; i++) {
+            const int s = i & 1;
+            const int p = ((int)blockIdx.x + i * (int)gridDim.x) * 256 + half * 128 + r;
+            float x[K];
+            if (p < pixels) {
+                const int wo = p % g.Wo;
+                const int t = p / g.Wo;
+                load_patch(x, in, g, t / g.Ho, t % g.Ho, wo);
+            } else {
+#pragma unroll
+                for (int k = 0; k < K; k++) x[k] = 0.f;
+            }
+            if (!mbar_wait(smem_u32(&bar_empty[s]), (uint32_t)(((i >> 1) & 1) ^ 1), err, 0xE20u + s, abortp)) break;
+            uint8_t* prow = gen + s * STAGE + (4 + half) * CHUNK;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                float4 qv;
+                float* qf = reinterpret_cast<float*>(&qv);
+#pragma unroll
+                for (int e = 0; e < 4; e++) qf[e] = (c * 4 + e) < K ? ncc::round_tf32(x[(c * 4 + e) < K ? (c * 4 + e) : 0]) : 0.f;
+                *reinterpret_cast<float4*>(prow + sw32(r, c)) = qv;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(smem_u32(&bar_full[s]));
+        }
+        if (warp < 4) {
+            // ---------------- the end: lanes 0-63 hold tile-0 sums in columns 0-31, lanes 64-127 tile-1 sums in columns 32-63 ----------------
+            const bool ok = nloc == 0 || __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_done), 0u, err, 0xE30u, abortp));
+            const int L = warp * 32 + lane, h = L >> 6, co = L & 63;
+            float* dst = partial + ((size_t)(2 * blockIdx.x + h) * COUT + co) * KP;
+            if (ok && nloc > 0) {
+                tc_fence_after();
+                uint32_t v[32];
+                tmem_ld32(tmem_base + (uint32_t)(h * 32) + ((uint32_t)(warp * 32) << 16), v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        // a wait expired somewhere: give copies still in flight time to land before the shared memory is released
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) { }
+        __syncthreads();
+    }
+    if (warp == 9) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(64u) : "memory");
+    }
+}
+}  // namespace tcw
+
+static int weight_grad_tc(float* dW, const float* dy, const float* x, const Geo& g, cudaStream_t st) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        NCC_TRY(cudaFuncSetAttribute(tcw::dw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tcw::SMEM));
+        attr_set = true;
+    }
+    const int pixels = g.N * g.Ho * g.Wo;
+    const int npairs = (pixels + 255) / 256;
+    const int sms = ncc::sm_count();
+    const int grid = npairs < sms ? npairs : sms;
+    CUtensorMap tm;
+    unsigned long long dims[2] = {(unsigned long long)tcw::COUT, (unsigned long long)pixels};
+    unsigned long long str[1] = {(unsigned long long)tcw::COUT};
+    unsigned box[2] = {32, 128};
+    if (!tc::make_map(&tm, dy, 2, dims, str, box, true)) return NC_CUDA_ERR_UNSUPPORTED;
+    float* partial = (float*)ncc::scratch(2, sizeof(float) * (size_t)(2 * grid) * tcw::COUT * KP, st);
+    if (!partial) return NC_CUDA_ERR_RUNTIME;
+    tcw::dw_kernel<<<grid, 320, tcw::SMEM, st>>>(tm, partial, x, g, pixels, npairs, ncc::device_error_word());
+    NCC_COUNT_LAUNCH();
+    dw_reduce_kernel<<<ncc::ceil_div(tcw::COUT * K * 32, 256), 256, 0, st>>>(dW, partial, 2 * grid, tcw::COUT);
+    NCC_COUNT_LAUNCH();
+    return ncc::launch_status("conv_first weight_grad (tensor core)");
+}
+
 // 32-bit index arithmetic is used throughout: everything addressed must stay below 2^31 elements
 static bool fits_int(int N, int H, int W, const long long xs[4], int Ho, int Wo) {
     long long span = 1 + (long long)(N - 1) * xs[0] + 2 * xs[1] + (long long)(H - 1) * xs[2] + (long long)(W - 1) * xs[3];
@@ -583,6 +756,10 @@ int weight_grad(float* dW, const float* dy, const float* x, const long long xs[4
     if (g.Ho <= 0 || g.Wo <= 0) return NC_CUDA_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(dy) & 15u) != 0) return NC_CUDA_ERR_UNSUPPORTED;
     if (!fits_int(N, H, W, xs, g.Ho, g.Wo)) return NC_CUDA_ERR_UNSUPPORTED;
+    if (Cout == tcw::COUT && ncc::math_mode() == NC_CUDA_MATH_TF32) {
+        const int rc = weight_grad_tc(dW, dy, x, g, st);
+        if (rc != NC_CUDA_ERR_UNSUPPORTED) return rc;
+    }
     constexpr int TRW = 4;  // rows per strip of dw_tile_kernel
     const int tiles_h = (g.Ho + TRW - 1) / TRW, tiles_w = (g.Wo + TW - 1) / TW;
     const long long ntiles = (long long)N * tiles_h * tiles_w;

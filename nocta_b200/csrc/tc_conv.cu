@@ -107,7 +107,7 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
     __shared__ double stat_sh[PXM ? 4 * NCH * 32 * 2 : 1];
-    __shared__ float stat_tile[PXM ? 4 : 1][PXM ? 32 : 1][PXM ? 33 : 1];   // per epilogue warp: 32 pixels x 32 channels, transposed to sum over pixels
+    __shared__ __align__(16) float stat_tile[PXM ? 4 : 1][PXM ? 32 : 1][PXM ? 36 : 1];   // per epilogue warp: 32 pixels x 32 channels, transposed between the accumulator (lane = pixel) and the store (lane = channel)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t halo_base = (smem_u32(dyn_smem) + 1023u) & ~1023u;
@@ -476,7 +476,6 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                 const int rows = (p.Ho - th * kTH) < kTH ? (p.Ho - th * kTH) : kTH;
                 const int nsub = rows > 16 ? 2 : 1;
                 const uint32_t ab = tile_iter & 1u;
-                const int w = tw * kTW + (r & 7);
                 ok = mbar_wait(smem_u32(&bar_acc_full[ab]), (tile_iter >> 1) & 1u, p.err, 0x400u + ab, abortp);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
@@ -484,9 +483,6 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                 const uint32_t acc = tmem_base + ab * 256u + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
                 for (int sub = 0; sub < nsub; sub++) {
-                    const int h = th * kTH + sub * 16 + (r >> 3);
-                    const bool px_ok = (w < p.Wo) && (h < p.Ho);
-                    float* dst = p.D + (((long long)n * p.Ho + h) * p.Wo + w) * p.ldd + m0;
 #pragma unroll
                     for (int ch = 0; ch < NCH; ch++) {
                         uint32_t v[32];
@@ -503,6 +499,10 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                             tc_fence_before();
                             mbar_arrive(smem_u32(&bar_acc_empty[ab]));
                         }
+                        // Transposed through the warp's tile: a thread holds 32 channels of ONE pixel, and storing them as they
+                        // are would make every store instruction touch 32 different 128-byte lines (the rate of such requests, not
+                        // the bytes, then bounds the epilogue).  After the transposition lane c holds channel c, and for one pixel
+                        // the warp stores one whole line.
 #pragma unroll
                         for (int j = 0; j < 32; j += 4) {
                             float4 o;
@@ -512,27 +512,41 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                                 const float4 b4 = *reinterpret_cast<const float4*>(p.bias + m0 + ch * 32 + j);
                                 o.x += b4.x; o.y += b4.y; o.z += b4.z; o.w += b4.w;
                             }
-                            if (px_ok) *reinterpret_cast<float4*>(dst + ch * 32 + j) = o;
-                            if (want_stat) {
-                                stat_tile[wq][lane][j] = px_ok ? o.x : 0.f;
-                                stat_tile[wq][lane][j + 1] = px_ok ? o.y : 0.f;
-                                stat_tile[wq][lane][j + 2] = px_ok ? o.z : 0.f;
-                                stat_tile[wq][lane][j + 3] = px_ok ? o.w : 0.f;
-                            }
+                            *reinterpret_cast<float4*>(&stat_tile[wq][lane][j]) = o;
                         }
-                        if (want_stat) {
-                            __syncwarp();
+                        __syncwarp();
+                        {
+                            // the warp's 32 pixels: 4 image rows x 8 columns starting at (h0, w0)
+                            const int w0 = tw * kTW, h0 = th * kTH + sub * 16 + q * 4;
+                            const int wlim = p.Wo - w0, hlim = p.Ho - h0;
+                            float* pb = p.D + (((long long)n * p.Ho + h0) * p.Wo + w0) * p.ldd + m0 + ch * 32 + lane;
+                            const int rowstep = p.Wo * p.ldd;
                             float a = 0.f, b = 0.f;
+                            if (wlim >= 8 && hlim >= 4 && !want_stat) {
 #pragma unroll
-                            for (int k = 0; k < 32; k++) {
-                                const float o = stat_tile[wq][k][lane];
-                                a += o;
-                                b = fmaf(o, o, b);
+                                for (int k = 0; k < 32; k++) pb[(k >> 3) * rowstep + (k & 7) * p.ldd] = stat_tile[wq][k][lane];
+                            } else if (wlim >= 8 && hlim >= 4) {
+#pragma unroll
+                                for (int k = 0; k < 32; k++) {
+                                    const float o = stat_tile[wq][k][lane];
+                                    pb[(k >> 3) * rowstep + (k & 7) * p.ldd] = o;
+                                    a += o;
+                                    b = fmaf(o, o, b);
+                                }
+                            } else {
+#pragma unroll
+                                for (int k = 0; k < 32; k++)
+                                    if ((k & 7) < wlim && (k >> 3) < hlim) {
+                                        const float o = stat_tile[wq][k][lane];
+                                        pb[(k >> 3) * rowstep + (k & 7) * p.ldd] = o;
+                                        a += o;
+                                        b = fmaf(o, o, b);
+                                    }
                             }
                             fs[ch] += (double)a;
                             fq[ch] += (double)b;
-                            __syncwarp();
                         }
+                        __syncwarp();
                     }
                 }
             }

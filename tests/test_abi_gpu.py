@@ -384,6 +384,9 @@ CONV_CASES = [
     (4, 128, 16, 16, 256, 3, 1, 1),
     (16, 32, 12, 12, 64, 5, 1, 2),
     (4, 3, 16, 16, 64, 3, 1, 1),    # first-layer kernels (3 input channels)
+    (3, 3, 9, 11, 64, 3, 1, 1),     # 297 pixels: a ragged 128-pixel tile, an odd number of tiles
+    (5, 3, 24, 40, 64, 3, 1, 0),    # no padding, 22 x 38 outputs
+    (64, 3, 32, 32, 64, 3, 1, 1),   # 512 tiles: several per CTA, the rings of the tensor-core kernels wrap
     (3, 3, 9, 11, 32, 3, 1, 0),
     # shapes the halo-resident tensor-core kernels take in plain TF32 mode: whole 8-wide pixel tiles, >= 32 channels
     (2, 32, 32, 8, 32, 3, 1, 1),
