@@ -265,7 +265,8 @@ def roofline_objects(fam, peaks, step_ms, workload):
         res["roofline_hbm"] = memory(("adam", "layernorm", "activation", "elementwise", "batchnorm", "maxpool"),
                                      "optimizer, normalisation and activation kernels")
     else:
-        res["roofline_hbm"] = memory(("batchnorm", "maxpool", "sgd"), "BatchNorm(+ReLU, +max-pool) forward / backward and the SGD update")
+        res["roofline_hbm"] = memory(("batchnorm", "maxpool", "sgd", "conv_first"),
+                                     "BatchNorm(+ReLU, +max-pool) forward / backward, the SGD update and the first-layer convolution (3 input channels: bound by its 268 MB output / gradient)")
     if res["roofline"] is not None and workload in NCU_TRAFFIC:
         res["roofline"]["traffic"], note = NCU_TRAFFIC[workload]
         res["roofline"]["traffic_source"] = "ncu capture summarised under profiles/, not measured by this run: " + note
