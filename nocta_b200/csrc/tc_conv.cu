@@ -74,6 +74,7 @@ struct ConvhParams {
     int wslot_bytes;       // one slot holds the kW taps of a filter row (one mbarrier round trip per 4 * kW MMAs)
     int pitch;             // halo line pitch in pixels
     int halo_bytes, halo_stride;
+    int half_rows;         // DUAL: halo lines per image (the tile holds two images of 16 rows, one above the other)
     double* stat;          // non-null: per CTA and channel (sum, sum of squares) of the output it wrote, [gridDim.x][M][2]
     // non-null bnx: the output is the upstream gradient g of a BatchNorm+ReLU with input bnx (same shape and strides as D);
     // stat then receives (sum of g', sum of g' * xhat), g' = g where gamma * xhat + beta > 0 and 0 elsewhere
@@ -86,16 +87,20 @@ struct ConvhParams {
     unsigned int* err;
 };
 
-// PXM: pixels on M.  NCH: output channels / 32 (PXM only; 0 otherwise).
-template <bool PXM, int NCH>
-__global__ void __launch_bounds__(PXM ? 288 : 320, 1)
+// PXM: pixels on M.  NCH: output channels / 32 (PXM only; 0 otherwise).  DUAL (channels on M only): images of 16 rows, two
+// per tile.  The output of an image pair is one run of 32 pixel rows, so everything but the halo load and the MMA issue sees
+// a 32-row image; the halo box spans two images (each with its own padding lines), and because the second image's lines do
+// not continue the first one's at the stride of a pixel row, each image half (N = 128) has its own issuing warp and its own
+// half of the accumulator's columns - which is also what keeps the pipe busy with N = 128 MMAs.
+template <bool PXM, int NCH, bool DUAL = false>
+__global__ void __launch_bounds__(PXM ? 288 : (DUAL ? 352 : 320), 1)
 convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const ConvhParams p) {
     constexpr int WSMAX = kConvhWStages;
     // MMA-issuing warps.  Channels on M: one.  Pixels on M: one per 8 x 16 pixel block of the tile, and with at most 64
     // output channels a second pair that takes k-steps 2 and 3 of every tap into accumulators of its own (added by the
     // epilogue): the short N <= 64 MMAs need four issuing threads to keep the tensor pipe busy.
     constexpr int KSPLIT = (PXM && NCH <= 2) ? 2 : 1;
-    constexpr int NISS = PXM ? 2 * KSPLIT : 1;
+    constexpr int NISS = PXM ? 2 * KSPLIT : (DUAL ? 2 : 1);
     const int WS = p.wstages;
     extern __shared__ uint8_t dyn_smem[];
     __shared__ __align__(8) uint64_t bar_hfull[2];
@@ -156,7 +161,7 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                 const int th = tt % p.tiles_h, n = tt / p.tiles_h;
                 const uint32_t full = smem_u32(&bar_hfull[slot]);
                 mbar_expect_tx(full, (uint32_t)p.halo_bytes);
-                tma_4d(halo_base + slot * (uint32_t)p.halo_stride, &tmX, hcc * 32, tw * kTW - p.pad, th * kTH - p.pad, n, full);
+                tma_4d(halo_base + slot * (uint32_t)p.halo_stride, &tmX, hcc * 32, tw * kTW - p.pad, th * kTH - p.pad, DUAL ? 2 * n : n, full);
                 hcount++;
                 if (++hcc == p.cchunks) { hcc = 0; ht += gridDim.x; }
             };
@@ -180,20 +185,21 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                 }
             }
         }
-    } else if (warp == 1 || (PXM && warp >= 6)) {
+    } else if (warp == 1 || (PXM && warp >= 6) || (DUAL && warp == 10)) {
         // ---------------- MMA issuers.  MMAs into one accumulator must come from one thread to stay ordered, and one
         // thread issues an MMA with fresh descriptors only every hundred-odd cycles; with the pixels on M the two
         // 8 x 16 pixel blocks of a tile have their own accumulators, so warp 1 issues the upper block and warp 6 the
         // lower one.  With the channels on M there is one accumulator and warp 1 issues alone.  The whole warp runs
         // the loop, lane 0 issues.
-        const int issuer = warp == 1 ? 0 : warp - 5;   // 0..3
+        const int issuer = warp == 1 ? 0 : (DUAL ? 1 : warp - 5);   // 0..3
         const int iss = issuer & 1, khalf = issuer >> 1;  // pixel block, half of the k-steps
         if (issuer < NISS) {
             const uint32_t leader = lane == 0 ? 1u : 0u;
             const uint64_t dw0 = smem_desc(w_base, 16u, 1024u, 2u);                      // weight tile: K-major, dense 8-row groups
             const uint64_t dh0 = smem_desc(halo_base, 16u, (uint32_t)p.pitch * 128u, 2u);  // halo: 8-row groups one halo line apart
             const uint32_t idesc_px = idesc_tf32(128u, (uint32_t)(NCH * 32), false, false);
-            const uint64_t sub_off = (uint64_t)(((uint32_t)(16 * iss * p.pitch) * 128u) >> 4);  // this issuer's 8 x 16 pixel block
+            // this issuer's 8 x 16 pixel block (pixels on M), or its image of the pair (DUAL)
+            const uint64_t sub_off = (uint64_t)(((uint32_t)((DUAL ? p.half_rows : 16) * iss * p.pitch) * 128u) >> 4);
             int s = 0;
             uint32_t ph = 0, tile_iter = 0, hcount = 0;
             bool ok = true;
@@ -201,12 +207,12 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                 const uint32_t ab = tile_iter & 1u;
                 const int th = ((t % p.tiles_px) / p.tiles_w) % p.tiles_h;
                 const int rows = (p.Ho - th * kTH) < kTH ? (p.Ho - th * kTH) : kTH;
-                const uint32_t idesc_ch = idesc_tf32(128u, (uint32_t)(8 * ((rows + 1) & ~1)), false, false);
+                const uint32_t idesc_ch = idesc_tf32(128u, DUAL ? 128u : (uint32_t)(8 * ((rows + 1) & ~1)), false, false);
                 const bool active = !PXM || rows > 16 * iss;   // a short tile has no lower block: that issuer only keeps the barriers moving
                 ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_acc_empty[ab]), ((tile_iter >> 1) & 1u) ^ 1u, p.err, 0x500u + ab, abortp));
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t acc = tmem_base + ab * 256u + (uint32_t)(PXM ? khalf * 128 + iss * NCH * 32 : 0);
+                const uint32_t acc = tmem_base + ab * 256u + (uint32_t)(PXM ? khalf * 128 + iss * NCH * 32 : (DUAL ? iss * 128 : 0));
                 for (int cc = 0; cc < p.cchunks && ok; cc++, hcount++) {
                     const uint32_t slot = hcount & 1u;
                     ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_hfull[slot]), (hcount >> 1) & 1u, p.err, 0x700u + slot, abortp));
@@ -827,12 +833,12 @@ dwh_kernel(const __grid_constant__ CUtensorMap tmDy, const __grid_constant__ CUt
 // ------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------
-template <bool PXM, int NCH>
+template <bool PXM, int NCH, bool DUAL = false>
 static int convh_launch(const CUtensorMap& tw, const CUtensorMap& tx, ConvhParams& p, int smem, double flops, cudaStream_t st) {
     static bool attr_set = false;
     if (!attr_set) {
-        NCC_TRY(cudaFuncSetAttribute(convh_kernel<PXM, NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     2 * 44 * 1024 + 6 * kWTileBytes + 1024));
+        NCC_TRY(cudaFuncSetAttribute(convh_kernel<PXM, NCH, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     2 * 46 * 1024 + 6 * kWTileBytes + 1024));
         attr_set = true;
     }
     const long long total = (long long)p.tiles_px * p.tiles_m;
@@ -855,7 +861,7 @@ static int convh_launch(const CUtensorMap& tw, const CUtensorMap& tx, ConvhParam
     }
     {
         ncc::ProfScope prof(ncc::prof_role(), flops, st, true);
-        convh_kernel<PXM, NCH><<<grid, PXM ? (NCH <= 2 ? 288 : 224) : 320, smem, st>>>(tw, tx, p);
+        convh_kernel<PXM, NCH, DUAL><<<grid, PXM ? (NCH <= 2 ? 288 : 224) : (DUAL ? 352 : 320), smem, st>>>(tw, tx, p);
     }
     NCC_COUNT_LAUNCH();
     if (p.bnx) ncc::bn_fold_publish(p.D, (int)slabs, p.stat);
@@ -871,9 +877,10 @@ int conv_halo_nhwc(float* y, const float* x, const float* wpacked, const float* 
     if ((Cin % 32) || (Cout % 4) || Cout < 16) return NC_CUDA_ERR_UNSUPPORTED;
     if ((long long)N * Ho * Wo * Cout >= 0x7fffffffLL) return NC_CUDA_ERR_UNSUPPORTED;
     // Tiles are 8 pixels wide and up to 32 high.  With the channels on M one thread issues all MMAs of a tile, which
-    // only keeps the tensor pipe busy with N = 8 * rows = 256; images lower than 24 rows (16 x 16: N = 128) run faster
-    // on the per-tap kernel, whose 256-pixel boxes span several images.
-    if (Ho < 24) return NC_CUDA_ERR_UNSUPPORTED;
+    // only keeps the tensor pipe busy with N = 8 * rows = 256.  Images of exactly 16 rows go two to a tile (DUAL, channels on
+    // M only); other images lower than 24 rows run faster on the per-tap kernel, whose 256-pixel boxes span several images.
+    const bool dual = Ho == 16 && (N % 2 == 0) && !(Cout % 32 == 0 && Cout <= 96);
+    if (Ho < 24 && !dual) return NC_CUDA_ERR_UNSUPPORTED;
     // Pixels on M for up to 96 output channels (measured on the 64-channel 64 x 64 layer at batch 256: 447 against 344
     // TFLOP/s with the channels on M); from 128 channels on, channels on M with N = 256 pixels is the faster shape
     // (698 against 636 TFLOP/s on the 128-channel 32 x 32 layer).
@@ -887,13 +894,14 @@ int conv_halo_nhwc(float* y, const float* x, const float* wpacked, const float* 
     if (!make_map(&tw, wpacked, 2, wd, ws, wb, false)) return NC_CUDA_ERR_UNSUPPORTED;
     unsigned long long dims[4] = {(unsigned long long)Cin, (unsigned long long)W, (unsigned long long)H, (unsigned long long)N};
     unsigned long long str[3] = {(unsigned long long)Cin, (unsigned long long)W * Cin, (unsigned long long)H * W * Cin};
-    unsigned box[4] = {32, (unsigned)(kTW + kW - 1), (unsigned)(kTH + kH - 1), 1};
+    unsigned box[4] = {32, (unsigned)(kTW + kW - 1), (unsigned)(dual ? Ho + kH - 1 : kTH + kH - 1), dual ? 2u : 1u};
     if (!make_map(&tx, x, 4, dims, str, box, false)) return NC_CUDA_ERR_UNSUPPORTED;
     ConvhParams p = {};
     p.D = y; p.ldd = Cout; p.bias = bias; p.M = Cout;
-    p.Ho = Ho; p.Wo = Wo;
-    p.tiles_w = (Wo + kTW - 1) / kTW; p.tiles_h = (Ho + kTH - 1) / kTH;
-    p.tiles_px = N * p.tiles_w * p.tiles_h;
+    p.Ho = dual ? 2 * Ho : Ho; p.Wo = Wo;   // DUAL: N / 2 "images" of 32 rows as far as the output is concerned
+    p.tiles_w = (Wo + kTW - 1) / kTW; p.tiles_h = (p.Ho + kTH - 1) / kTH;
+    p.tiles_px = (dual ? N / 2 : N) * p.tiles_w * p.tiles_h;
+    p.half_rows = Ho + kH - 1;
     p.tiles_m = pxm ? Cout / ncol : (Cout + kBM - 1) / kBM;
     p.kH = kH; p.kW = kW; p.pad = pad;
     p.cchunks = Cin / 32;
@@ -903,7 +911,7 @@ int conv_halo_nhwc(float* y, const float* x, const float* wpacked, const float* 
     p.wstages = 6 * kWTileBytes / p.wslot_bytes;
     if (p.wstages > kConvhWStages) p.wstages = kConvhWStages;
     p.pitch = kTW + kW - 1;
-    p.halo_bytes = p.pitch * (kTH + kH - 1) * 128;
+    p.halo_bytes = p.pitch * (dual ? 2 * (Ho + kH - 1) : kTH + kH - 1) * 128;
     p.halo_stride = (p.halo_bytes + 1023) & ~1023;
     p.err = ncc::device_error_word();
     const int smem = 2 * p.halo_stride + 6 * kWTileBytes + 1024;
@@ -915,6 +923,7 @@ int conv_halo_nhwc(float* y, const float* x, const float* wpacked, const float* 
             case 3: return convh_launch<true, 3>(tw, tx, p, smem, flops, st);
         }
     }
+    if (dual) return convh_launch<false, 0, true>(tw, tx, p, smem, flops, st);
     return convh_launch<false, 0>(tw, tx, p, smem, flops, st);
 }
 

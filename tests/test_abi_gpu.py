@@ -395,6 +395,9 @@ CONV_CASES = [
     (2, 64, 32, 8, 64, 1, 1, 0),    # 1 x 1 filter
     (2, 64, 56, 56, 64, 3, 1, 1),   # the isolated-backward benchmark's layer at a small batch (ragged in h: 56 = 32 + 24)
     (3, 128, 16, 16, 128, 3, 1, 1), # half-height tile
+    (6, 256, 16, 16, 256, 3, 1, 1), # 16-row images, even batch: two images per tile, one issuing warp each
+    (2, 128, 16, 24, 128, 3, 1, 1), # the same, three tiles wide
+    (4, 128, 16, 12, 160, 3, 1, 1), # the same, ragged in width and in the channel tile
     (2, 64, 20, 12, 32, 3, 1, 1),   # ragged in both directions
 ]
 
