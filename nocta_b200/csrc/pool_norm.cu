@@ -11,6 +11,10 @@ using namespace ncc;
 namespace {
 
 constexpr int kThreads = 256;
+// tensors above this size cannot stay in the 126 MB L2 between two kernels: passes that read or write them exactly once use
+// streaming (evict-first) accesses in the two plain apply kernels, which measured 2 - 3 % faster on the BatchNorm family of the
+// 268 MB layers (the fused pooling kernels got slower with the same hints: their four window positions share lines)
+constexpr size_t kStreamBytes = 100ull << 20;
 
 // =============================================================================================
 // Max pooling
@@ -550,15 +554,16 @@ __global__ void __launch_bounds__(kThreads) bn_apply_nhwc4_kernel(float4* __rest
     }
 #pragma unroll 4
     for (size_t i = tid; i < nvec; i += total) {
-        const float4 t = x[i];
+        const float4 t = (rnd & 2) ? __ldcs(&x[i]) : x[i];   // bit 1: tensors larger than L2, read and written once: streaming hints
         float o[4] = {g[0] * ((t.x - mu[0]) * is[0]) + b[0], g[1] * ((t.y - mu[1]) * is[1]) + b[1],
                       g[2] * ((t.z - mu[2]) * is[2]) + b[2], g[3] * ((t.w - mu[3]) * is[3]) + b[3]};
 #pragma unroll
         for (int v = 0; v < 4; v++) {
             if (RELU && !(o[v] > 0.f)) o[v] = 0.f;
-            if (rnd) o[v] = round_tf32(o[v]);
+            if (rnd & 1) o[v] = round_tf32(o[v]);
         }
-        y[i] = make_float4(o[0], o[1], o[2], o[3]);
+        if (rnd & 2) __stcs(&y[i], make_float4(o[0], o[1], o[2], o[3]));
+        else y[i] = make_float4(o[0], o[1], o[2], o[3]);
     }
 }
 
@@ -585,8 +590,8 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_apply_nhwc4_kernel(float4* __
     }
 #pragma unroll 2
     for (size_t i = tid; i < nvec; i += total) {
-        const float4 t = x[i];
-        const float4 u = dy[i];
+        const float4 t = (rnd & 2) ? __ldcs(&x[i]) : x[i];
+        const float4 u = (rnd & 2) ? __ldcs(&dy[i]) : dy[i];
         float4 yv = make_float4(1.f, 1.f, 1.f, 1.f);
         if (MASK == 1) yv = yfwd[i];
         const float xv[4] = {t.x, t.y, t.z, t.w}, yy[4] = {yv.x, yv.y, yv.z, yv.w};
@@ -597,9 +602,10 @@ __global__ void __launch_bounds__(kThreads) bn_bwd_apply_nhwc4_kernel(float4* __
             if (MASK == 1 && !(yy[v] > 0.f)) gv[v] = 0.f;
             if (MASK == 2 && !((g[v] * xh + b[v]) > 0.f)) gv[v] = 0.f;
             o[v] = coeff[v] * (Mf * gv[v] - s1[v] - xh * s2[v]);
-            if (rnd) o[v] = round_tf32(o[v]);
+            if (rnd & 1) o[v] = round_tf32(o[v]);
         }
-        dx[i] = make_float4(o[0], o[1], o[2], o[3]);
+        if (rnd & 2) __stcs(&dx[i], make_float4(o[0], o[1], o[2], o[3]));
+        else dx[i] = make_float4(o[0], o[1], o[2], o[3]);
     }
 }
 
@@ -645,7 +651,7 @@ __global__ void __launch_bounds__(kThreads) bn_relu_pool2_fwd_kernel(float4* __r
                 if (o > best[v]) { best[v] = o; bi[v] = pos; }
             }
         }
-        if (rnd) {   // rounding is monotonic: the rounded maximum is the maximum of the rounded values
+        if (rnd & 1) {   // rounding is monotonic: the rounded maximum is the maximum of the rounded values
 #pragma unroll
             for (int v = 0; v < 4; v++) best[v] = round_tf32(best[v]);
         }
@@ -733,7 +739,7 @@ __global__ void __launch_bounds__(kThreads) bn_relu_pool2_bwd_apply_kernel(float
                 float gv = sel[v] == pos ? gp[v] : 0.f;
                 if (!((g[v] * xh + b[v]) > 0.f)) gv = 0.f;
                 o[v] = coeff[v] * (Mf * gv - s1[v] - xh * s2[v]);
-                if (rnd) o[v] = round_tf32(o[v]);
+                if (rnd & 1) o[v] = round_tf32(o[v]);
             }
             dx[at] = make_float4(o[0], o[1], o[2], o[3]);
         }
@@ -994,8 +1000,9 @@ int nc_cuda_batchnorm_forward_f32_ex(float* y, const float* x, const float* gamm
     } else {
         if (vec) {
             const int g4 = nhwc4_grid(nvec, C);
-            if (relu) bn_apply_nhwc4_kernel<1><<<g4, kThreads, 0, st>>>((float4*)y, (const float4*)x, gamma, beta, save_mean, save_var, fe, C, nvec, round_outputs() ? 1 : 0);
-            else bn_apply_nhwc4_kernel<0><<<g4, kThreads, 0, st>>>((float4*)y, (const float4*)x, gamma, beta, save_mean, save_var, fe, C, nvec, round_outputs() ? 1 : 0);
+            const int flags = (round_outputs() ? 1 : 0) | (total * 4 > kStreamBytes ? 2 : 0);
+            if (relu) bn_apply_nhwc4_kernel<1><<<g4, kThreads, 0, st>>>((float4*)y, (const float4*)x, gamma, beta, save_mean, save_var, fe, C, nvec, flags);
+            else bn_apply_nhwc4_kernel<0><<<g4, kThreads, 0, st>>>((float4*)y, (const float4*)x, gamma, beta, save_mean, save_var, fe, C, nvec, flags);
         } else bn_apply_kernel<1, 1><<<grid, kThreads, 0, st>>>(y, x, gamma, beta, save_mean, save_var, fe, C, spatial, nvec, relu, round_outputs() ? 1 : 0);
     }
     NCC_COUNT_LAUNCH();
@@ -1041,7 +1048,7 @@ int nc_cuda_batchnorm_backward_f32_ex(float* dx, float* dgamma, float* dbeta, co
     } else {
         if (vec) {
             const int g4 = nhwc4_grid(nvec, C);
-            const int rnd = round_outputs() ? 1 : 0;
+            const int rnd = (round_outputs() ? 1 : 0) | (total * 4 > kStreamBytes ? 2 : 0);
             if (relu_out) bn_bwd_apply_nhwc4_kernel<1><<<g4, kThreads, 0, st>>>((float4*)dx, (const float4*)dy, (const float4*)x, (const float4*)relu_out, gamma, relu_beta, save_mean, save_var, sums, fe, Mf, C, nvec, rnd);
             else if (relu_recompute) bn_bwd_apply_nhwc4_kernel<2><<<g4, kThreads, 0, st>>>((float4*)dx, (const float4*)dy, (const float4*)x, nullptr, gamma, relu_beta, save_mean, save_var, sums, fe, Mf, C, nvec, rnd);
             else bn_bwd_apply_nhwc4_kernel<0><<<g4, kThreads, 0, st>>>((float4*)dx, (const float4*)dy, (const float4*)x, nullptr, gamma, relu_beta, save_mean, save_var, sums, fe, Mf, C, nvec, rnd);
