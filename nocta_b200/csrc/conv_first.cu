@@ -1,9 +1,12 @@
-// First-layer convolution (3 input channels, 3x3, stride 1) with a channels-last output: the case the
-// tensor-core implicit GEMM cannot tile (reduction length 27) and that is bound by writing the output,
-// not by arithmetic.  Forward: a shared-memory tiled kernel for the common channel counts (below), else
-// 4..16 threads per output pixel, 16 output channels each, the 27 patch values in registers.  Weight gradient: the reduction over all
-// pixels is split over CTAs; each CTA stages 64-pixel tiles of dY and of the 27-wide patches in shared
-// memory (see dw_tile_kernel); per-CTA partial sums are combined in a fixed order.  No input gradient: the network input needs none.
+// First-layer convolution (3 input channels, 3x3, stride 1) with a channels-last output: reduction length 27, bound by writing
+// the output (forward) or reading the output gradient (weight gradient), not by arithmetic.
+// TF32 mode with 64 output channels: tensor-core kernels (namespaces tcf and tcw below) whose operand rows are the 27-wide
+// patches padded to 32 floats, built in shared memory by the threads themselves.
+// Other modes and channel counts: CUDA-core kernels.  Forward: a shared-memory tiled kernel for the common channel counts,
+// else 4..16 threads per output pixel, 16 output channels each, the 27 patch values in registers.  Weight gradient: the
+// reduction over all pixels is split over CTAs; each CTA stages 64-pixel tiles of dY and of the 27-wide patches in shared
+// memory (see dw_tile_kernel); per-CTA partial sums are combined in a fixed order.  No input gradient: the network input
+// needs none.
 // Semantics: src/nn/conv.c:269-299 (dW), :381-586 (forward) of the reference.
 #include "nc_common.cuh"
 #include "tc_ptx.cuh"
