@@ -15,13 +15,20 @@
 //
 //   convh_kernel<false>  forward / input gradient, output channels on M (weights = A, streamed one filter row per
 //                        stage), 8 x <=32 pixels of one image on N (halo = B).  One MMA of N = 8 * rows per k-step, one
-//                        issuing warp.  Used from 128 output channels on.
+//                        issuing warp.  Used from 128 output channels on.  Eight epilogue warps (two per quarter of the
+//                        accumulator's lanes): one warp per scheduler executes dependent epilogue code at a few cycles
+//                        per instruction, which bounded the kernel as soon as the epilogue did more than store.  Its
+//                        epilogue can also sum, per channel, what the backward pass of a BatchNorm+ReLU that produced
+//                        this convolution's input needs (see nc_cuda_offer_batchnorm_backward_sums_f32).
+//   convh_kernel<false, 0, true>  the same for images of exactly 16 rows: two images per tile, each with its own issuing
+//                        warp (N = 128) and half of the accumulator's columns.
 //   convh_kernel<true>   the same convolution with the roles swapped for layers with at most 96 output channels: 8 x 16
 //                        pixels on M (halo = A), all output channels on N (weights = B).  An MMA costs
 //                        max(N / 2, operand bytes / 128, ~46) cycles whatever M is, so 64 channels on M run at half
 //                        rate while 128 pixels on M with N = 64 run at two thirds.  The two 8 x 16 blocks of a tile have
 //                        their own accumulators and issuing warps; up to 64 channels a second pair of warps takes
-//                        k-steps 2 and 3 into accumulators of its own, which the epilogue adds.
+//                        k-steps 2 and 3 into accumulators of its own, which the epilogue adds.  The epilogue transposes
+//                        each 32 pixel x 32 channel block through shared memory so that a warp stores whole lines.
 //   dwh_kernel<false>    weight gradient for Cin % 128 == 0: A = dY tile (128 output channels, MN-major), B = x halo
 //                        tile (128 input channels, MN-major); one filter row per work item, the kW taps of the row are kW
 //                        MMAs per 8-pixel k-step against the same two tiles (B start moved by kw pixel rows) into kW
