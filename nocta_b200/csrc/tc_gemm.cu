@@ -633,7 +633,15 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(float* __restrict__ 
     const size_t total = (size_t)M * N, stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         double acc = 0.0;   // the splits are combined in double, in order: no rounding that grows with their number
-        for (int z = 0; z < splits; z++) acc += (double)partial[(size_t)z * total + i];
+        int z = 0;
+        for (; z + 8 <= splits; z += 8) {   // eight loads requested before the first one is added
+            float v[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) v[k] = partial[(size_t)(z + k) * total + i];
+#pragma unroll
+            for (int k = 0; k < 8; k++) acc += (double)v[k];
+        }
+        for (; z < splits; z++) acc += (double)partial[(size_t)z * total + i];
         const int m = (int)(i / N), n = (int)(i % N);
         float* d = D + (size_t)m * ldd + n;
         float o = alpha * (float)acc;
@@ -643,20 +651,29 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(float* __restrict__ 
     }
 }
 
-// partial[z][co][(kh*kW+kw)*Cin + ci]  ->  dW[co][ci][kh][kw]
+// partial[z][co][(kh*kW+kw)*Cin + ci]  ->  dW[co][ci][kh][kw].  Threads walk the SOURCE order (coalesced reads of every split;
+// walking the destination order reads with a stride of Cin floats, eight times the sectors), eight splits are requested
+// before the first one is added, and only the single write per element is scattered.
 __global__ void __launch_bounds__(256) dw_reduce_kernel(float* __restrict__ dW, const float* __restrict__ partial, int splits,
                                                         int Cout, int Cin, int kH, int kW) {
-    const size_t total = (size_t)Cout * Cin * kH * kW, stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        size_t r = i;
-        const int kw = r % kW; r /= kW;
-        const int kh = r % kH; r /= kH;
-        const int ci = r % Cin;
-        const int co = (int)(r / Cin);
-        const size_t src = (size_t)co * (kH * kW * Cin) + (size_t)(kh * kW + kw) * Cin + ci;
+    const int T = kH * kW;
+    const size_t total = (size_t)Cout * Cin * T, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t src = (size_t)blockIdx.x * blockDim.x + threadIdx.x; src < total; src += stride) {
         double acc = 0.0;
-        for (int z = 0; z < splits; z++) acc += (double)partial[(size_t)z * total + src];
-        dW[i] = (float)acc;
+        int z = 0;
+        for (; z + 8 <= splits; z += 8) {
+            float v[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) v[k] = partial[(size_t)(z + k) * total + src];
+#pragma unroll
+            for (int k = 0; k < 8; k++) acc += (double)v[k];
+        }
+        for (; z < splits; z++) acc += (double)partial[(size_t)z * total + src];
+        const int ci = (int)(src % Cin);
+        const size_t r = src / Cin;
+        const int tap = (int)(r % T);
+        const size_t co = r / T;
+        dW[(co * Cin + ci) * T + tap] = (float)acc;
     }
 }
 
