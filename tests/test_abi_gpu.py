@@ -579,7 +579,8 @@ def test_batchnorm_takes_statistics_offered_by_the_convolution(abi, shape):
         abi.nc_cuda_set_conv_stats(prev)
 
 
-@pytest.mark.parametrize("shape", [(4, 128, 32, 128), (2, 128, 27, 160), (3, 256, 40, 64), (2, 160, 24, 128), (5, 128, 26, 32)])
+@pytest.mark.parametrize("shape", [(4, 128, 32, 128), (2, 128, 27, 160), (3, 256, 40, 64), (2, 160, 24, 128), (5, 128, 26, 32),
+                                   (4, 256, 16, 256), (6, 128, 16, 64)])   # the last two: 16-row images, two per tile
 def test_batchnorm_backward_takes_sums_from_the_input_gradient_convolution(abi, shape):
     """nc_cuda_offer_batchnorm_backward_sums_f32: the input-gradient convolution that writes the upstream gradient of a
     BatchNorm+ReLU also sums g' and g' * xhat per channel, and the BatchNorm backward called right after it skips its own
