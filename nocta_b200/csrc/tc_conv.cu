@@ -949,8 +949,10 @@ static bool pick_dw_tile(int Wo, int Ho, int kW, int halo_rows, int nchunk_dy, i
             if (sb * min_stages > kMaxDynSmem - 1024) continue;
             const int hblocks = (Ho + r - 1) / r;
             const double useful = (double)Wo * Ho / ((double)tiles_w * tw * hblocks * r);
-            // prefer useful pixels, then less halo re-read, then larger stages (fewer barrier round trips)
-            const double score = useful * 1000.0 - (double)(r + halo_rows) / r * 10.0 + (tw * r >= 64 ? 1.0 : 0.0) + tw * r * 1e-3;
+            // prefer useful pixels, then stages of up to 128 pixels (fewer barrier round trips: measured 6 % on the 56 x 56
+            // layer, 56 x 2 against 8 x 8 pixels per stage) weighed against the halo lines read again per stage
+            const int px = tw * r;
+            const double score = useful * 1000.0 - (double)(r + halo_rows) / r * 10.0 + (px < 128 ? px : 128) * 0.2 + px * 1e-3;
             if (score > best) { best = score; *TW = tw; *R = r; *stage_bytes = sb; *a_stride_dy = dy_stride; *b_stride_x = x_stride; }
         }
     }
