@@ -11,7 +11,8 @@
 // fresh descriptors every 65 - 80 cycles at best, a barrier test costs it another ~180 cycles, while the tensor pipe needs
 // 128 cycles for M = 128, N = 256, 64 for N = 128 and 48 for N = 64 (K = 8).  MMAs into ONE accumulator must come from one
 // thread to stay ordered, but different accumulators can be issued by different warps.  So: one barrier round trip covers
-// a whole filter row of taps (12 MMAs), and wherever a tile has several accumulators they get an issuing warp each.
+// as many filter taps as leave two weight stages in shared memory (a filter row of 128-row weight tiles, five taps of 64-row
+// ones), and wherever a tile has several accumulators they get an issuing warp each.
 //
 //   convh_kernel<false>  forward / input gradient, output channels on M (weights = A, streamed one filter row per
 //                        stage), 8 x <=32 pixels of one image on N (halo = B).  One MMA of N = 8 * rows per k-step, one
@@ -78,10 +79,11 @@ struct ConvhParams {
     int wrows;             // rows per tap in the packed weights
     int wbox_bytes;        // bytes one weight copy delivers
     int wstages;           // weight ring depth: slots of wslot_bytes in the 96 KB weight region
-    int wslot_bytes;       // one slot holds the kW taps of a filter row (one mbarrier round trip per 4 * kW MMAs)
+    int wslot_bytes;       // one slot holds `tps` taps (one mbarrier round trip per 4 * tps MMAs)
     int pitch;             // halo line pitch in pixels
     int halo_bytes, halo_stride;
     int half_rows;         // DUAL: halo lines per image (the tile holds two images of 16 rows, one above the other)
+    int tps;               // filter taps per weight stage, in (kh, kw) order; the last stage of a chunk may hold fewer
     double* stat;          // non-null: per CTA and channel (sum, sum of squares) of the output it wrote, [gridDim.x][M][2]
     // non-null bnx: the output is the upstream gradient g of a BatchNorm+ReLU with input bnx (same shape and strides as D);
     // stat then receives (sum of g', sum of g' * xhat), g' = g where gamma * xhat + beta > 0 and 0 elsewhere
@@ -179,14 +181,15 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                 const int m0 = (t / p.tiles_px) * (PXM ? NCH * 32 : kBM);
                 for (int cc = 0; cc < p.cchunks && ok; cc++) {
                     int wrow = m0;
-                    for (int kh = 0; kh < p.kH; kh++) {
-                        if (kh == (p.kH > 1 ? 1 : 0)) issue_halo();   // the next chunk's halo, once this chunk is under way
+                    for (int t0 = 0; t0 < ntaps && ok; t0 += p.tps) {
+                        if (t0 == (ntaps > p.tps ? p.tps : 0)) issue_halo();   // the next chunk's halo, once this chunk is under way
                         if (!ok) break;
+                        const int nt = (ntaps - t0) < p.tps ? (ntaps - t0) : p.tps;
                         if (!mbar_wait(smem_u32(&bar_wempty[s]), ph ^ 1u, p.err, 0x100u + s, abortp)) { ok = false; break; }
                         const uint32_t full = smem_u32(&bar_wfull[s]);
-                        mbar_expect_tx(full, (uint32_t)(p.kW * p.wbox_bytes));
-                        for (int kw = 0; kw < p.kW; kw++, wrow += p.wrows)
-                            tma_2d(w_base + (uint32_t)(s * p.wslot_bytes + kw * p.wbox_bytes), &tmW, cc * 32, wrow, full);
+                        mbar_expect_tx(full, (uint32_t)(nt * p.wbox_bytes));
+                        for (int i = 0; i < nt; i++, wrow += p.wrows)
+                            tma_2d(w_base + (uint32_t)(s * p.wslot_bytes + i * p.wbox_bytes), &tmW, cc * 32, wrow, full);
                         if (++s == WS) { s = 0; ph ^= 1u; }
                     }
                 }
@@ -220,27 +223,33 @@ convh_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t acc = tmem_base + ab * 256u + (uint32_t)(PXM ? khalf * 128 + iss * NCH * 32 : (DUAL ? iss * 128 : 0));
+                uint32_t acc_started = 0u;   // the first MMA of a tile overwrites the accumulator
                 for (int cc = 0; cc < p.cchunks && ok; cc++, hcount++) {
                     const uint32_t slot = hcount & 1u;
                     ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_hfull[slot]), (hcount >> 1) & 1u, p.err, 0x700u + slot, abortp));
                     if (!ok) break;
                     const uint64_t dhs = dh0 + sub_off + (uint64_t)((slot * (uint32_t)p.halo_stride) >> 4);
-                    for (int kh = 0; kh < p.kH; kh++) {
+                    uint64_t dh_row = dhs;   // first pixel of filter row kh in this issuer's part of the halo
+                    int kw = 0;
+                    for (int t0 = 0; t0 < ntaps; t0 += p.tps) {
                         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_wfull[s]), ph, p.err, 0x200u + s, abortp));
                         if (!ok) break;
                         tc_fence_after();
+                        const int nt = (ntaps - t0) < p.tps ? (ntaps - t0) : p.tps;
                         uint64_t dw = dw0 + (uint64_t)(((uint32_t)s * (uint32_t)p.wslot_bytes) >> 4);
-                        uint64_t dh = dhs + (uint64_t)(((uint32_t)(kh * p.pitch) * 128u) >> 4);
-                        if (active) {
-                            for (int kw = 0; kw < p.kW; kw++, dw += (uint64_t)((uint32_t)p.wbox_bytes >> 4), dh += 8u) {
+                        for (int i = 0; i < nt; i++, dw += (uint64_t)((uint32_t)p.wbox_bytes >> 4)) {
+                            if (active) {
+                                const uint64_t dh = dh_row + (uint64_t)(uint32_t)(kw * 8);   // one halo pixel = 128 bytes = 8 units
 #pragma unroll
                                 for (int k2 = 0; k2 < 4 / KSPLIT; k2++) {
                                     const int ks = khalf * (4 / KSPLIT) + k2;
-                                    const uint32_t accum = (uint32_t)((cc | kh | kw | k2) != 0);
+                                    const uint32_t accum = acc_started | (uint32_t)(k2 != 0);
                                     if (PXM) umma_tf32_w(acc, dh + (uint64_t)(ks * 2), dw + (uint64_t)(ks * 2), idesc_px, accum, leader);
                                     else umma_tf32_w(acc, dw + (uint64_t)(ks * 2), dh + (uint64_t)(ks * 2), idesc_ch, accum, leader);
                                 }
+                                acc_started = 1u;
                             }
+                            if (++kw == p.kW) { kw = 0; dh_row += (uint64_t)((uint32_t)p.pitch * 8u); }
                         }
                         umma_commit_w(smem_u32(&bar_wempty[s]), leader);
                         if (++s == WS) { s = 0; ph ^= 1u; }
@@ -914,7 +923,19 @@ int conv_halo_nhwc(float* y, const float* x, const float* wpacked, const float* 
     p.cchunks = Cin / 32;
     p.wrows = Cout;
     p.wbox_bytes = (pxm ? ncol : 128) * 128;
-    p.wslot_bytes = (kW * p.wbox_bytes + 1023) & ~1023;
+    // Taps per weight stage: as many as leave two stages in the 96 KB weight region, spread evenly over the stages of a
+    // chunk.  Every stage costs each issuing warp a barrier round trip of ~200 cycles during which it issues nothing, so
+    // two large stages beat four small ones (64 channels, 64 x 64: five taps per stage 487 / 499 TFLOP/s against 447 / 467
+    // with three); 128-row weight tiles (channels on M) fit three taps, a filter row, as before.
+    {
+        const int ntaps = kH * kW;
+        int fit = (3 * kWTileBytes) / p.wbox_bytes;
+        if (fit > ntaps) fit = ntaps;
+        if (fit < 1) fit = 1;
+        const int per_chunk = (ntaps + fit - 1) / fit;
+        p.tps = (ntaps + per_chunk - 1) / per_chunk;
+    }
+    p.wslot_bytes = (p.tps * p.wbox_bytes + 1023) & ~1023;
     p.wstages = 6 * kWTileBytes / p.wslot_bytes;
     if (p.wstages > kConvhWStages) p.wstages = kConvhWStages;
     p.pitch = kTW + kW - 1;
